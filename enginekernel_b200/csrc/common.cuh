@@ -1,0 +1,93 @@
+// Shared helpers for the sm_100a kernels of enginekernel_b200.
+//
+// Every launcher is an extern "C" function that takes raw device pointers, sizes
+// and a cudaStream_t, launches on that stream and returns 0 or a CUDA error code
+// (negative values are argument errors found before any launch).  Nothing here
+// allocates memory.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define EK_PAGE 64          // tokens per cache page (must match cache/pages.py)
+#define EK_MAX_HEAD_DIM 256
+
+#define EK_ERR_ARG (-2)      // a size the kernel does not take
+#define EK_EXPORT extern "C" __attribute__((visibility("default")))
+
+namespace ek {
+
+typedef __nv_bfloat16 bf16;
+
+template <typename T> __device__ __forceinline__ float to_f(T v);
+template <> __device__ __forceinline__ float to_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f<bf16>(bf16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f(float v);
+template <> __device__ __forceinline__ float from_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ bf16 from_f<bf16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Sum over a block whose size is a multiple of 32 (at most 1024 threads).
+// `scratch` holds 33 floats of shared memory; every thread gets the result.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  v = warp_sum(v);
+  __syncthreads();                       // scratch may still be read from an earlier call
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    const int nw = (blockDim.x + 31) >> 5;
+    float t = lane < nw ? scratch[lane] : 0.f;
+    t = warp_sum(t);
+    if (lane == 0) scratch[32] = t;
+  }
+  __syncthreads();
+  return scratch[32];
+}
+__device__ __forceinline__ float block_max(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  v = warp_max(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    const int nw = (blockDim.x + 31) >> 5;
+    float t = lane < nw ? scratch[lane] : -INFINITY;
+    t = warp_max(t);
+    if (lane == 0) scratch[32] = t;
+  }
+  __syncthreads();
+  return scratch[32];
+}
+
+// Where the keys and values of one cache entry live.  A page holds EK_PAGE
+// consecutive positions of one sequence for all KV heads:
+//   base[((page * heads + head) * EK_PAGE + pos % EK_PAGE) * head_dim + d]
+// `block_table[slot * table_stride + pos / EK_PAGE]` gives the page of a position.
+struct PagedKV {
+  void* k;                  // this entry's key pages
+  void* v;                  // this entry's value pages
+  const int* block_table;   // [slots, table_stride]
+  int table_stride;
+  int heads;                // KV heads
+  int head_dim;
+};
+
+__device__ __forceinline__ size_t page_offset(const PagedKV& c, int page, int head, int pos) {
+  return (((size_t)page * c.heads + head) * EK_PAGE + (pos & (EK_PAGE - 1))) * (size_t)c.head_dim;
+}
+
+}  // namespace ek
+
+#define EK_RETURN_LAUNCH_STATUS() return (int)cudaGetLastError()

@@ -1,0 +1,117 @@
+// Per-head RMSNorm of queries and keys, rotary position encoding, and the write of
+// keys and values into the paged cache - one pass over the fused q/k/v rows.
+//
+// Same work as the reference's _qk_norm_rope_kv_kernel (engine/ek_kernels.py:223-279):
+// normalise each head over its dimension, rotate pairs (j, j + rot/2) by the angle of
+// the token's position (NeoX pairing, engine/ek_model.py:164-174), leave values
+// untouched, store keys and values at the token's place in its sequence's cache.
+// Differences: positions and slots come per token (no padded rectangle), the cache is
+// paged, and all arithmetic is 32-bit with one rounding at the end.
+#include "common.cuh"
+
+namespace ek {
+
+constexpr int kRopeWarps = 4;
+
+template <typename T>
+__global__ void qk_norm_rope_kv_kernel(T* __restrict__ qkv, int row_stride,
+                                       const float* __restrict__ q_gain,
+                                       const float* __restrict__ k_gain,
+                                       const float* __restrict__ cos_tab,
+                                       const float* __restrict__ sin_tab, int rot_dim,
+                                       const int* __restrict__ positions,
+                                       const int* __restrict__ token_slot, PagedKV cache,
+                                       int n_q_heads, float eps, int write_kv) {
+  __shared__ float buf[kRopeWarps][EK_MAX_HEAD_DIM];
+  const int t = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int head = blockIdx.y * kRopeWarps + warp;
+  const int n_kv = cache.heads, d = cache.head_dim;
+  if (head >= n_q_heads + 2 * n_kv) return;
+  const int pos = positions[t];
+  if (pos < 0) return;                        // a row of a finished sequence
+  const bool is_q = head < n_q_heads;
+  const bool is_k = !is_q && head < n_q_heads + n_kv;
+  if (!is_q && !write_kv) return;
+
+  T* src = qkv + (size_t)t * row_stride + (size_t)head * d;
+  T* dst = src;
+  if (!is_q) {
+    const int slot = token_slot[t];
+    const int page = cache.block_table[(size_t)slot * cache.table_stride + pos / EK_PAGE];
+    const int kv_head = is_k ? head - n_q_heads : head - n_q_heads - n_kv;
+    dst = (T*)(is_k ? cache.k : cache.v) + page_offset(cache, page, kv_head, pos);
+  }
+
+  if (!is_q && !is_k) {                       // values: a copy
+    for (int i = lane; i < d; i += 32) dst[i] = src[i];
+    return;
+  }
+
+  const float* gain = is_q ? q_gain : k_gain;
+  float ss = 0.f;
+  for (int i = lane; i < d; i += 32) {
+    const float v = to_f<T>(src[i]);
+    buf[warp][i] = v;
+    ss += v * v;
+  }
+  float rstd = 1.f;
+  if (gain) {
+    ss = warp_sum(ss);
+    rstd = rsqrtf(ss / (float)d + eps);
+  }
+  __syncwarp();
+  const int half = rot_dim >> 1;
+  const float* cs = cos_tab + (size_t)pos * half;
+  const float* sn = sin_tab + (size_t)pos * half;
+  for (int i = lane; i < d; i += 32) {
+    const float g = gain ? gain[i] : 1.f;
+    const float x = buf[warp][i] * rstd * g;
+    float out = x;
+    if (i < half) {
+      const float partner = buf[warp][i + half] * rstd * (gain ? gain[i + half] : 1.f);
+      out = x * cs[i] - partner * sn[i];
+    } else if (i < rot_dim) {
+      const int j = i - half;
+      const float partner = buf[warp][j] * rstd * (gain ? gain[j] : 1.f);
+      out = x * cs[j] + partner * sn[j];
+    }
+    dst[i] = from_f<T>(out);
+  }
+}
+
+template <typename T>
+static int launch(void* qkv, int row_stride, const float* q_gain, const float* k_gain,
+                  const float* cos_tab, const float* sin_tab, int rot_dim, const int* positions,
+                  const int* token_slot, void* k_pages, void* v_pages, const int* block_table,
+                  int table_stride, int n_tokens, int n_q_heads, int n_kv_heads, int head_dim,
+                  float eps, int write_kv, cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  if (head_dim <= 0 || head_dim > EK_MAX_HEAD_DIM || (head_dim & 1) || rot_dim < 0 ||
+      rot_dim > head_dim || (rot_dim & 1) || n_tokens > 2147483647 / 2)
+    return EK_ERR_ARG;
+  PagedKV cache{k_pages, v_pages, block_table, table_stride, n_kv_heads, head_dim};
+  const int heads = n_q_heads + 2 * n_kv_heads;
+  dim3 grid(n_tokens, (heads + kRopeWarps - 1) / kRopeWarps);
+  qk_norm_rope_kv_kernel<T><<<grid, kRopeWarps * 32, 0, stream>>>(
+      (T*)qkv, row_stride, q_gain, k_gain, cos_tab, sin_tab, rot_dim, positions, token_slot, cache,
+      n_q_heads, eps, write_kv);
+  EK_RETURN_LAUNCH_STATUS();
+}
+
+}  // namespace ek
+
+#define EK_INSTANTIATE(SUFFIX, T)                                                              \
+  EK_EXPORT int ek_qk_norm_rope_kv_##SUFFIX(                                                    \
+      void* qkv, int row_stride, const float* q_gain, const float* k_gain, const float* cos_tab, \
+      const float* sin_tab, int rot_dim, const int* positions, const int* token_slot,          \
+      void* k_pages, void* v_pages, const int* block_table, int table_stride, int n_tokens,    \
+      int n_q_heads, int n_kv_heads, int head_dim, float eps, int write_kv,                    \
+      cudaStream_t stream) {                                                                   \
+    return ek::launch<T>(qkv, row_stride, q_gain, k_gain, cos_tab, sin_tab, rot_dim, positions, \
+                         token_slot, k_pages, v_pages, block_table, table_stride, n_tokens,    \
+                         n_q_heads, n_kv_heads, head_dim, eps, write_kv, stream);              \
+  }
+
+EK_INSTANTIATE(f32, float)
+EK_INSTANTIATE(bf16, ek::bf16)

@@ -1,0 +1,276 @@
+"""Python faces of the CUDA kernels: argument checks, then one launch each.
+
+Every function takes CUDA tensors and launches on torch's current stream.  There is
+no CPU or torch fallback: a tensor that is not on a CUDA device, or a kernel library
+that cannot be built or loaded, raises.  The reference pairs every Triton kernel with
+a torch fallback chosen at call time (engine/ek_kernels.py:1025-1559); here the plain
+counterparts live only in the tests.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_ulonglong, c_void_p
+
+import torch
+
+from .lib import Function, KernelError
+
+PAGE = 64                 # tokens per cache page; must equal EK_PAGE in csrc/common.cuh
+MAX_HEAD_DIM = 256
+GEMV_MAX_ROWS = 64
+
+_SUFFIX = {torch.float32: "f32", torch.bfloat16: "bf16"}
+_P = c_void_p
+
+
+def _suffix(dtype) -> str:
+    try:
+        return _SUFFIX[dtype]
+    except KeyError:
+        raise KernelError(f"kernels exist for float32 and bfloat16, not {dtype}") from None
+
+
+def _ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _need_cuda(*tensors):
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise KernelError("enginekernel_b200 kernels run on CUDA tensors only; got a tensor on "
+                              f"{t.device} (there is no CPU path)")
+
+
+def _need(cond, msg):
+    if not cond:
+        raise KernelError(msg)
+
+
+def _per_dtype(module, name, argtypes):
+    return {dt: Function(module, f"{name}_{sfx}", argtypes) for dt, sfx in _SUFFIX.items()}
+
+
+# ------------------------------------------------------------------ elementwise
+_embed = _per_dtype("elementwise", "ek_embed", [_P, _P, _P, c_int, c_int, c_int, _P])
+_rmsnorm = _per_dtype("elementwise", "ek_rmsnorm",
+                      [_P, _P, _P, _P, _P, c_float, c_int, c_int, c_int, _P])
+_add_residual = _per_dtype("elementwise", "ek_add_residual", [_P, _P, c_longlong, _P])
+_silu_mul = _per_dtype("elementwise", "ek_silu_mul", [_P, _P, c_int, c_int, _P])
+
+
+def embed(resid, table, ids, n_tokens):
+    """resid[t, :] = table[ids[t], :] as 32-bit, for the first ``n_tokens`` ids."""
+    _need_cuda(resid, table, ids)
+    _need(resid.dtype == torch.float32 and ids.dtype == torch.int32, "embed: resid f32, ids int32")
+    _need(table.is_contiguous() and resid.is_contiguous(), "embed: contiguous tensors")
+    vocab, hidden = table.shape
+    _need(resid.shape[-1] == hidden and resid.shape[0] >= n_tokens, "embed: resid shape")
+    _embed[table.dtype](_ptr(resid), _ptr(table), _ptr(ids), n_tokens, hidden, vocab, _stream())
+
+
+def rmsnorm(y, resid, gain, eps, add=None, rows=None, n_rows=None, write_back=True):
+    """y = gain * n(resid [+ add]); with ``add`` the stream is updated in place when
+    ``write_back``.  ``rows`` (int32) picks stream rows; y then has one row per entry."""
+    _need_cuda(y, resid, gain, add, rows)
+    hidden = resid.shape[-1]
+    _need(resid.dtype == torch.float32 and gain.dtype == torch.float32, "rmsnorm: 32-bit stream and gain")
+    _need(gain.numel() == hidden and y.shape[-1] == hidden, "rmsnorm: sizes disagree")
+    _need(add is None or (add.dtype == y.dtype and add.shape[-1] == hidden and add.is_contiguous()),
+          "rmsnorm: add must have y's dtype and the stream's width")
+    _need(y.is_contiguous() and resid.is_contiguous(), "rmsnorm: contiguous tensors")
+    if n_rows is None:
+        n_rows = rows.numel() if rows is not None else resid.shape[0]
+    _need(y.shape[0] >= n_rows, "rmsnorm: y has too few rows")
+    _rmsnorm[y.dtype](_ptr(y), _ptr(resid), _ptr(add), _ptr(gain), _ptr(rows), float(eps),
+                      n_rows, hidden, 1 if write_back else 0, _stream())
+
+
+def add_residual(resid, x, n_rows=None):
+    _need_cuda(resid, x)
+    n = (n_rows if n_rows is not None else resid.shape[0]) * resid.shape[-1]
+    _need(resid.dtype == torch.float32 and x.shape[-1] == resid.shape[-1], "add_residual: shapes")
+    _add_residual[x.dtype](_ptr(resid), _ptr(x), n, _stream())
+
+
+def silu_mul(out, gu, n_rows=None):
+    """out[r, i] = silu(gu[r, i]) * gu[r, I + i] for gu of width 2I."""
+    _need_cuda(out, gu)
+    inter = gu.shape[-1] // 2
+    _need(gu.shape[-1] == 2 * inter and out.shape[-1] == inter and out.dtype == gu.dtype,
+          "silu_mul: out must be [rows, I] for gu [rows, 2I]")
+    _need(out.is_contiguous() and gu.is_contiguous(), "silu_mul: contiguous tensors")
+    rows = n_rows if n_rows is not None else gu.shape[0]
+    for r0 in range(0, rows, 65535):
+        r1 = min(rows, r0 + 65535)
+        _silu_mul[gu.dtype](_ptr(out[r0:]), _ptr(gu[r0:]), r1 - r0, inter, _stream())
+
+
+# ------------------------------------------------------------------ rope + cache write
+_rope_kv = _per_dtype("rope_kv", "ek_qk_norm_rope_kv",
+                      [_P, c_int, _P, _P, _P, _P, c_int, _P, _P, _P, _P, _P, c_int, c_int, c_int,
+                       c_int, c_int, c_float, c_int, _P])
+
+
+def check_head_dim(head_dim):
+    if head_dim % 16 or not 16 <= head_dim <= MAX_HEAD_DIM:
+        raise KernelError(f"head size {head_dim} is not supported: the attention kernels take "
+                          f"multiples of 16 from 16 to {MAX_HEAD_DIM}")
+
+
+def qk_norm_rope_kv(qkv, n_tokens, q_gain, k_gain, cos, sin, rot_dim, positions, token_slot,
+                    k_pages, v_pages, block_table, n_q_heads, n_kv_heads, head_dim, eps,
+                    write_kv=True):
+    """In place on the q part of ``qkv`` [T, (NQ + 2 NKV) D]; keys and values go to the pages."""
+    _need_cuda(qkv, cos, sin, positions, token_slot, k_pages, v_pages, block_table)
+    check_head_dim(head_dim)
+    _need(qkv.stride(-1) == 1 and qkv.shape[-1] == (n_q_heads + 2 * n_kv_heads) * head_dim,
+          "qk_norm_rope_kv: qkv width")
+    _need(cos.dtype == torch.float32 and sin.dtype == torch.float32 and cos.is_contiguous()
+          and cos.shape[-1] * 2 == rot_dim, "qk_norm_rope_kv: 32-bit tables of rot_dim/2 columns")
+    _need(k_pages.dtype == qkv.dtype and v_pages.dtype == qkv.dtype, "qk_norm_rope_kv: cache dtype")
+    _need(block_table.dtype == torch.int32 and positions.dtype == torch.int32
+          and token_slot.dtype == torch.int32, "qk_norm_rope_kv: int32 indices")
+    for g in (q_gain, k_gain):
+        _need(g is None or (g.dtype == torch.float32 and g.numel() == head_dim), "qk gains: 32-bit [D]")
+    _rope_kv[qkv.dtype](_ptr(qkv), qkv.stride(0), _ptr(q_gain), _ptr(k_gain), _ptr(cos), _ptr(sin),
+                        rot_dim, _ptr(positions), _ptr(token_slot), _ptr(k_pages), _ptr(v_pages),
+                        _ptr(block_table), block_table.stride(0), n_tokens, n_q_heads, n_kv_heads,
+                        head_dim, float(eps), 1 if write_kv else 0, _stream())
+
+
+# ------------------------------------------------------------------ attention
+_attn_generic = _per_dtype("attention_generic", "ek_attention_generic",
+                           [_P, _P, c_int, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int,
+                            c_float, c_int, c_int, c_int, _P, _P, _P])
+
+
+def attention_generic(out, q, n_tokens, positions, token_slot, k_pages, v_pages, block_table,
+                      n_q_heads, n_kv_heads, head_dim, scale, window=None, n_splits=1,
+                      keys_per_split=0, part_acc=None, part_ml=None):
+    """out[t, h*D:(h+1)*D] = softmax(scale q.K^T) V over the keys token t may see.
+
+    ``q`` is any tensor whose row t starts with the NQ*D query values (the fused q/k/v
+    rows qualify).  With ``n_splits`` > 1 the keys are cut every ``keys_per_split`` and
+    merged from ``part_acc`` [T, NQ, splits, D] / ``part_ml`` [T, NQ, splits, 2] (32-bit).
+    """
+    _need_cuda(out, q, positions, token_slot, k_pages, v_pages, block_table, part_acc, part_ml)
+    check_head_dim(head_dim)
+    _need(out.dtype == q.dtype == k_pages.dtype, "attention: one dtype for q, cache and out")
+    _need(out.is_contiguous() and out.shape[-1] == n_q_heads * head_dim, "attention: out [T, NQ*D]")
+    _need(q.stride(-1) == 1, "attention: q rows must be dense")
+    if n_splits > 1:
+        _need(part_acc is not None and part_ml is not None
+              and part_acc.numel() >= n_tokens * n_q_heads * n_splits * head_dim
+              and part_ml.numel() >= n_tokens * n_q_heads * n_splits * 2, "attention: split buffers")
+    _attn_generic[q.dtype](_ptr(out), _ptr(q), q.stride(0), _ptr(positions), _ptr(token_slot),
+                           _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.stride(0),
+                           n_tokens, n_q_heads, n_kv_heads, head_dim, float(scale),
+                           int(window or 0), n_splits, keys_per_split, _ptr(part_acc),
+                           _ptr(part_ml), _stream())
+
+
+# ------------------------------------------------------------------ matrix products
+_gemm_f32 = Function("gemm_f32", "ek_gemm_nt_f32",
+                     [_P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P])
+_gemv_bf16 = Function("gemv_bf16", "ek_gemv_bf16",
+                      [_P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P])
+
+EPI_BF16, EPI_F32, EPI_SWIGLU = 0, 1, 2
+
+
+def gemm_f32(out, x, w, n_rows=None):
+    """out[M, N] = x[M, K] . w[N, K]^T in true 32-bit."""
+    _need_cuda(out, x, w)
+    _need(out.dtype == x.dtype == w.dtype == torch.float32, "gemm_f32: float32 tensors")
+    _need(x.stride(-1) == 1 and w.stride(-1) == 1 and out.stride(-1) == 1, "gemm_f32: dense rows")
+    m = n_rows if n_rows is not None else x.shape[0]
+    n, k = w.shape
+    _need(x.shape[-1] == k and out.shape[-1] == n and out.shape[0] >= m, "gemm_f32: shapes disagree")
+    _gemm_f32(_ptr(out), _ptr(x), _ptr(w), m, n, k, x.stride(0), w.stride(0), out.stride(0), _stream())
+
+
+def _gemv_warps(n_tiles, k):
+    """Warps per block (they split K): enough blocks x warps to fill 148 SMs."""
+    chunks = max(1, k // 32)
+    want = max(4, min(16, -(-148 * 16 // max(1, n_tiles))))
+    w = 4
+    while w * 2 <= want and w * 2 <= chunks:
+        w *= 2
+    return w
+
+
+def gemv_bf16(out, x, w, epilogue=EPI_BF16, n_rows=None, warps=None):
+    """out = x . w^T for at most 64 rows of x, bfloat16 in, 32-bit accumulation.
+
+    ``epilogue``: EPI_BF16 -> out bfloat16 [M, N]; EPI_F32 -> out float32 [M, N];
+    EPI_SWIGLU -> w holds I gate rows then I up rows, out bfloat16 [M, I] = silu(g) * u.
+    """
+    _need_cuda(out, x, w)
+    m = n_rows if n_rows is not None else x.shape[0]
+    n, k = w.shape
+    _need(x.dtype == w.dtype == torch.bfloat16, "gemv_bf16: bfloat16 operands")
+    _need(m <= GEMV_MAX_ROWS, f"gemv_bf16: at most {GEMV_MAX_ROWS} rows")
+    _need(k % 8 == 0, f"gemv_bf16: inner size {k} must be a multiple of 8")
+    _need(x.stride(-1) == 1 and w.stride(-1) == 1 and out.stride(-1) == 1 and x.shape[-1] == k,
+          "gemv_bf16: dense rows of matching inner size")
+    n_out = n // 2 if epilogue == EPI_SWIGLU else n
+    _need(out.shape[-1] == n_out and out.shape[0] >= m, "gemv_bf16: out shape")
+    _need(out.dtype == (torch.float32 if epilogue == EPI_F32 else torch.bfloat16), "gemv_bf16: out dtype")
+    if epilogue == EPI_SWIGLU:
+        _need(n % 2 == 0, "gemv_bf16: SwiGLU needs gate and up rows")
+    tiles = -(-n_out // (8 if epilogue == EPI_SWIGLU else 16))
+    _gemv_bf16(_ptr(out), _ptr(x), _ptr(w), m, n, k, x.stride(0), w.stride(0), out.stride(0),
+               epilogue, warps or _gemv_warps(tiles, k), _stream())
+
+
+# ------------------------------------------------------------------ sampling and decode state
+_sample = Function("sampling", "ek_sample",
+                   [_P, _P, c_longlong, c_int, c_int, c_float, c_int, c_ulonglong, _P, _P, _P, _P, _P])
+_decode_advance = Function("sampling", "ek_decode_advance",
+                           [_P, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, _P])
+
+
+def sampling_settings(temperature, top_k, seed, device):
+    """The 4-int device block ``sample(dyn=...)`` reads its settings from."""
+    import struct
+    seed = int(seed) & 0xFFFFFFFFFFFFFFFF
+    bits = struct.unpack("<i", struct.pack("<f", float(temperature)))[0]
+    lo, hi = seed & 0xFFFFFFFF, seed >> 32
+    as_i32 = lambda v: v - (1 << 32) if v >= (1 << 31) else v
+    return torch.tensor([bits, int(top_k), as_i32(lo), as_i32(hi)], dtype=torch.int32, device=device)
+
+
+def sample(out_token, logits, temperature, top_k, seed, streams=None, draws=None, active=None,
+           n_rows=None, dyn=None):
+    """out_token[r] from logits[r, :] (32-bit): arg-max when temperature is 0, else
+    Gumbel-max over the top_k largest (0: all).  ``dyn`` (see ``sampling_settings``)
+    overrides temperature, top_k and seed from device memory."""
+    _need_cuda(out_token, logits, streams, draws, active, dyn)
+    _need(logits.dtype == torch.float32 and logits.stride(-1) == 1, "sample: dense 32-bit logits")
+    _need(out_token.dtype == torch.int32, "sample: int32 out")
+    rows = n_rows if n_rows is not None else logits.shape[0]
+    _sample(_ptr(out_token), _ptr(logits), logits.stride(0), rows, logits.shape[-1],
+            float(temperature), int(top_k), int(seed) & 0xFFFFFFFFFFFFFFFF, _ptr(streams),
+            _ptr(draws), _ptr(active), _ptr(dyn), _stream())
+
+
+def decode_advance(sampled, token_ids, positions, draws, remaining, out_tokens, step_index,
+                   stop_ids, n_stop, batch):
+    _need_cuda(sampled, token_ids, positions, draws, remaining, out_tokens, step_index, stop_ids)
+    for t in (sampled, token_ids, positions, draws, remaining, out_tokens, step_index):
+        _need(t.dtype == torch.int32, "decode_advance: int32 state")
+    _need(out_tokens.shape[-1] == batch, "decode_advance: out_tokens [steps, batch]")
+    _decode_advance(_ptr(sampled), _ptr(token_ids), _ptr(positions), _ptr(draws), _ptr(remaining),
+                    _ptr(out_tokens), _ptr(step_index), _ptr(stop_ids), n_stop, batch,
+                    out_tokens.shape[0], _stream())
+
+
+def build_all():
+    """Compile every kernel library (used by the build check)."""
+    from . import build
+    return build.build_all()

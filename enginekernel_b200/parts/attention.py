@@ -1,0 +1,116 @@
+"""Grouped-query attention over the paged cache.
+
+Per token: q/k/v projections without bias (one fused product), optional RMSNorm of each
+query and key head over the head dimension, position encoding of queries and keys, keys
+and values stored in the cache entry, softmax(scale * q.K^T) V over the keys the token may
+see (all earlier ones, or the last ``window``), output projection
+(engine/ek_model.py:298-325 for prompts, 380-403 for decode; formula 475-488).
+Query head h reads KV head h // (num_heads // num_kv_heads).
+
+Parameters: ``hidden_size``, ``num_heads``, ``num_kv_heads``, ``head_dim``, ``scale``,
+``qk_norm_eps`` (None: no q/k norm), ``window`` (None: all keys), ``position`` (a
+position PartSpec or None).  Tensors: ``q`` [NH*D, H], ``k``, ``v`` [NKV*D, H], ``o``
+[H, NH*D], and with q/k norm ``q_norm``, ``k_norm`` [D].  q, k and v are concatenated at
+load as the reference does (engine/ek_model.py:140-144).
+"""
+
+from __future__ import annotations
+
+import torch
+
+from ..ops import kernels
+from ..ops.linear import linear
+from ..registry import lookup_part, register_part
+from .base import Mixer
+from .spec import CacheSpec, TensorSpec
+
+SM_COUNT = 148
+
+
+@register_part("mixer", "attention")
+class Attention(Mixer):
+    @classmethod
+    def tensors(cls, spec):
+        p, w = spec.params, spec.weights
+        h, nh, nkv, d = p["hidden_size"], p["num_heads"], p["num_kv_heads"], p["head_dim"]
+        out = [TensorSpec(w["q"], (nh * d, h)), TensorSpec(w["k"], (nkv * d, h)),
+               TensorSpec(w["v"], (nkv * d, h)), TensorSpec(w["o"], (h, nh * d))]
+        if p.get("qk_norm_eps") is not None:
+            out += [TensorSpec(w["q_norm"], (d,), "gain"), TensorSpec(w["k_norm"], (d,), "gain")]
+        return out
+
+    def __init__(self, spec, dtype, device):
+        super().__init__(spec, dtype, device)
+        self.hidden = int(self.param("hidden_size"))
+        self.num_heads = int(self.param("num_heads"))
+        self.num_kv_heads = int(self.param("num_kv_heads"))
+        self.head_dim = int(self.param("head_dim"))
+        self.scale = float(self.param("scale"))
+        self.qk_norm_eps = spec.params.get("qk_norm_eps")
+        self.window = spec.params.get("window")
+        if self.num_heads % self.num_kv_heads:
+            raise ValueError("num_heads must be a multiple of num_kv_heads")
+        kernels.check_head_dim(self.head_dim)
+        pos = spec.params.get("position")
+        self.position = lookup_part("position", pos.kind)(pos, dtype, device) if pos else None
+        self.w_qkv = self.w_o = self.q_gain = self.k_gain = None
+
+    def cache_spec(self):
+        return CacheSpec("kv", heads=self.num_kv_heads, head_dim=self.head_dim, window=self.window)
+
+    def prepare(self, max_positions):
+        if self.position is not None:
+            self.position.prepare(max_positions)
+
+    def load(self, tensors):
+        w = self.spec.weights
+        self.w_qkv = torch.cat([tensors[w["q"]], tensors[w["k"]], tensors[w["v"]]], dim=0) \
+            .to(self.dtype).contiguous()
+        self.w_o = tensors[w["o"]].to(self.dtype).contiguous()
+        if self.qk_norm_eps is not None:
+            self.q_gain = tensors[w["q_norm"]].to(torch.float32).contiguous()
+            self.k_gain = tensors[w["k_norm"]].to(torch.float32).contiguous()
+
+    # ------------------------------------------------------------------
+    def forward(self, x, ctx, entry, writes_cache=True):
+        t = ctx.n_tokens
+        qkv = linear(x, self.w_qkv, ctx, "qkv", n_rows=t)
+        pos = self.position
+        kernels.qk_norm_rope_kv(
+            qkv, t, self.q_gain, self.k_gain,
+            pos.cos if pos else _no_table(self.device), pos.sin if pos else _no_table(self.device),
+            pos.rotary_dim if pos else 0, ctx.positions, ctx.token_slot, entry.k_pages,
+            entry.v_pages, entry.block_table, self.num_heads, self.num_kv_heads, self.head_dim,
+            self.qk_norm_eps if self.qk_norm_eps is not None else 0.0, write_kv=writes_cache)
+        out = ctx.workspace.get("attn_out", (t, self.num_heads * self.head_dim), self.dtype)
+        self._attend(out, qkv, ctx, entry)
+        return linear(out, self.w_o, ctx, "attn_proj", n_rows=t)
+
+    def _attend(self, out, qkv, ctx, entry):
+        t = ctx.n_tokens
+        splits, per_split, acc, ml = 1, 0, None, None
+        blocks = t * self.num_heads
+        if blocks < 2 * SM_COUNT and ctx.max_context > 512:
+            visible = min(ctx.max_context, self.window) if self.window else ctx.max_context
+            splits = max(1, min(-(-visible // 256), -(-4 * SM_COUNT // blocks), 64))
+            if splits > 1:
+                per_split = -(-(-(-ctx.max_context // splits)) // 128) * 128
+                splits = -(-ctx.max_context // per_split)
+        if splits > 1:
+            acc = ctx.workspace.get("attn_part_acc", (t, self.num_heads, splits, self.head_dim),
+                                    torch.float32)
+            ml = ctx.workspace.get("attn_part_ml", (t, self.num_heads, splits, 2), torch.float32)
+        kernels.attention_generic(out, qkv, t, ctx.positions, ctx.token_slot, entry.k_pages,
+                                  entry.v_pages, entry.block_table, self.num_heads,
+                                  self.num_kv_heads, self.head_dim, self.scale, self.window,
+                                  splits, per_split, acc, ml)
+
+
+_EMPTY = {}
+
+
+def _no_table(device):
+    key = str(device)
+    if key not in _EMPTY:
+        _EMPTY[key] = torch.zeros((1, 0), dtype=torch.float32, device=device)
+    return _EMPTY[key]

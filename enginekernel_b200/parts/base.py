@@ -1,0 +1,152 @@
+"""Interfaces of the parts a layer is put together from, and the step context.
+
+A part is built from a :class:`~enginekernel_b200.parts.spec.PartSpec` (its kind, its
+sizes and constants, the checkpoint names of its tensors), the engine's dtype and a
+device.  It never sees the model's configuration or which model it is in.  Roles:
+
+``norm``          ``forward(stream, ctx, add=None, rows=None, write_back=True) -> y``
+``position``      tables or constants a mixer needs to place tokens (``tables()``)
+``mixer``         ``cache_spec()``, ``forward(x, ctx, entry, writes_cache) -> [T, hidden]``
+``feed_forward``  ``forward(x, ctx) -> [T, hidden]``
+``block``         ``forward(stream, pending, ctx, entry, writes_cache) -> pending``
+
+``stream`` is the 32-bit residual stream ``[T, hidden]``; ``pending`` is a part's output
+that has not been added to the stream yet (the add is folded into the next norm, as the
+reference folds it into ``add_rms_norm``, engine/ek_model.py:291-296, 326-334).
+"""
+
+from __future__ import annotations
+
+import dataclasses
+from typing import Dict, List, Optional
+
+import torch
+
+from .spec import CacheSpec, PartSpec, TensorSpec
+
+
+class Workspace:
+    """Named scratch tensors that live as long as the runner and are reused by every
+    layer, so a step allocates nothing after its first run at a given size."""
+
+    def __init__(self, device):
+        self.device = device
+        self._bufs: Dict[tuple, torch.Tensor] = {}
+
+    def get(self, name: str, shape, dtype) -> torch.Tensor:
+        n = 1
+        for s in shape:
+            n *= int(s)
+        key = (name, dtype)
+        buf = self._bufs.get(key)
+        if buf is None or buf.numel() < n:
+            grow = max(n, int(buf.numel() * 1.5) if buf is not None else 0)
+            buf = torch.empty(grow, dtype=dtype, device=self.device)
+            self._bufs[key] = buf
+        return buf[:n].view(*shape)
+
+    def bytes(self) -> int:
+        return sum(b.numel() * b.element_size() for b in self._bufs.values())
+
+
+@dataclasses.dataclass
+class StepContext:
+    """One step's tokens as the kernels see them (all index tensors int32, on device).
+
+    Token t of the step belongs to the sequence in slot ``token_slot[t]`` and stands at
+    ``positions[t]`` in it (negative: the row belongs to a finished sequence and is
+    skipped).  Sequence b owns tokens ``cu_seqlens[b] .. cu_seqlens[b+1]``.
+    """
+    n_tokens: int
+    n_seqs: int
+    token_ids: torch.Tensor
+    positions: torch.Tensor
+    token_slot: torch.Tensor
+    cu_seqlens: torch.Tensor
+    is_decode: bool                 # every sequence brings exactly one token
+    max_new: int                    # longest run of new tokens of one sequence
+    max_context: int                # no sequence is longer than this after the step
+    dtype: torch.dtype
+    device: torch.device
+    workspace: Workspace
+    #: host copies for parts written in plain torch (tests, toy parts); None inside a
+    #: captured decode step, where the host does not know the values
+    host_positions: Optional[List[int]] = None
+    host_token_slot: Optional[List[int]] = None
+    host_cu_seqlens: Optional[List[int]] = None
+
+
+class Part:
+    """Base of all parts."""
+    role = ""
+
+    @classmethod
+    def tensors(cls, spec: PartSpec) -> List[TensorSpec]:
+        """The checkpoint tensors an instance built from ``spec`` reads."""
+        return []
+
+    def __init__(self, spec: PartSpec, dtype: torch.dtype, device):
+        self.spec, self.dtype, self.device = spec, dtype, torch.device(device)
+
+    def load(self, tensors: Dict[str, torch.Tensor]) -> None:
+        """Take the tensors named in ``spec.weights`` (already on the device, in their
+        stored precision) and keep them in the form the kernels want."""
+
+    def param(self, name: str):
+        try:
+            return self.spec.params[name]
+        except KeyError:
+            raise KeyError(f"{type(self).__name__} needs the parameter {name!r}") from None
+
+
+class Norm(Part):
+    role = "norm"
+
+    def forward(self, stream, ctx: StepContext, add=None, rows=None, n_rows=None,
+                write_back=True):
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    role = "position"
+
+    def prepare(self, max_positions: int) -> None:
+        raise NotImplementedError
+
+
+class Mixer(Part):
+    role = "mixer"
+
+    def cache_spec(self) -> Optional[CacheSpec]:
+        """What one cache entry of this mixer holds per sequence (None: nothing)."""
+        return None
+
+    def prepare(self, max_positions: int) -> None:
+        """Called once the longest position is known (tables and the like)."""
+
+    def forward(self, x, ctx: StepContext, entry, writes_cache: bool):
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    role = "feed_forward"
+
+    def forward(self, x, ctx: StepContext):
+        raise NotImplementedError
+
+
+class Block(Part):
+    """An arrangement of norms, a mixer and a feed-forward around the residual stream."""
+    role = "block"
+
+    def __init__(self, spec, dtype, device, mixer: Mixer, feed_forward: FeedForward,
+                 norms: Dict[str, Norm]):
+        super().__init__(spec, dtype, device)
+        self.mixer, self.feed_forward, self.norms = mixer, feed_forward, norms
+
+    @classmethod
+    def norm_names(cls, spec: PartSpec) -> List[str]:
+        return []
+
+    def forward(self, stream, pending, ctx: StepContext, entry, writes_cache: bool):
+        raise NotImplementedError

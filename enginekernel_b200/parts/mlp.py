@@ -1,0 +1,53 @@
+"""Gated feed-forward (SwiGLU): down(act(gate(x)) * up(x)), no biases.
+
+engine/ek_model.py:205-209 with engine/ek_kernels.py:125-143; gate and up are
+concatenated at load (gate rows first, engine/ek_model.py:145-147).  Parameters:
+``hidden_size``, ``intermediate_size``, ``activation`` ("silu").  Tensors: ``gate``,
+``up`` [I, H], ``down`` [H, I].
+"""
+
+from __future__ import annotations
+
+import torch
+
+from ..ops import kernels
+from ..ops.linear import linear
+from ..registry import register_part
+from .base import FeedForward
+from .spec import TensorSpec
+
+
+@register_part("feed_forward", "gated_mlp")
+class GatedMLP(FeedForward):
+    @classmethod
+    def tensors(cls, spec):
+        p, w = spec.params, spec.weights
+        h, i = p["hidden_size"], p["intermediate_size"]
+        return [TensorSpec(w["gate"], (i, h)), TensorSpec(w["up"], (i, h)),
+                TensorSpec(w["down"], (h, i))]
+
+    def __init__(self, spec, dtype, device):
+        super().__init__(spec, dtype, device)
+        self.hidden = int(self.param("hidden_size"))
+        self.inter = int(self.param("intermediate_size"))
+        act = spec.params.get("activation", "silu")
+        if act != "silu":
+            raise ValueError(f"gated_mlp has no activation {act!r} (only silu)")
+        self.w_gate_up = self.w_down = None
+
+    def load(self, tensors):
+        w = self.spec.weights
+        self.w_gate_up = torch.cat([tensors[w["gate"]], tensors[w["up"]]], dim=0) \
+            .to(self.dtype).contiguous()
+        self.w_down = tensors[w["down"]].to(self.dtype).contiguous()
+
+    def forward(self, x, ctx):
+        t = ctx.n_tokens
+        if self.dtype == torch.bfloat16 and t <= kernels.GEMV_MAX_ROWS and self.inter % 8 == 0:
+            act = ctx.workspace.get("mlp_act", (t, self.inter), self.dtype)
+            kernels.gemv_bf16(act, x, self.w_gate_up, kernels.EPI_SWIGLU, n_rows=t)
+        else:
+            gu = linear(x, self.w_gate_up, ctx, "mlp_gate_up", n_rows=t)
+            act = ctx.workspace.get("mlp_act", (t, self.inter), self.dtype)
+            kernels.silu_mul(act, gu, n_rows=t)
+        return linear(act, self.w_down, ctx, "mlp_down", n_rows=t)

@@ -209,10 +209,10 @@ def uniform_for(seed, stream, step, index):
     """The uniform number in (0, 1) that belongs to vocabulary entry ``index`` of the
     draw ``step`` of sequence ``stream`` under ``seed``: word index % 4 of the Philox
     block with counter (index // 4, step, stream, 0) and key (seed low, seed high);
-    its top 24 bits b give (b + 0.5) / 2^24, which 32-bit floats hold exactly."""
+    its top 23 bits b give (b + 0.5) / 2^23, which 32-bit floats hold exactly."""
     words = philox4x32((index // 4, step & 0xFFFFFFFF, stream & 0xFFFFFFFF, 0),
                        (seed & 0xFFFFFFFF, (seed >> 32) & 0xFFFFFFFF))
-    return ((words[index % 4] >> 8) + 0.5) / 16777216.0
+    return ((words[index % 4] >> 9) + 0.5) / 8388608.0
 
 
 def sample_token(logits_row, temperature, top_k, seed, stream, step):

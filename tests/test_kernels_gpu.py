@@ -1,0 +1,339 @@
+"""Each CUDA kernel alone against a plain torch formula, at sizes other than the models'.
+
+Error measure as in the reference's kernel tests (bench/test_kernels.py:18-33): largest
+absolute error over the reference tensor's largest magnitude; 2e-2 for bfloat16 storage,
+1e-5 for 32-bit.
+"""
+
+import math
+
+import pytest
+import torch
+
+from tests.plain import qwen3_plain as plain
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda"
+TOL = {torch.float32: 1e-5, torch.bfloat16: 2e-2}
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def K():
+    from enginekernel_b200.ops import kernels
+    return kernels
+
+
+def rel(got, want):
+    got, want = got.double().cpu(), want.double().cpu()
+    return (got - want).abs().max().item() / max(want.abs().max().item(), 1e-9)
+
+
+def rnd(*shape, dtype=torch.float32, seed=0, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * scale).to(dtype).to(DEV)
+
+
+# ------------------------------------------------------------------ norms, embedding, gate
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("rows,hidden", [(1, 80), (37, 2560), (5, 1000), (3, 12288)])
+def test_rmsnorm_plain_add_and_gathered(dtype, rows, hidden):
+    k = K()
+    stream = rnd(rows, hidden, seed=1)
+    gain = 1 + 0.1 * rnd(hidden, seed=2)
+    add = rnd(rows, hidden, dtype=dtype, seed=3)
+    eps = 3e-6
+
+    def ref(x):
+        x = x.double()
+        return (x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps) * gain.double())
+
+    y = torch.empty(rows, hidden, dtype=dtype, device=DEV)
+    k.rmsnorm(y, stream.clone(), gain, eps)
+    assert rel(y, ref(stream)) <= TOL[dtype]
+
+    s2 = stream.clone()
+    k.rmsnorm(y, s2, gain, eps, add=add)
+    summed = stream.double() + add.double()
+    assert rel(s2, summed) <= 1e-6                       # the stream itself stays 32-bit
+    assert rel(y, ref(summed)) <= TOL[dtype]
+
+    pick = torch.tensor([rows - 1, 0, rows // 2], dtype=torch.int32, device=DEV)
+    s3 = stream.clone()
+    y3 = torch.empty(3, hidden, dtype=dtype, device=DEV)
+    k.rmsnorm(y3, s3, gain, eps, add=add, rows=pick, write_back=False)
+    assert torch.equal(s3, stream)                       # not written back
+    assert rel(y3, ref(summed)[pick.long().cpu()]) <= TOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_embed_and_silu_mul(dtype):
+    k = K()
+    table = rnd(331, 80, dtype=dtype, seed=4)
+    ids = torch.tensor([0, 330, 7, 7, 100], dtype=torch.int32, device=DEV)
+    out = torch.zeros(6, 80, device=DEV)
+    k.embed(out, table, ids, 5)
+    assert torch.equal(out[:5], table[ids.long()].float()) and out[5].abs().sum() == 0
+
+    for rows, inter in ((1, 176), (19, 9728), (4, 1001)):
+        gu = rnd(rows, 2 * inter, dtype=dtype, seed=5, scale=2.0)
+        act = torch.empty(rows, inter, dtype=dtype, device=DEV)
+        k.silu_mul(act, gu)
+        g, u = gu.double()[:, :inter], gu.double()[:, inter:]
+        assert rel(act, g / (1 + torch.exp(-g)) * u) <= TOL[dtype]
+
+
+# ------------------------------------------------------------------ paged cache helpers
+class Pages:
+    """A little paged cache with a shuffled page order, plus its dense mirror."""
+
+    def __init__(self, n_slots, max_len, heads, d, dtype, seed=0):
+        self.page = K().PAGE
+        per = -(-max_len // self.page)
+        n_pages = n_slots * per + 3
+        g = torch.Generator().manual_seed(seed)
+        perm = torch.randperm(n_pages, generator=g)[: n_slots * per].view(n_slots, per)
+        self.table = perm.to(torch.int32).to(DEV)
+        self.k = torch.zeros(n_pages, heads, self.page, d, dtype=dtype, device=DEV)
+        self.v = torch.zeros_like(self.k)
+        self.heads, self.d = heads, d
+
+    def fill(self, slot, keys, values):
+        """keys/values [len, heads, d] written at positions 0..len-1 of ``slot``."""
+        for p in range(keys.shape[0]):
+            page = int(self.table[slot, p // self.page])
+            self.k[page, :, p % self.page] = keys[p]
+            self.v[page, :, p % self.page] = values[p]
+
+    def dense(self, slot, length):
+        idx = torch.arange(length)
+        pages = self.table[slot, (idx // self.page).to(DEV)].long()
+        off = (idx % self.page).to(DEV)
+        return self.k[pages, :, off], self.v[pages, :, off]      # [len, heads, d]
+
+
+def ref_attention(q, keys, values, pos, scale, window=None):
+    """q [NH, D] at position pos over keys/values [len, NKV, D] (len > pos), float64."""
+    nh, nkv = q.shape[0], keys.shape[1]
+    lo = 0 if not window else max(0, pos - window + 1)
+    kk = keys[lo:pos + 1].double().repeat_interleave(nh // nkv, 1)
+    vv = values[lo:pos + 1].double().repeat_interleave(nh // nkv, 1)
+    s = torch.einsum("hd,jhd->hj", q.double(), kk) * scale
+    p = torch.softmax(s, -1)
+    return torch.einsum("hj,jhd->hd", p, vv).reshape(-1)
+
+
+# ------------------------------------------------------------------ rope + cache write
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nq,nkv,d,rot", [(4, 2, 16, 16), (6, 3, 48, 48), (8, 1, 128, 128),
+                                          (2, 2, 80, 32), (3, 1, 256, 256)])
+def test_qk_norm_rope_kv(dtype, nq, nkv, d, rot):
+    k = K()
+    eps, theta, max_len, n_slots = 1e-5, 50000.0, 200, 3
+    pages = Pages(n_slots, max_len, nkv, d, dtype, seed=d)
+    before_k, before_v = pages.k.clone(), pages.v.clone()
+    toks = [(0, 0), (0, 1), (2, 63), (2, 64), (1, 199), (1, -1), (0, 130)]     # (slot, position)
+    t = len(toks)
+    qkv = rnd(t, (nq + 2 * nkv) * d, dtype=dtype, seed=7)
+    orig = qkv.clone()
+    qg, kg = 1 + 0.1 * rnd(d, seed=8), 1 + 0.1 * rnd(d, seed=9)
+    inv = 1.0 / (theta ** (torch.arange(0, rot, 2, dtype=torch.float32) / rot))
+    freqs = torch.outer(torch.arange(max_len, dtype=torch.float32), inv)
+    cos, sin = freqs.cos().to(DEV), freqs.sin().to(DEV)
+    positions = torch.tensor([p for _, p in toks], dtype=torch.int32, device=DEV)
+    slots = torch.tensor([s for s, _ in toks], dtype=torch.int32, device=DEV)
+    k.qk_norm_rope_kv(qkv, t, qg, kg, cos, sin, rot, positions, slots, pages.k, pages.v,
+                      pages.table, nq, nkv, d, eps)
+
+    def ref_head(x, gain, p):
+        x = x.double()
+        x = x * torch.rsqrt(x.pow(2).mean() + eps) * gain.double().cpu()
+        out = x.clone()
+        h = rot // 2
+        c, s = freqs[p].cos().double(), freqs[p].sin().double()
+        out[:h] = x[:h] * c - x[h:rot] * s
+        out[h:rot] = x[h:rot] * c + x[:h] * s
+        return out
+
+    touched = set()
+    for i, (slot, p) in enumerate(toks):
+        row = orig[i].cpu()
+        if p < 0:                                        # a finished row: nothing happens
+            assert torch.equal(qkv[i], orig[i])
+            continue
+        for h in range(nq):
+            want = ref_head(row[h * d:(h + 1) * d], qg, p)
+            assert rel(qkv[i, h * d:(h + 1) * d], want) <= TOL[dtype]
+        page = int(pages.table[slot, p // 64])
+        for h in range(nkv):
+            want = ref_head(row[(nq + h) * d:(nq + h + 1) * d], kg, p)
+            assert rel(pages.k[page, h, p % 64], want) <= TOL[dtype]
+            assert torch.equal(pages.v[page, h, p % 64], orig[i, (nq + nkv + h) * d:(nq + nkv + h + 1) * d])
+            touched.add((page, h, p % 64))
+    # everything else in the cache is untouched
+    mask = torch.ones(pages.k.shape[:3], dtype=torch.bool)
+    for page, h, o in touched:
+        mask[page, h, o] = False
+    assert torch.equal(pages.k.cpu()[mask], before_k.cpu()[mask])
+    assert torch.equal(pages.v.cpu()[mask], before_v.cpu()[mask])
+    # a run that must not write the cache leaves it alone but still rotates q
+    k2, v2, q2 = pages.k.clone(), pages.v.clone(), orig.clone()
+    k.qk_norm_rope_kv(q2, t, qg, kg, cos, sin, rot, positions, slots, k2, v2, pages.table, nq, nkv,
+                      d, eps, write_kv=False)
+    assert torch.equal(k2, pages.k) and torch.equal(v2, pages.v)
+    assert torch.equal(q2[:, :nq * d], qkv[:, :nq * d])
+
+
+# ------------------------------------------------------------------ attention
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nq,nkv,d", [(4, 2, 16), (6, 3, 48), (8, 2, 128), (5, 5, 80), (16, 1, 256)])
+def test_attention_generic_positions_splits_window(dtype, nq, nkv, d):
+    k = K()
+    lens = [1, 64, 65, 517, 130]
+    pages = Pages(len(lens), max(lens), nkv, d, dtype, seed=3)
+    kv = []
+    for s, n in enumerate(lens):
+        keys, vals = rnd(n, nkv, d, dtype=dtype, seed=10 + s), rnd(n, nkv, d, dtype=dtype, seed=20 + s)
+        pages.fill(s, keys, vals)
+        kv.append((keys, vals))
+    toks = [(0, 0), (1, 63), (2, 64), (3, 516), (3, 0), (3, 255), (4, 129), (4, 64), (2, -1)]
+    t = len(toks)
+    q = rnd(t, nq * d + 5 * d, dtype=dtype, seed=30)           # rows wider than the q part
+    # make one far key stand out for the long sequence: a fault in paging or in the split
+    # merge that loses key 3 of 517 changes the result completely
+    keys3 = kv[3][0]
+    q[3, :d] = (keys3[3, 0].float() * 4).to(dtype)
+    positions = torch.tensor([p for _, p in toks], dtype=torch.int32, device=DEV)
+    slots = torch.tensor([s for s, _ in toks], dtype=torch.int32, device=DEV)
+    scale = 1.0 / math.sqrt(d)
+    for window, splits, per in ((None, 1, 0), (None, 5, 128), (100, 1, 0), (64, 3, 192), (1, 1, 0)):
+        out = torch.full((t, nq * d), 7.0, dtype=dtype, device=DEV)
+        acc = torch.empty(t * nq * max(splits, 1) * d, device=DEV)
+        ml = torch.empty(t * nq * max(splits, 1) * 2, device=DEV)
+        k.attention_generic(out, q, t, positions, slots, pages.k, pages.v, pages.table, nq, nkv, d,
+                            scale, window, splits, per, acc, ml)
+        for i, (s, p) in enumerate(toks):
+            if p < 0:
+                assert out[i].abs().max().item() == 0
+                continue
+            want = ref_attention(q[i, :nq * d].view(nq, d).cpu(), kv[s][0].cpu(), kv[s][1].cpu(), p,
+                                 scale, window)
+            assert rel(out[i], want) <= TOL[dtype], (window, splits, i)
+
+
+# ------------------------------------------------------------------ matrix products
+@pytest.mark.parametrize("m,n,k_", [(1, 331, 80), (3, 2560, 176), (16, 100, 33), (17, 65, 64),
+                                    (130, 384, 96), (64, 1, 1)])
+def test_gemm_f32_is_true_32_bit(m, n, k_):
+    k = K()
+    x, w = rnd(m, k_, seed=1), rnd(n, k_, seed=2)
+    out = torch.empty(m, n, device=DEV)
+    k.gemm_f32(out, x, w)
+    want = x.double() @ w.double().t()
+    assert rel(out, want) <= 2e-6
+    # a TF32 product would be off by ~1e-3 here
+    # rows do not depend on their batch mates, bit for bit
+    if m > 1:
+        one = torch.empty(1, n, device=DEV)
+        k.gemm_f32(one, x[m - 1:m].contiguous(), w)
+        assert torch.equal(one[0], out[m - 1])
+
+
+@pytest.mark.parametrize("m", [1, 3, 8, 9, 33, 64])
+@pytest.mark.parametrize("n,k_", [(331, 80), (2560, 4096), (48, 8), (1000, 1000)])
+def test_gemv_bf16_epilogues(m, n, k_):
+    k = K()
+    x = rnd(m, k_, dtype=torch.bfloat16, seed=1)
+    w = rnd(n, k_, dtype=torch.bfloat16, seed=2, scale=0.05)
+    want = x.double() @ w.double().t()
+    out32 = torch.empty(m, n, device=DEV)
+    k.gemv_bf16(out32, x, w, k.EPI_F32)
+    assert rel(out32, want) <= 1e-5
+    out16 = torch.empty(m, n, dtype=torch.bfloat16, device=DEV)
+    k.gemv_bf16(out16, x, w, k.EPI_BF16)
+    assert rel(out16, want) <= 4e-3                       # one rounding to bfloat16
+    if n % 2 == 0:
+        inter = n // 2
+        act = torch.empty(m, inter, dtype=torch.bfloat16, device=DEV)
+        k.gemv_bf16(act, x, w, k.EPI_SWIGLU)
+        g, u = want[:, :inter], want[:, inter:]
+        assert rel(act, g / (1 + torch.exp(-g)) * u) <= 4e-3
+    for warps in (1, 4, 32):
+        o = torch.empty(m, n, device=DEV)
+        k.gemv_bf16(o, x, w, k.EPI_F32, warps=warps)
+        assert rel(o, want) <= 1e-5
+
+
+def test_gemv_refuses_what_it_cannot_do():
+    k = K()
+    from enginekernel_b200.ops.lib import KernelError
+    x = rnd(2, 12, dtype=torch.bfloat16)
+    w = rnd(16, 12, dtype=torch.bfloat16)
+    with pytest.raises(KernelError):
+        k.gemv_bf16(torch.empty(2, 16, dtype=torch.bfloat16, device=DEV), x, w)
+    with pytest.raises(KernelError):
+        k.check_head_dim(24)
+    with pytest.raises(KernelError):
+        k.rmsnorm(torch.empty(1, 8), torch.empty(1, 8), torch.empty(8), 1e-6)   # CPU tensors
+
+
+# ------------------------------------------------------------------ sampling and state
+def test_sample_greedy_gumbel_topk():
+    k = K()
+    vocab = 1000
+    g = torch.Generator().manual_seed(3)
+    logits = (torch.randn(5, vocab, generator=g) * 3).to(DEV)
+    logits[1, 17] = logits[1, 900] = 50.0                 # a tie: the lower index wins
+    out = torch.full((5,), -5, dtype=torch.int32, device=DEV)
+    k.sample(out, logits, 0.0, 0, 0)
+    assert out.tolist() == [int(torch.argmax(r)) for r in logits.cpu()] and out[1].item() == 17
+
+    streams = torch.tensor([4, 0, 9, 2, 2], dtype=torch.int32, device=DEV)
+    draws = torch.tensor([0, 3, 1, 7, 8], dtype=torch.int32, device=DEV)
+    active = torch.tensor([5, 5, -1, 5, 5], dtype=torch.int32, device=DEV)
+    for temp, topk, seed in ((0.8, 0, 1234), (1.5, 3, 7), (0.3, 50, (1 << 40) + 5)):
+        out.fill_(-5)
+        k.sample(out, logits, temp, topk, seed, streams=streams, draws=draws, active=active)
+        dyn = torch.full((5,), -5, dtype=torch.int32, device=DEV)
+        k.sample(dyn, logits, 0.0, 0, 0, streams=streams, draws=draws, active=active,
+                 dyn=k.sampling_settings(temp, topk, seed, DEV))
+        assert torch.equal(out, dyn)
+        for r in range(5):
+            if r == 2:
+                assert out[r].item() == -5                # inactive rows are left alone
+                continue
+            want = plain.sample_token(logits[r].cpu(), temp, topk, seed, int(streams[r]), int(draws[r]))
+            assert out[r].item() == want, (temp, topk, r)
+
+
+def test_sample_distribution():
+    """Many draws of one row follow softmax(logits / T)."""
+    k = K()
+    logits = torch.tensor([[2.0, 1.0, 0.0, -1.0, 0.5]], device=DEV).repeat(4000, 1)
+    out = torch.empty(4000, dtype=torch.int32, device=DEV)
+    draws = torch.arange(4000, dtype=torch.int32, device=DEV)
+    streams = torch.zeros(4000, dtype=torch.int32, device=DEV)
+    k.sample(out, logits, 0.7, 0, 99, streams=streams, draws=draws)
+    freq = torch.bincount(out.long().cpu(), minlength=5).double() / 4000
+    want = torch.softmax(logits[0].double().cpu() / 0.7, -1)
+    assert (freq - want).abs().max().item() < 0.03
+
+
+def test_decode_advance():
+    k = K()
+    b = 5
+    i32 = dict(dtype=torch.int32, device=DEV)
+    sampled = torch.tensor([11, 99, 13, 14, 15], **i32)
+    tokens = torch.tensor([1, 2, 3, 4, 5], **i32)
+    positions = torch.tensor([10, 20, -1, 40, 50], **i32)
+    draws = torch.zeros(b, **i32)
+    remaining = torch.tensor([5, 5, 5, 1, 5], **i32)
+    out = torch.full((4, b), -7, **i32)
+    step = torch.tensor([2], **i32)
+    stop = torch.tensor([99, 98], **i32)
+    k.decode_advance(sampled, tokens, positions, draws, remaining, out, step, stop, 2, b)
+    assert out[2].tolist() == [11, 99, -1, 14, 15] and step.item() == 3
+    assert positions.tolist() == [11, -1, -1, -1, 51]     # stop token, finished, budget used up
+    assert tokens.tolist() == [11, 2, 3, 4, 15]
+    assert draws.tolist() == [1, 1, 0, 1, 1] and remaining.tolist() == [4, 4, 5, 0, 4]
+    assert (out[[0, 1, 3]] == -7).all()
