@@ -155,6 +155,7 @@ static int launch(void* out, const void* x, const void* W, int M, int N, int K, 
   if (M > 64 || K <= 0 || K % 8 || ldx % 8 || ldw % 8 || warps < 1 || warps > 32 ||
       (EPI == EPI_SWIGLU && (N & 1)))
     return EK_ERR_ARG;
+  if (warps > 16) warps = 16;              // 8 batch tiles need 96 registers a thread
   if (M <= 8) return launch_nt<1, EPI>(out, x, W, M, N, K, ldx, ldw, ldo, warps, stream);
   if (M <= 16) return launch_nt<2, EPI>(out, x, W, M, N, K, ldx, ldw, ldo, warps, stream);
   if (M <= 32) return launch_nt<4, EPI>(out, x, W, M, N, K, ldx, ldw, ldo, warps, stream);

@@ -51,6 +51,7 @@ class DecodeState:
         self.workspace = Workspace(dev)          # owned by the graph: never regrown elsewhere
         self.graph = None
         self.use_graph = use_graph
+        self.launches_per_step = 0               # kernel launcher calls in one step
         self.ctx = StepContext(
             n_tokens=batch, n_seqs=batch, token_ids=self.token_ids, positions=self.positions,
             token_slot=self.token_slot, cu_seqlens=self.cu_seqlens, is_decode=True, max_new=1,
@@ -97,9 +98,12 @@ class DecodeState:
             self._body()
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
+        from ..ops.lib import launch_calls
         g = torch.cuda.CUDAGraph()
+        before = launch_calls()
         with torch.cuda.graph(g):
             self._body()
+        self.launches_per_step = launch_calls() - before
         self.positions.copy_(saved[0])
         self.step_index.copy_(saved[1])
         torch.cuda.synchronize()

@@ -10,6 +10,11 @@ from . import build
 
 _libs: Dict[str, ctypes.CDLL] = {}
 _lock = threading.Lock()
+_launch_calls = 0          # launcher calls made from Python (a captured graph replays them)
+
+
+def launch_calls() -> int:
+    return _launch_calls
 
 
 class KernelError(RuntimeError):
@@ -71,5 +76,7 @@ class Function:
         return fn
 
     def __call__(self, *args):
+        global _launch_calls
         fn = self._fn or self._bind()
+        _launch_calls += 1
         check(fn(*args), self.name)
