@@ -174,6 +174,37 @@ def attention_generic(out, q, n_tokens, positions, token_slot, k_pages, v_pages,
                            _ptr(part_ml), _stream())
 
 
+_attn_decode_bf16 = Function("attention_decode_bf16", "ek_attention_decode_bf16",
+                             [_P, _P, c_int, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int,
+                              c_float, c_int, c_int, c_int, _P, _P, _P])
+
+
+def attention_decode_supported(dtype, head_dim):
+    return dtype == torch.bfloat16 and head_dim % 32 == 0 and 32 <= head_dim <= MAX_HEAD_DIM
+
+
+def attention_decode_bf16(out, q, n_tokens, positions, token_slot, k_pages, v_pages, block_table,
+                          n_q_heads, n_kv_heads, head_dim, scale, window=None, n_splits=1,
+                          keys_per_split=0, part_acc=None, part_ml=None):
+    """One query token per row of ``q`` (bfloat16, head_dim a multiple of 32): same contract
+    as :func:`attention_generic`; ``keys_per_split`` must be a multiple of 16."""
+    _need_cuda(out, q, positions, token_slot, k_pages, v_pages, block_table, part_acc, part_ml)
+    _need(attention_decode_supported(q.dtype, head_dim),
+          "attention_decode_bf16: bfloat16 and a head size that is a multiple of 32")
+    _need(out.dtype == q.dtype == k_pages.dtype, "attention: one dtype for q, cache and out")
+    _need(out.is_contiguous() and out.shape[-1] == n_q_heads * head_dim, "attention: out [T, NQ*D]")
+    _need(q.stride(-1) == 1 and q.stride(0) % 8 == 0, "attention: dense, 16-byte aligned q rows")
+    if n_splits > 1:
+        _need(keys_per_split % 16 == 0, "attention_decode_bf16: keys_per_split multiple of 16")
+        _need(part_acc is not None and part_ml is not None
+              and part_acc.numel() >= n_tokens * n_q_heads * n_splits * head_dim
+              and part_ml.numel() >= n_tokens * n_q_heads * n_splits * 2, "attention: split buffers")
+    _attn_decode_bf16(_ptr(out), _ptr(q), q.stride(0), _ptr(positions), _ptr(token_slot),
+                      _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.stride(0),
+                      n_tokens, n_q_heads, n_kv_heads, head_dim, float(scale), int(window or 0),
+                      n_splits, keys_per_split, _ptr(part_acc), _ptr(part_ml), _stream())
+
+
 # ------------------------------------------------------------------ matrix products
 _gemm_f32 = Function("gemm_f32", "ek_gemm_nt_f32",
                      [_P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P])

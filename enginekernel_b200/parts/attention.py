@@ -88,22 +88,32 @@ class Attention(Mixer):
 
     def _attend(self, out, qkv, ctx, entry):
         t = ctx.n_tokens
-        splits, per_split, acc, ml = 1, 0, None, None
-        blocks = t * self.num_heads
-        if blocks < 2 * SM_COUNT and ctx.max_context > 512:
-            visible = min(ctx.max_context, self.window) if self.window else ctx.max_context
-            splits = max(1, min(-(-visible // 256), -(-4 * SM_COUNT // blocks), 64))
-            if splits > 1:
-                per_split = -(-(-(-ctx.max_context // splits)) // 128) * 128
-                splits = -(-ctx.max_context // per_split)
+        visible = min(ctx.max_context, self.window) if self.window else ctx.max_context
+        fast_decode = ctx.is_decode and kernels.attention_decode_supported(self.dtype, self.head_dim)
+        if fast_decode:
+            # blocks = tokens x KV heads (x 16-row blocks of the group); split the keys until
+            # about four blocks per SM exist, never finer than one page
+            blocks = t * self.num_kv_heads * -(-(self.num_heads // self.num_kv_heads) // 16)
+            splits = max(1, min(-(-4 * SM_COUNT // blocks), -(-visible // 64)))
+            unit = 64
+        else:
+            blocks = t * self.num_heads
+            splits = 1
+            if blocks < 2 * SM_COUNT and ctx.max_context > 512:
+                splits = max(1, min(-(-visible // 256), -(-4 * SM_COUNT // blocks), 64))
+            unit = 128
+        per_split, acc, ml = 0, None, None
+        if splits > 1:
+            per_split = -(-(-(-ctx.max_context // splits)) // unit) * unit
+            splits = -(-ctx.max_context // per_split)
         if splits > 1:
             acc = ctx.workspace.get("attn_part_acc", (t, self.num_heads, splits, self.head_dim),
                                     torch.float32)
             ml = ctx.workspace.get("attn_part_ml", (t, self.num_heads, splits, 2), torch.float32)
-        kernels.attention_generic(out, qkv, t, ctx.positions, ctx.token_slot, entry.k_pages,
-                                  entry.v_pages, entry.block_table, self.num_heads,
-                                  self.num_kv_heads, self.head_dim, self.scale, self.window,
-                                  splits, per_split, acc, ml)
+        fn = kernels.attention_decode_bf16 if fast_decode else kernels.attention_generic
+        fn(out, qkv, t, ctx.positions, ctx.token_slot, entry.k_pages, entry.v_pages,
+           entry.block_table, self.num_heads, self.num_kv_heads, self.head_dim, self.scale,
+           self.window, splits, per_split, acc, ml)
 
 
 _EMPTY = {}

@@ -221,6 +221,45 @@ def test_attention_generic_positions_splits_window(dtype, nq, nkv, d):
             assert rel(out[i], want) <= TOL[dtype], (window, splits, i)
 
 
+@pytest.mark.parametrize("nq,nkv,d", [(4, 2, 32), (6, 3, 64), (32, 8, 128), (5, 5, 96), (16, 1, 256),
+                                      (20, 1, 64), (40, 2, 128)])
+def test_attention_decode_bf16(nq, nkv, d):
+    """The register-streaming decode kernel: groups of 1 to 20 heads (more than 16 take two
+    row blocks), every head size it takes, windows, key splits, finished rows."""
+    k = K()
+    dtype = torch.bfloat16
+    lens = [1, 64, 65, 517, 130, 16, 17]
+    pages = Pages(len(lens), max(lens), nkv, d, dtype, seed=5)
+    kv = []
+    for s, n in enumerate(lens):
+        keys, vals = rnd(n, nkv, d, dtype=dtype, seed=10 + s), rnd(n, nkv, d, dtype=dtype, seed=20 + s)
+        pages.fill(s, keys, vals)
+        kv.append((keys, vals))
+    toks = [(0, 0), (1, 63), (2, 64), (3, 516), (3, 0), (3, 255), (4, 129), (4, 64), (2, -1),
+            (5, 15), (6, 16), (3, 300)]
+    t = len(toks)
+    q = rnd(t, nq * d + 2 * nkv * d, dtype=dtype, seed=30)
+    q[3, :d] = (kv[3][0][3, 0].float() * 4).to(dtype)          # one far key dominates
+    q[11, (nq - 1) * d:nq * d] = (kv[3][0][299, nkv - 1].float() * 4).to(dtype)
+    positions = torch.tensor([p for _, p in toks], dtype=torch.int32, device=DEV)
+    slots = torch.tensor([s for s, _ in toks], dtype=torch.int32, device=DEV)
+    scale = 1.0 / math.sqrt(d)
+    for window, splits, per in ((None, 1, 0), (None, 5, 128), (None, 9, 64), (100, 1, 0), (64, 3, 192),
+                                (1, 1, 0), (17, 33, 16)):
+        out = torch.full((t, nq * d), 7.0, dtype=dtype, device=DEV)
+        acc = torch.empty(t * nq * max(splits, 1) * d, device=DEV)
+        ml = torch.empty(t * nq * max(splits, 1) * 2, device=DEV)
+        k.attention_decode_bf16(out, q, t, positions, slots, pages.k, pages.v, pages.table, nq, nkv,
+                                d, scale, window, splits, per, acc, ml)
+        for i, (s, p) in enumerate(toks):
+            if p < 0:
+                assert out[i].abs().max().item() == 0
+                continue
+            want = ref_attention(q[i, :nq * d].view(nq, d).cpu(), kv[s][0].cpu(), kv[s][1].cpu(), p,
+                                 scale, window)
+            assert rel(out[i], want) <= TOL[dtype], (window, splits, i)
+
+
 # ------------------------------------------------------------------ matrix products
 @pytest.mark.parametrize("m,n,k_", [(1, 331, 80), (3, 2560, 176), (16, 100, 33), (17, 65, 64),
                                     (130, 384, 96), (64, 1, 1)])
