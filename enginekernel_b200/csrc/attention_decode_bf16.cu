@@ -310,3 +310,70 @@ EK_EXPORT int ek_attention_decode_bf16(void* out, const void* q, int q_row_strid
 #undef EK_CASE
   return EK_ERR_ARG;
 }
+
+// ---------------------------------------------------------------------------------------
+// The allocation-free variant (declared and described in attention_decode_noalloc.h).
+// ---------------------------------------------------------------------------------------
+#include <stdio.h>
+
+#include "attention_decode_noalloc.h"
+
+namespace ek {
+
+// Partial accumulators and (max, sum) pairs of the key splits.  In host code this name is
+// only a handle for cudaGetSymbolAddress, never a pointer a kernel may be given.
+static __device__ __align__(256) float noalloc_scratch[EK_NOALLOC_SCRATCH_FLOATS];
+
+constexpr int kMaxDevices = 64;
+static float* noalloc_scratch_address[kMaxDevices];     // per device, filled on first use
+
+// Device address of the array on the current device; looked up once per device.
+static int noalloc_scratch_pointer(float** ptr) {
+  int device = 0;
+  cudaError_t e = cudaGetDevice(&device);
+  if (e != cudaSuccess) return (int)e;
+  if (device < 0 || device >= kMaxDevices) return EK_ERR_ARG;
+  if (noalloc_scratch_address[device] == nullptr) {
+    float* p = nullptr;
+    e = cudaGetSymbolAddress((void**)&p, noalloc_scratch);
+    if (e != cudaSuccess) return (int)e;
+    noalloc_scratch_address[device] = p;
+  }
+  *ptr = noalloc_scratch_address[device];
+  return 0;
+}
+
+}  // namespace ek
+
+EK_EXPORT int ek_attention_decode_bf16_noalloc(void* out, const void* q, int q_row_stride,
+                                               const int* positions, const int* token_slot,
+                                               const void* k_pages, const void* v_pages,
+                                               const int* block_table, int table_stride,
+                                               int n_tokens, int n_q_heads, int n_kv_heads,
+                                               int head_dim, float scale, int window, int n_splits,
+                                               int keys_per_split, cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  float* part_acc = nullptr;
+  float* part_ml = nullptr;
+  if (n_splits > 1) {
+    if (n_q_heads <= 0 || head_dim <= 0) return EK_ERR_ARG;
+    const unsigned long long cells = (unsigned long long)n_tokens * (unsigned long long)n_q_heads *
+                                     (unsigned long long)n_splits;
+    const unsigned long long need = cells * (unsigned long long)(head_dim + 2);
+    if (need > (unsigned long long)EK_NOALLOC_SCRATCH_FLOATS) {
+      fprintf(stderr,
+              "ek_attention_decode_bf16_noalloc: this call needs %llu scratch values, the fixed "
+              "array holds %d; nothing was launched\n", need, EK_NOALLOC_SCRATCH_FLOATS);
+      return EK_NOALLOC_TOO_LARGE;
+    }
+    float* base = nullptr;
+    const int status = ek::noalloc_scratch_pointer(&base);
+    if (status != 0) return status;
+    part_acc = base;                                         // [cells][head_dim]
+    part_ml = base + cells * (unsigned long long)head_dim;   // [cells][2]
+  }
+  return ek_attention_decode_bf16(out, q, q_row_stride, positions, token_slot, k_pages, v_pages,
+                                  block_table, table_stride, n_tokens, n_q_heads, n_kv_heads,
+                                  head_dim, scale, window, n_splits, keys_per_split, part_acc,
+                                  part_ml, stream);
+}
