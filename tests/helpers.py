@@ -81,3 +81,18 @@ def batch_then_steps(engine, seqs, heads):
 
 def plain_model(folder):
     return plain.PlainModel(str(folder), torch.float32)
+
+
+def make_context(dtype, device, positions, slots, cu_seqlens, max_context=None):
+    """A StepContext over explicit per-token positions and slots (for tests of parts alone)."""
+    from enginekernel_b200.parts.base import StepContext, Workspace
+    i32 = dict(dtype=torch.int32, device=device)
+    n = len(positions)
+    lens = [b - a for a, b in zip(cu_seqlens[:-1], cu_seqlens[1:])]
+    return StepContext(
+        n_tokens=n, n_seqs=len(lens), token_ids=torch.zeros(n, **i32),
+        positions=torch.tensor(positions, **i32), token_slot=torch.tensor(slots, **i32),
+        cu_seqlens=torch.tensor(cu_seqlens, **i32), is_decode=all(x == 1 for x in lens),
+        max_new=max(lens), max_context=max_context or (max(positions) + 1), dtype=dtype,
+        device=torch.device(device), workspace=Workspace(device), host_positions=list(positions),
+        host_token_slot=list(slots), host_cu_seqlens=list(cu_seqlens))
