@@ -205,6 +205,35 @@ def attention_decode_bf16(out, q, n_tokens, positions, token_slot, k_pages, v_pa
                       n_splits, keys_per_split, _ptr(part_acc), _ptr(part_ml), _stream())
 
 
+_attn_prefill_bf16 = Function("attention_prefill_bf16", "ek_attention_prefill_bf16",
+                              [_P, _P, c_int, _P, _P, _P, c_int, c_int, _P, _P, _P, c_int, c_int,
+                               c_int, c_int, c_float, c_int, _P])
+
+
+def attention_prefill_supported(dtype, head_dim, n_q_heads, n_kv_heads):
+    return (dtype == torch.bfloat16 and head_dim % 16 == 0 and 16 <= head_dim <= MAX_HEAD_DIM
+            and n_q_heads // n_kv_heads <= 128)
+
+
+def attention_prefill_bf16(out, q, n_tokens, positions, token_slot, cu_seqlens, n_seqs, k_pages,
+                           v_pages, block_table, n_q_heads, n_kv_heads, head_dim, scale,
+                           window=None):
+    """Several new tokens per sequence (bfloat16): sequence b owns rows cu_seqlens[b] ..
+    cu_seqlens[b+1] of ``q``, which stand at consecutive positions; their keys and values
+    are already in the pages."""
+    _need_cuda(out, q, positions, token_slot, cu_seqlens, k_pages, v_pages, block_table)
+    _need(attention_prefill_supported(q.dtype, head_dim, n_q_heads, n_kv_heads),
+          "attention_prefill_bf16: bfloat16, head size a multiple of 16, at most 128 heads a group")
+    _need(out.dtype == q.dtype == k_pages.dtype, "attention: one dtype for q, cache and out")
+    _need(out.is_contiguous() and out.shape[-1] == n_q_heads * head_dim, "attention: out [T, NQ*D]")
+    _need(q.stride(-1) == 1 and q.stride(0) % 8 == 0, "attention: dense, 16-byte aligned q rows")
+    _need(cu_seqlens.dtype == torch.int32 and cu_seqlens.numel() >= n_seqs + 1, "attention: cu_seqlens")
+    _attn_prefill_bf16(_ptr(out), _ptr(q), q.stride(0), _ptr(positions), _ptr(token_slot),
+                       _ptr(cu_seqlens), n_seqs, n_tokens, _ptr(k_pages), _ptr(v_pages),
+                       _ptr(block_table), block_table.stride(0), n_q_heads, n_kv_heads, head_dim,
+                       float(scale), int(window or 0), _stream())
+
+
 # ------------------------------------------------------------------ matrix products
 _gemm_f32 = Function("gemm_f32", "ek_gemm_nt_f32",
                      [_P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P])

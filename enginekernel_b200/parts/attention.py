@@ -90,6 +90,13 @@ class Attention(Mixer):
         t = ctx.n_tokens
         visible = min(ctx.max_context, self.window) if self.window else ctx.max_context
         fast_decode = ctx.is_decode and kernels.attention_decode_supported(self.dtype, self.head_dim)
+        if not ctx.is_decode and kernels.attention_prefill_supported(
+                self.dtype, self.head_dim, self.num_heads, self.num_kv_heads):
+            kernels.attention_prefill_bf16(
+                out, qkv, t, ctx.positions, ctx.token_slot, ctx.cu_seqlens, ctx.n_seqs,
+                entry.k_pages, entry.v_pages, entry.block_table, self.num_heads, self.num_kv_heads,
+                self.head_dim, self.scale, self.window)
+            return
         if fast_decode:
             # blocks = tokens x KV heads (x 16-row blocks of the group); split the keys until
             # about four blocks per SM exist, never finer than one page

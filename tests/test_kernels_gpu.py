@@ -260,6 +260,51 @@ def test_attention_decode_bf16(nq, nkv, d):
             assert rel(out[i], want) <= TOL[dtype], (window, splits, i)
 
 
+@pytest.mark.parametrize("nq,nkv,d", [(4, 2, 16), (6, 2, 48), (32, 8, 128), (5, 5, 80), (16, 1, 256),
+                                      (3, 1, 64), (8, 2, 128)])
+def test_attention_prefill_bf16(nq, nkv, d):
+    """The prompt kernel: several sequences of unequal lengths in one launch, some of them
+    continuing after tokens already in the cache, groups that do not divide 128, windows."""
+    k = K()
+    dtype = torch.bfloat16
+    # (length of the sequence, first new token)
+    seqs = [(1, 0), (64, 0), (65, 0), (517, 0), (130, 100), (200, 199), (300, 37)]
+    pages = Pages(len(seqs), max(n for n, _ in seqs), nkv, d, dtype, seed=7)
+    kv, rows, positions, slots, cu = [], [], [], [], [0]
+    for s, (n, start) in enumerate(seqs):
+        keys, vals = rnd(n, nkv, d, dtype=dtype, seed=10 + s), rnd(n, nkv, d, dtype=dtype, seed=20 + s)
+        pages.fill(s, keys, vals)
+        kv.append((keys, vals))
+        for p in range(start, n):
+            rows.append((s, p))
+            positions.append(p)
+            slots.append(s)
+        cu.append(len(rows))
+    t = len(rows)
+    q = rnd(t, nq * d + 2 * nkv * d, dtype=dtype, seed=30)
+    far = rows.index((3, 516))
+    q[far, :d] = (kv[3][0][3, 0].float() * 4).to(dtype)            # one far key dominates
+    positions = torch.tensor(positions, dtype=torch.int32, device=DEV)
+    slots = torch.tensor(slots, dtype=torch.int32, device=DEV)
+    cu_t = torch.tensor(cu, dtype=torch.int32, device=DEV)
+    scale = 1.0 / math.sqrt(d)
+    for window in (None, 100, 1, 64):
+        out = torch.full((t, nq * d), 7.0, dtype=dtype, device=DEV)
+        k.attention_prefill_bf16(out, q, t, positions, slots, cu_t, len(seqs), pages.k, pages.v,
+                                 pages.table, nq, nkv, d, scale, window)
+        outc, qc = out.cpu(), q.cpu()
+        worst = 0.0
+        for i in range(0, t, 7 if t > 200 else 1):
+            s, p = rows[i]
+            want = ref_attention(qc[i, :nq * d].view(nq, d), kv[s][0].cpu(), kv[s][1].cpu(), p, scale, window)
+            worst = max(worst, rel(outc[i], want))
+        for i in (far, t - 1, cu[4], cu[5], cu[6]):
+            s, p = rows[i]
+            want = ref_attention(qc[i, :nq * d].view(nq, d), kv[s][0].cpu(), kv[s][1].cpu(), p, scale, window)
+            worst = max(worst, rel(outc[i], want))
+        assert worst <= TOL[dtype], (window, worst)
+
+
 # ------------------------------------------------------------------ matrix products
 @pytest.mark.parametrize("m,n,k_", [(1, 331, 80), (3, 2560, 176), (16, 100, 33), (17, 65, 64),
                                     (130, 384, 96), (64, 1, 1)])
