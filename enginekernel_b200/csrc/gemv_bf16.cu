@@ -6,15 +6,18 @@
 //     the contraction index is permuted identically for both operands, which lets each
 //     thread fetch eight consecutive weights of one row (no shared-memory staging);
 //   * the batch is the 8-column operand (M padded to a multiple of 8 in registers);
-//   * the warps of a block split K between them in interleaved 32-element slices and
-//     add their partial tiles in shared memory in warp order (no atomics, so results
-//     are the same from run to run).
+//   * K is split three ways to put enough bytes in flight on 148 SMs whatever N is: over
+//     blocks (grid.y), over the warps of a block, and each warp issues the loads of
+//     several slices before it uses the first;
+//   * partial tiles are summed in a fixed order - warps in shared memory, blocks through
+//     a scratch buffer where the block that arrives last (an atomic ticket, no waiting)
+//     adds the others' partials in split order - so results are the same from run to run.
 // The reference does this with Triton kernels that pad the batch to 16 rows
-// (engine/ek_kernels.py:281-308 `_gemv_kernel`, 413-445 split-K parts,
-// 375-411 SwiGLU epilogue); the epilogues here are: store bfloat16, store 32-bit
-// (logits), and SwiGLU, where one 16-row tile holds 8 gate rows and the 8 matching up
-// rows so that silu(gate) * up is formed in registers and the [M, 2I] intermediate is
-// never written.
+// (engine/ek_kernels.py:281-308 `_gemv_kernel`, 413-445 split-K parts summed by the
+// consumer 447-470, 375-411 SwiGLU epilogue); the epilogues here are: store bfloat16,
+// store 32-bit (logits), and SwiGLU, where one 16-row tile holds 8 gate rows and the 8
+// matching up rows so that silu(gate) * up is formed in registers and the [M, 2I]
+// intermediate is never written.
 #include "common.cuh"
 
 namespace ek {
@@ -42,16 +45,55 @@ __device__ __forceinline__ void mma_bf16(float c[4], uint32_t a0, uint32_t a1, u
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+template <int EPI>
+__device__ __forceinline__ void store_tile(void* out, float4 s, int M, int m0, int ldo, int row_lo,
+                                           int hi_offset, bool lo_ok, bool hi_ok) {
+  // s.x, s.y: weight row lo, batch columns m0, m0+1;  s.z, s.w: weight row hi, same columns
+  if (EPI == EPI_SWIGLU) {
+    if (lo_ok) {
+      bf16* o = (bf16*)out;
+      if (m0 < M) o[(size_t)m0 * ldo + row_lo] = __float2bfloat16_rn(s.x / (1.f + expf(-s.x)) * s.z);
+      if (m0 + 1 < M)
+        o[(size_t)(m0 + 1) * ldo + row_lo] = __float2bfloat16_rn(s.y / (1.f + expf(-s.y)) * s.w);
+    }
+  } else if (EPI == EPI_F32) {
+    float* o = (float*)out;
+    if (lo_ok) {
+      if (m0 < M) o[(size_t)m0 * ldo + row_lo] = s.x;
+      if (m0 + 1 < M) o[(size_t)(m0 + 1) * ldo + row_lo] = s.y;
+    }
+    if (hi_ok) {
+      if (m0 < M) o[(size_t)m0 * ldo + row_lo + hi_offset] = s.z;
+      if (m0 + 1 < M) o[(size_t)(m0 + 1) * ldo + row_lo + hi_offset] = s.w;
+    }
+  } else {
+    bf16* o = (bf16*)out;
+    if (lo_ok) {
+      if (m0 < M) o[(size_t)m0 * ldo + row_lo] = __float2bfloat16_rn(s.x);
+      if (m0 + 1 < M) o[(size_t)(m0 + 1) * ldo + row_lo] = __float2bfloat16_rn(s.y);
+    }
+    if (hi_ok) {
+      if (m0 < M) o[(size_t)m0 * ldo + row_lo + hi_offset] = __float2bfloat16_rn(s.z);
+      if (m0 + 1 < M) o[(size_t)(m0 + 1) * ldo + row_lo + hi_offset] = __float2bfloat16_rn(s.w);
+    }
+  }
+}
+
 // Tile `blockIdx.x` covers weight rows  lo = tile * lo_step + g  and  hi = lo + hi_offset
 // for g = 0..7  (plain: lo_step 16, hi_offset 8; SwiGLU: lo_step 8, hi_offset I).
+// Block (tile, split) handles the 32-wide slices [split * per_split, (split+1) * per_split).
 template <int NT, int EPI>
 __global__ void gemv_bf16_kernel(void* __restrict__ out, const bf16* __restrict__ x,
                                  const bf16* __restrict__ W, int M, int n_lo_rows, int K, int ldx,
-                                 int ldw, int ldo, int lo_step, int hi_offset) {
+                                 int ldw, int ldo, int lo_step, int hi_offset, int per_split,
+                                 float* __restrict__ partials, unsigned int* __restrict__ tickets) {
+  constexpr int UNR = NT <= 2 ? 4 : (NT == 4 ? 2 : 1);   // slices whose loads are issued together
   extern __shared__ float red[];               // [warps][NT][32][4]
+  __shared__ int is_last;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
   const int g = lane >> 2, t = lane & 3;
-  const int row_lo = blockIdx.x * lo_step + g;
+  const int tile = blockIdx.x, split = blockIdx.y, n_split = gridDim.y;
+  const int row_lo = tile * lo_step + g;
   // EPI_BF16/F32: n_lo_rows = N and both halves are checked against it.
   const bool lo_ok = row_lo < n_lo_rows;
   const bool hi_ok = (EPI == EPI_SWIGLU) ? lo_ok : (row_lo + hi_offset < n_lo_rows);
@@ -63,26 +105,31 @@ __global__ void gemv_bf16_kernel(void* __restrict__ out, const bf16* __restrict_
   for (int j = 0; j < NT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
 
   const int n_chunks = (K + 31) >> 5;
-#pragma unroll 4
-  for (int c = warp; c < n_chunks; c += warps) {
-    const int k = (c << 5) + (t << 3);
-    uint4 a_lo = make_uint4(0, 0, 0, 0), a_hi = make_uint4(0, 0, 0, 0);
-    const bool k_ok = k < K;                   // K is a multiple of 8
-    if (k_ok) {
-      a_lo = ldg_stream(w_lo + k);
-      a_hi = ldg_stream(w_hi + k);
+  const int c_begin = split * per_split, c_end = min(n_chunks, c_begin + per_split);
+  for (int c = c_begin + warp * UNR; c < c_end; c += warps * UNR) {
+    uint4 a_lo[UNR], a_hi[UNR], b[UNR][NT];
+#pragma unroll
+    for (int u = 0; u < UNR; ++u) {
+      const int k = ((c + u) << 5) + (t << 3);
+      const bool ok = (c + u) < c_end && k < K;          // K is a multiple of 8
+      a_lo[u] = ok ? ldg_stream(w_lo + k) : make_uint4(0, 0, 0, 0);
+      a_hi[u] = ok ? ldg_stream(w_hi + k) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+      for (int j = 0; j < NT; ++j) {
+        const int m = 8 * j + g;
+        b[u][j] = (ok && m < M) ? ldg_cached(x + (size_t)m * ldx + k) : make_uint4(0, 0, 0, 0);
+      }
     }
 #pragma unroll
-    for (int j = 0; j < NT; ++j) {
-      const int m = 8 * j + g;
-      uint4 b = make_uint4(0, 0, 0, 0);
-      if (k_ok && m < M) b = ldg_cached(x + (size_t)m * ldx + k);
-      mma_bf16(acc[j], a_lo.x, a_hi.x, a_lo.y, a_hi.y, b.x, b.y);
-      mma_bf16(acc[j], a_lo.z, a_hi.z, a_lo.w, a_hi.w, b.z, b.w);
-    }
+    for (int u = 0; u < UNR; ++u)
+#pragma unroll
+      for (int j = 0; j < NT; ++j) {
+        mma_bf16(acc[j], a_lo[u].x, a_hi[u].x, a_lo[u].y, a_hi[u].y, b[u][j].x, b[u][j].y);
+        mma_bf16(acc[j], a_lo[u].z, a_hi[u].z, a_lo[u].w, a_hi[u].w, b[u][j].z, b[u][j].w);
+      }
   }
 
-  // partial tiles -> shared memory, summed in warp order by the first NT warps
+  // warps -> shared memory, summed in warp order by the first NT warps
 #pragma unroll
   for (int j = 0; j < NT; ++j)
     *reinterpret_cast<float4*>(&red[((warp * NT + j) * 32 + lane) * 4]) =
@@ -94,42 +141,41 @@ __global__ void gemv_bf16_kernel(void* __restrict__ out, const bf16* __restrict_
       const float4 p = *reinterpret_cast<const float4*>(&red[((w * NT + j) * 32 + lane) * 4]);
       s.x += p.x; s.y += p.y; s.z += p.z; s.w += p.w;
     }
-    // s.x, s.y: row lo, batch columns 8j+2t, 8j+2t+1;  s.z, s.w: row hi, same columns
-    const int m0 = 8 * j + 2 * t;
-    if (EPI == EPI_SWIGLU) {
-      if (lo_ok) {
-        bf16* o = (bf16*)out;
-        if (m0 < M) o[(size_t)m0 * ldo + row_lo] = __float2bfloat16_rn(s.x / (1.f + expf(-s.x)) * s.z);
-        if (m0 + 1 < M)
-          o[(size_t)(m0 + 1) * ldo + row_lo] = __float2bfloat16_rn(s.y / (1.f + expf(-s.y)) * s.w);
-      }
-    } else if (EPI == EPI_F32) {
-      float* o = (float*)out;
-      if (lo_ok) {
-        if (m0 < M) o[(size_t)m0 * ldo + row_lo] = s.x;
-        if (m0 + 1 < M) o[(size_t)(m0 + 1) * ldo + row_lo] = s.y;
-      }
-      if (hi_ok) {
-        if (m0 < M) o[(size_t)m0 * ldo + row_lo + hi_offset] = s.z;
-        if (m0 + 1 < M) o[(size_t)(m0 + 1) * ldo + row_lo + hi_offset] = s.w;
-      }
+    if (n_split == 1) {
+      store_tile<EPI>(out, s, M, 8 * j + 2 * t, ldo, row_lo, hi_offset, lo_ok, hi_ok);
     } else {
-      bf16* o = (bf16*)out;
-      if (lo_ok) {
-        if (m0 < M) o[(size_t)m0 * ldo + row_lo] = __float2bfloat16_rn(s.x);
-        if (m0 + 1 < M) o[(size_t)(m0 + 1) * ldo + row_lo] = __float2bfloat16_rn(s.y);
-      }
-      if (hi_ok) {
-        if (m0 < M) o[(size_t)m0 * ldo + row_lo + hi_offset] = __float2bfloat16_rn(s.z);
-        if (m0 + 1 < M) o[(size_t)(m0 + 1) * ldo + row_lo + hi_offset] = __float2bfloat16_rn(s.w);
-      }
+      *reinterpret_cast<float4*>(
+          &partials[((((size_t)tile * n_split + split) * NT + j) * 32 + lane) * 4]) = s;
     }
+  }
+  if (n_split == 1) return;
+
+  // blocks: the last one to finish this tile adds all partials in split order
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned int ticket = atomicAdd(&tickets[tile], 1u);
+    is_last = ticket == (unsigned int)(n_split - 1);
+    if (is_last) tickets[tile] = 0;            // ready for the next launch
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  for (int j = warp; j < NT; j += warps) {
+    float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int sp = 0; sp < n_split; ++sp) {
+      const float4 p = __ldcg(reinterpret_cast<const float4*>(
+          &partials[((((size_t)tile * n_split + sp) * NT + j) * 32 + lane) * 4]));
+      s.x += p.x; s.y += p.y; s.z += p.z; s.w += p.w;
+    }
+    store_tile<EPI>(out, s, M, 8 * j + 2 * t, ldo, row_lo, hi_offset, lo_ok, hi_ok);
   }
 }
 
 template <int NT, int EPI>
 static int launch_nt(void* out, const void* x, const void* W, int M, int N, int K, int ldx, int ldw,
-                     int ldo, int warps, cudaStream_t stream) {
+                     int ldo, int warps, int n_split, float* partials, unsigned int* tickets,
+                     long long partial_floats, int n_tickets, cudaStream_t stream) {
   int tiles, lo_step, hi_offset, n_lo_rows;
   if (EPI == EPI_SWIGLU) {                     // N = 2 * I rows: gate rows then up rows
     const int inter = N / 2;
@@ -137,40 +183,67 @@ static int launch_nt(void* out, const void* x, const void* W, int M, int N, int 
   } else {
     tiles = (N + 15) / 16; lo_step = 16; hi_offset = 8; n_lo_rows = N;
   }
+  const int n_chunks = (K + 31) / 32;
+  if (n_split > n_chunks) n_split = n_chunks;
+  if (n_split > 1) {
+    if (!partials || !tickets || tiles > n_tickets ||
+        (long long)tiles * n_split * NT * 128 > partial_floats)
+      n_split = 1;                             // no room for partials: one block per tile
+  }
+  const int per_split = (n_chunks + n_split - 1) / n_split;
+  n_split = (n_chunks + per_split - 1) / per_split;
   const size_t smem = (size_t)warps * NT * 32 * 4 * sizeof(float);
   if (smem > 40 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(gemv_bf16_kernel<NT, EPI>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
-  gemv_bf16_kernel<NT, EPI><<<tiles, warps * 32, smem, stream>>>(
-      out, (const bf16*)x, (const bf16*)W, M, n_lo_rows, K, ldx, ldw, ldo, lo_step, hi_offset);
+  dim3 grid(tiles, n_split);
+  gemv_bf16_kernel<NT, EPI><<<grid, warps * 32, smem, stream>>>(
+      out, (const bf16*)x, (const bf16*)W, M, n_lo_rows, K, ldx, ldw, ldo, lo_step, hi_offset,
+      per_split, partials, tickets);
   EK_RETURN_LAUNCH_STATUS();
 }
 
 template <int EPI>
 static int launch(void* out, const void* x, const void* W, int M, int N, int K, int ldx, int ldw,
-                  int ldo, int warps, cudaStream_t stream) {
+                  int ldo, int warps, int n_split, float* partials, unsigned int* tickets,
+                  long long partial_floats, int n_tickets, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
-  if (M > 64 || K <= 0 || K % 8 || ldx % 8 || ldw % 8 || warps < 1 || warps > 32 ||
-      (EPI == EPI_SWIGLU && (N & 1)))
+  if (M > 64 || K <= 0 || K % 8 || ldx % 8 || ldw % 8 || warps < 1 || warps > 32 || n_split < 1 ||
+      n_split > 65535 || (EPI == EPI_SWIGLU && (N & 1)))
     return EK_ERR_ARG;
-  if (warps > 16) warps = 16;              // 8 batch tiles need 96 registers a thread
-  if (M <= 8) return launch_nt<1, EPI>(out, x, W, M, N, K, ldx, ldw, ldo, warps, stream);
-  if (M <= 16) return launch_nt<2, EPI>(out, x, W, M, N, K, ldx, ldw, ldo, warps, stream);
-  if (M <= 32) return launch_nt<4, EPI>(out, x, W, M, N, K, ldx, ldw, ldo, warps, stream);
-  return launch_nt<8, EPI>(out, x, W, M, N, K, ldx, ldw, ldo, warps, stream);
+  if (warps > 16) warps = 16;              // 8 batch tiles need up to 128 registers a thread
+#define EK_GO(NT) \
+  return launch_nt<NT, EPI>(out, x, W, M, N, K, ldx, ldw, ldo, warps, n_split, partials, tickets, \
+                            partial_floats, n_tickets, stream)
+  if (M <= 8) EK_GO(1);
+  if (M <= 16) EK_GO(2);
+  if (M <= 32) EK_GO(4);
+  EK_GO(8);
+#undef EK_GO
 }
 
 }  // namespace ek
 
-// epilogue: 0 bfloat16 out [M,N]; 1 float out [M,N]; 2 SwiGLU, bfloat16 out [M,N/2]
+// epilogue: 0 bfloat16 out [M,N]; 1 float out [M,N]; 2 SwiGLU, bfloat16 out [M,N/2].
+// n_split > 1 cuts K over blocks and needs `partials` (partial_floats 32-bit values, at least
+// tiles * n_split * ceil8(M) * 16) and `tickets` (n_tickets >= tiles unsigned ints, zero before
+// the first launch; every launch leaves them zero).  Without room it runs unsplit.
 EK_EXPORT int ek_gemv_bf16(void* out, const void* x, const void* W, int M, int N, int K, int ldx,
-                           int ldw, int ldo, int epilogue, int warps, cudaStream_t stream) {
+                           int ldw, int ldo, int epilogue, int warps, int n_split, float* partials,
+                           unsigned int* tickets, long long partial_floats, int n_tickets,
+                           cudaStream_t stream) {
   switch (epilogue) {
-    case ek::EPI_BF16: return ek::launch<ek::EPI_BF16>(out, x, W, M, N, K, ldx, ldw, ldo, warps, stream);
-    case ek::EPI_F32: return ek::launch<ek::EPI_F32>(out, x, W, M, N, K, ldx, ldw, ldo, warps, stream);
-    case ek::EPI_SWIGLU: return ek::launch<ek::EPI_SWIGLU>(out, x, W, M, N, K, ldx, ldw, ldo, warps, stream);
+    case ek::EPI_BF16:
+      return ek::launch<ek::EPI_BF16>(out, x, W, M, N, K, ldx, ldw, ldo, warps, n_split, partials,
+                                      tickets, partial_floats, n_tickets, stream);
+    case ek::EPI_F32:
+      return ek::launch<ek::EPI_F32>(out, x, W, M, N, K, ldx, ldw, ldo, warps, n_split, partials,
+                                     tickets, partial_floats, n_tickets, stream);
+    case ek::EPI_SWIGLU:
+      return ek::launch<ek::EPI_SWIGLU>(out, x, W, M, N, K, ldx, ldw, ldo, warps, n_split, partials,
+                                        tickets, partial_floats, n_tickets, stream);
   }
   return EK_ERR_ARG;
 }

@@ -142,6 +142,80 @@ sample_kernel(int* __restrict__ out_token, const float* __restrict__ logits, lon
   if (tid == 0) out_token[row] = best.index == 0x7fffffff ? 0 : best.index;
 }
 
+// Wide rows without top-k: the vocabulary is cut into `segments` pieces, one block each,
+// whose best (score, index) pairs a second small kernel merges.  Maximum and tie rule are
+// associative, so the result equals the one-block kernel's.
+__global__ void __launch_bounds__(256)
+sample_partial_kernel(float* __restrict__ part_score, int* __restrict__ part_index,
+                      const float* __restrict__ logits, long long row_stride, int vocab,
+                      int segments, float temperature, unsigned long long seed,
+                      const int* __restrict__ streams, const int* __restrict__ draws,
+                      const int* __restrict__ active, const int* __restrict__ dyn) {
+  __shared__ Best scratch[33];
+  const int row = blockIdx.x, seg = blockIdx.y, tid = threadIdx.x;
+  if (active && active[row] < 0) return;
+  if (dyn) {
+    temperature = __int_as_float(dyn[0]);
+    seed = (unsigned long long)(uint32_t)dyn[2] | ((unsigned long long)(uint32_t)dyn[3] << 32);
+  }
+  const float* x = logits + (size_t)row * row_stride;
+  // segments are whole groups of 4 entries, so a Philox block never straddles two of them
+  const int groups = (vocab + 3) / 4;
+  const int per = (groups + segments - 1) / segments;
+  const int g_begin = seg * per, g_end = min(groups, g_begin + per);
+  Best best{-INFINITY, 0x7fffffff};
+  if (temperature > 0.f) {
+    const float inv_t = 1.f / temperature;
+    const uint32_t k0 = (uint32_t)seed, k1 = (uint32_t)(seed >> 32);
+    const uint32_t stream = streams ? (uint32_t)streams[row] : (uint32_t)row;
+    const uint32_t draw = draws ? (uint32_t)draws[row] : 0u;
+    for (int g = g_begin + tid; g < g_end; g += blockDim.x) {
+      uint32_t w[4];
+      philox4x32_10((uint32_t)g, draw, stream, 0u, k0, k1, w);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int i = 4 * g + j;
+        if (i >= vocab) break;
+        const float v = x[i];
+        if (!(v == v)) continue;
+        const float u = ((float)(w[j] >> 9) + 0.5f) * (1.0f / 8388608.0f);
+        best = better(best, Best{v * inv_t - logf(-logf(u)), i});
+      }
+    }
+  } else {
+    for (int g = g_begin + tid; g < g_end; g += blockDim.x) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int i = 4 * g + j;
+        if (i >= vocab) break;
+        const float v = x[i];
+        if (v == v) best = better(best, Best{v, i});
+      }
+    }
+  }
+  best = block_best(best, scratch);
+  if (tid == 0) {
+    part_score[(size_t)row * segments + seg] = best.score;
+    part_index[(size_t)row * segments + seg] = best.index;
+  }
+}
+
+__global__ void sample_final_kernel(int* __restrict__ out_token, const float* __restrict__ part_score,
+                                    const int* __restrict__ part_index, int segments,
+                                    const int* __restrict__ active) {
+  const int row = blockIdx.x;
+  if (active && active[row] < 0) return;
+  Best best{-INFINITY, 0x7fffffff};
+  for (int s = threadIdx.x; s < segments; s += 32)
+    best = better(best, Best{part_score[(size_t)row * segments + s], part_index[(size_t)row * segments + s]});
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    Best other{__shfl_xor_sync(0xffffffffu, best.score, o), __shfl_xor_sync(0xffffffffu, best.index, o)};
+    best = better(best, other);
+  }
+  if (threadIdx.x == 0) out_token[row] = best.index == 0x7fffffff ? 0 : best.index;
+}
+
 // After sampling: record the token, count the draw, decide whether the sequence goes on.
 // A row whose position is negative is finished: it emits -1 and nothing of it changes.
 __global__ void decode_advance_kernel(const int* __restrict__ sampled, int* __restrict__ token_ids,
@@ -184,6 +258,28 @@ EK_EXPORT int ek_sample(int* out_token, const float* logits, long long row_strid
   ek::sample_kernel<<<rows, ek::kSampleThreads, 0, stream>>>(out_token, logits, row_stride, vocab,
                                                             temperature, top_k, seed, streams,
                                                             draws, active, dyn);
+  EK_RETURN_LAUNCH_STATUS();
+}
+
+// Two launches over `segments` pieces of the vocabulary; top-k is not offered here.
+// part_score / part_index: rows * segments values each.
+EK_EXPORT int ek_sample_wide(int* out_token, const float* logits, long long row_stride, int rows,
+                             int vocab, float temperature, unsigned long long seed,
+                             const int* streams, const int* draws, const int* active,
+                             const int* dyn, float* part_score, int* part_index, int segments,
+                             cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (vocab <= 0 || temperature < 0.f || segments < 1 || segments > 1024 || !part_score ||
+      !part_index || rows > 65535)
+    return EK_ERR_ARG;
+  dim3 grid(rows, segments);
+  ek::sample_partial_kernel<<<grid, 256, 0, stream>>>(part_score, part_index, logits, row_stride,
+                                                     vocab, segments, temperature, seed, streams,
+                                                     draws, active, dyn);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return (int)e;
+  ek::sample_final_kernel<<<rows, 32, 0, stream>>>(out_token, part_score, part_index, segments,
+                                                  active);
   EK_RETURN_LAUNCH_STATUS();
 }
 

@@ -48,6 +48,9 @@ class DecodeState:
         self.stop_ids = torch.zeros(64, **i32)
         self.n_stop = 0
         self.settings = kernels.sampling_settings(0.0, 0, 0, dev)
+        self.top_k = 0                           # host copy: chooses the sampling kernel
+        self.part_score = torch.zeros(batch * kernels.SAMPLE_SEGMENTS, dtype=torch.float32, device=dev)
+        self.part_index = torch.zeros(batch * kernels.SAMPLE_SEGMENTS, **i32)
         self.workspace = Workspace(dev)          # owned by the graph: never regrown elsewhere
         self.graph = None
         self.use_graph = use_graph
@@ -57,18 +60,28 @@ class DecodeState:
             token_slot=self.token_slot, cu_seqlens=self.cu_seqlens, is_decode=True, max_new=1,
             max_context=bucket, dtype=runner.model.dtype, device=dev, workspace=self.workspace)
 
-    def configure(self, stop_ids: Sequence[int]):
+    def configure(self, stop_ids: Sequence[int], sampling: SamplingParams):
         if len(stop_ids) > self.stop_ids.numel():
             raise ValueError(f"at most {self.stop_ids.numel()} stop tokens")
-        if self.n_stop != len(stop_ids) and self.graph is not None:
-            self.graph = None                     # the count is a launch constant
+        # the stop count and the choice of sampling kernel are fixed in a captured step
+        if (self.n_stop != len(stop_ids) or (self.top_k > 0) != (sampling.top_k > 0)) \
+                and self.graph is not None:
+            self.graph = None
         self.n_stop = len(stop_ids)
+        self.top_k = sampling.top_k
         if stop_ids:
             self.stop_ids[:len(stop_ids)] = torch.tensor(list(stop_ids), dtype=torch.int32)
+        self.settings.copy_(kernels.sampling_settings(sampling.temperature, sampling.top_k,
+                                                      sampling.seed, self.settings.device))
 
     def sample_and_advance(self, logits):
-        kernels.sample(self.sampled, logits, 0.0, 0, 0, streams=self.streams, draws=self.draws,
-                       active=self.positions, n_rows=self.batch, dyn=self.settings)
+        if self.top_k > 0 or logits.shape[-1] < 4096:
+            kernels.sample(self.sampled, logits, 0.0, 0, 0, streams=self.streams, draws=self.draws,
+                           active=self.positions, n_rows=self.batch, dyn=self.settings)
+        else:
+            kernels.sample_wide(self.sampled, logits, 0.0, 0, self.part_score, self.part_index,
+                                streams=self.streams, draws=self.draws, active=self.positions,
+                                n_rows=self.batch, dyn=self.settings)
         kernels.decode_advance(self.sampled, self.token_ids, self.positions, self.draws,
                                self.remaining, self.out_tokens, self.step_index, self.stop_ids,
                                self.n_stop, self.batch)
@@ -129,9 +142,7 @@ class DeviceBatchRun:
             self.max_steps = max(max_new)
             st = backend.state_for(self.batch, total, self.max_steps)
             self.state = st
-            st.configure(stop_ids)
-            st.settings.copy_(kernels.sampling_settings(sampling.temperature, sampling.top_k,
-                                                        sampling.seed, runner.device))
+            st.configure(stop_ids, sampling)
             # prefill: every prompt in one step, logits at each prompt's last token
             logits = runner.step([StepEntry(s, p, [len(p) - 1]) for s, p in zip(self.slots, prompts)])
             i32 = dict(dtype=torch.int32)

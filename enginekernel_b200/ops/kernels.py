@@ -238,7 +238,8 @@ def attention_prefill_bf16(out, q, n_tokens, positions, token_slot, cu_seqlens, 
 _gemm_f32 = Function("gemm_f32", "ek_gemm_nt_f32",
                      [_P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P])
 _gemv_bf16 = Function("gemv_bf16", "ek_gemv_bf16",
-                      [_P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P])
+                      [_P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                       _P, _P, c_longlong, c_int, _P])
 
 EPI_BF16, EPI_F32, EPI_SWIGLU = 0, 1, 2
 
@@ -254,17 +255,33 @@ def gemm_f32(out, x, w, n_rows=None):
     _gemm_f32(_ptr(out), _ptr(x), _ptr(w), m, n, k, x.stride(0), w.stride(0), out.stride(0), _stream())
 
 
-def _gemv_warps(n_tiles, k):
-    """Warps per block (they split K): enough blocks x warps to fill 148 SMs."""
-    chunks = max(1, k // 32)
-    want = max(4, min(16, -(-148 * 16 // max(1, n_tiles))))
-    w = 4
-    while w * 2 <= want and w * 2 <= chunks:
-        w *= 2
-    return w
+SM_COUNT = 148
+_GEMV_PARTIAL_FLOATS = 4 * 1024 * 1024      # 16 MiB of split partials per device
+_GEMV_TICKETS = 16384
+_gemv_scratch = {}
 
 
-def gemv_bf16(out, x, w, epilogue=EPI_BF16, n_rows=None, warps=None):
+def gemv_scratch(device):
+    """Per-device scratch of the split-K path: partial tiles and zeroed tickets.  Created on
+    first use; create it before capturing a graph (``ModelRunner`` does)."""
+    key = str(torch.device(device))
+    if key not in _gemv_scratch:
+        _gemv_scratch[key] = (torch.empty(_GEMV_PARTIAL_FLOATS, dtype=torch.float32, device=device),
+                              torch.zeros(_GEMV_TICKETS, dtype=torch.int32, device=device))
+    return _gemv_scratch[key]
+
+
+def _gemv_plan(n_tiles, k, m):
+    """(warps a block, blocks along K): about four blocks an SM, each warp with at least one
+    full batch of loads."""
+    chunks = max(1, -(-k // 32))
+    unroll = 4 if m <= 16 else (2 if m <= 32 else 1)
+    warps = max(1, min(8, chunks // unroll))
+    splits = max(1, min(-(-4 * SM_COUNT // n_tiles), chunks // (warps * unroll)))
+    return warps, splits
+
+
+def gemv_bf16(out, x, w, epilogue=EPI_BF16, n_rows=None, warps=None, splits=None):
     """out = x . w^T for at most 64 rows of x, bfloat16 in, 32-bit accumulation.
 
     ``epilogue``: EPI_BF16 -> out bfloat16 [M, N]; EPI_F32 -> out float32 [M, N];
@@ -284,13 +301,22 @@ def gemv_bf16(out, x, w, epilogue=EPI_BF16, n_rows=None, warps=None):
     if epilogue == EPI_SWIGLU:
         _need(n % 2 == 0, "gemv_bf16: SwiGLU needs gate and up rows")
     tiles = -(-n_out // (8 if epilogue == EPI_SWIGLU else 16))
+    plan_warps, plan_splits = _gemv_plan(tiles, k, m)
+    warps = warps or plan_warps
+    splits = splits or plan_splits
+    partials, tickets = gemv_scratch(x.device) if splits > 1 else (None, None)
     _gemv_bf16(_ptr(out), _ptr(x), _ptr(w), m, n, k, x.stride(0), w.stride(0), out.stride(0),
-               epilogue, warps or _gemv_warps(tiles, k), _stream())
+               epilogue, warps, splits, _ptr(partials), _ptr(tickets),
+               _GEMV_PARTIAL_FLOATS if partials is not None else 0,
+               _GEMV_TICKETS if tickets is not None else 0, _stream())
 
 
 # ------------------------------------------------------------------ sampling and decode state
 _sample = Function("sampling", "ek_sample",
                    [_P, _P, c_longlong, c_int, c_int, c_float, c_int, c_ulonglong, _P, _P, _P, _P, _P])
+_sample_wide = Function("sampling", "ek_sample_wide",
+                        [_P, _P, c_longlong, c_int, c_int, c_float, c_ulonglong, _P, _P, _P, _P, _P,
+                         _P, c_int, _P])
 _decode_advance = Function("sampling", "ek_decode_advance",
                            [_P, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, _P])
 
@@ -317,6 +343,25 @@ def sample(out_token, logits, temperature, top_k, seed, streams=None, draws=None
     _sample(_ptr(out_token), _ptr(logits), logits.stride(0), rows, logits.shape[-1],
             float(temperature), int(top_k), int(seed) & 0xFFFFFFFFFFFFFFFF, _ptr(streams),
             _ptr(draws), _ptr(active), _ptr(dyn), _stream())
+
+
+SAMPLE_SEGMENTS = 32
+
+
+def sample_wide(out_token, logits, temperature, seed, part_score, part_index, streams=None,
+                draws=None, active=None, n_rows=None, dyn=None):
+    """:func:`sample` without top-k, spread over ``SAMPLE_SEGMENTS`` blocks a row (for wide
+    vocabularies).  ``part_score`` float32 / ``part_index`` int32: rows * SAMPLE_SEGMENTS each."""
+    _need_cuda(out_token, logits, streams, draws, active, dyn, part_score, part_index)
+    _need(logits.dtype == torch.float32 and logits.stride(-1) == 1, "sample: dense 32-bit logits")
+    rows = n_rows if n_rows is not None else logits.shape[0]
+    _need(part_score.dtype == torch.float32 and part_index.dtype == torch.int32
+          and part_score.numel() >= rows * SAMPLE_SEGMENTS
+          and part_index.numel() >= rows * SAMPLE_SEGMENTS, "sample_wide: partial buffers")
+    _sample_wide(_ptr(out_token), _ptr(logits), logits.stride(0), rows, logits.shape[-1],
+                 float(temperature), int(seed) & 0xFFFFFFFFFFFFFFFF, _ptr(streams), _ptr(draws),
+                 _ptr(active), _ptr(dyn), _ptr(part_score), _ptr(part_index), SAMPLE_SEGMENTS,
+                 _stream())
 
 
 def decode_advance(sampled, token_ids, positions, draws, remaining, out_tokens, step_index,

@@ -342,10 +342,20 @@ def test_gemv_bf16_epilogues(m, n, k_):
         k.gemv_bf16(act, x, w, k.EPI_SWIGLU)
         g, u = want[:, :inter], want[:, inter:]
         assert rel(act, g / (1 + torch.exp(-g)) * u) <= 4e-3
-    for warps in (1, 4, 32):
+    for warps, splits in ((1, 1), (4, 3), (8, 7), (32, 2), (2, 64)):
         o = torch.empty(m, n, device=DEV)
-        k.gemv_bf16(o, x, w, k.EPI_F32, warps=warps)
+        k.gemv_bf16(o, x, w, k.EPI_F32, warps=warps, splits=splits)
         assert rel(o, want) <= 1e-5
+        again = torch.empty(m, n, device=DEV)
+        k.gemv_bf16(again, x, w, k.EPI_F32, warps=warps, splits=splits)
+        assert torch.equal(o, again)                       # fixed summation order: bit-stable
+        if n % 2 == 0:
+            act2 = torch.empty(m, n // 2, dtype=torch.bfloat16, device=DEV)
+            k.gemv_bf16(act2, x, w, k.EPI_SWIGLU, warps=warps, splits=splits)
+            g, u = want[:, :n // 2], want[:, n // 2:]
+            assert rel(act2, g / (1 + torch.exp(-g)) * u) <= 4e-3
+    _, tickets = k.gemv_scratch(DEV)
+    assert int(tickets.abs().sum()) == 0                   # every launch leaves the tickets zero
 
 
 def test_gemv_refuses_what_it_cannot_do():
@@ -388,6 +398,31 @@ def test_sample_greedy_gumbel_topk():
                 continue
             want = plain.sample_token(logits[r].cpu(), temp, topk, seed, int(streams[r]), int(draws[r]))
             assert out[r].item() == want, (temp, topk, r)
+
+
+def test_sample_wide_equals_the_one_block_kernel():
+    k = K()
+    for vocab in (4099, 151936):
+        g = torch.Generator().manual_seed(vocab)
+        logits = (torch.randn(6, vocab, generator=g) * 2).to(DEV)
+        logits[2, 5] = logits[2, vocab - 1] = 40.0            # a tie across segments
+        streams = torch.tensor([3, 1, 4, 1, 5, 9], dtype=torch.int32, device=DEV)
+        draws = torch.tensor([0, 1, 2, 3, 4, 5], dtype=torch.int32, device=DEV)
+        active = torch.tensor([1, 1, 1, -1, 1, 1], dtype=torch.int32, device=DEV)
+        ps = torch.empty(6 * k.SAMPLE_SEGMENTS, device=DEV)
+        pi = torch.empty(6 * k.SAMPLE_SEGMENTS, dtype=torch.int32, device=DEV)
+        for temp, seed in ((0.0, 0), (0.9, 77), (2.0, (1 << 35) + 1)):
+            one = torch.full((6,), -5, dtype=torch.int32, device=DEV)
+            wide = torch.full((6,), -5, dtype=torch.int32, device=DEV)
+            k.sample(one, logits, temp, 0, seed, streams=streams, draws=draws, active=active)
+            k.sample_wide(wide, logits, temp, seed, ps, pi, streams=streams, draws=draws, active=active)
+            assert torch.equal(one, wide) and wide[3].item() == -5
+            dyn = torch.full((6,), -5, dtype=torch.int32, device=DEV)
+            k.sample_wide(dyn, logits, 0.0, 0, ps, pi, streams=streams, draws=draws, active=active,
+                          dyn=k.sampling_settings(temp, 0, seed, DEV))
+            assert torch.equal(dyn, wide)
+        if temp == 0.0:
+            assert wide[2].item() == 5
 
 
 def test_sample_distribution():
