@@ -25,8 +25,9 @@ constexpr int kUnit = 16;                    // keys per warp iteration
 
 __device__ __forceinline__ uint4 ldg16(const void* p) {
   uint4 v;
-  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  // not .nc: the newest key and value were written by the kernel just before this one
+  asm volatile("ld.global.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
   return v;
 }
 __device__ __forceinline__ void mma16816(float c[4], uint32_t a0, uint32_t a1, uint32_t a2,
@@ -53,8 +54,8 @@ __device__ __forceinline__ uint32_t reg_of(const uint4& v, int i) {
 // grid (tokens, kv_heads * row_blocks, splits); DCH = head_dim / 32
 template <int DCH>
 __global__ void __launch_bounds__(kDecWarps * 32)
-attention_decode_bf16_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, int q_row_stride,
-                             const int* __restrict__ positions, const int* __restrict__ token_slot,
+attention_decode_bf16_kernel(bf16* __restrict__ out, const bf16* q, int q_row_stride,
+                             const int* positions, const int* token_slot,
                              PagedKV cache, int n_q_heads, int row_blocks, float scale_log2,
                              int window, int n_splits, int keys_per_split,
                              float* __restrict__ part_acc, float* __restrict__ part_ml) {
@@ -62,6 +63,8 @@ attention_decode_bf16_kernel(bf16* __restrict__ out, const bf16* __restrict__ q,
   extern __shared__ float smem[];              // [warps][16][D] accumulators, then [warps][16][2]
   float* o_s = smem;
   float* ml_s = smem + kDecWarps * 16 * D;
+  pdl_launch_dependents();
+  pdl_wait();
 
   const int t = blockIdx.x;
   const int kv_head = blockIdx.y / row_blocks, rb = blockIdx.y % row_blocks;
@@ -236,9 +239,11 @@ attention_decode_bf16_kernel(bf16* __restrict__ out, const bf16* __restrict__ q,
 
 // Merge split partials in split order (running maxima are in log2 units).
 __global__ void attention_decode_combine_kernel(bf16* __restrict__ out,
-                                                const float* __restrict__ part_acc,
-                                                const float* __restrict__ part_ml, int n_q_heads,
+                                                const float* part_acc,
+                                                const float* part_ml, int n_q_heads,
                                                 int head_dim, int n_splits) {
+  pdl_launch_dependents();
+  pdl_wait();
   const size_t th = (size_t)blockIdx.x * n_q_heads + blockIdx.y;
   const float* ml = part_ml + 2 * th * n_splits;
   float m = -INFINITY;
@@ -271,15 +276,14 @@ static int launch_dch(bf16* out, const bf16* q, int q_row_stride, const int* pos
     if (e != cudaSuccess) return (int)e;
   }
   dim3 grid(n_tokens, cache.heads * row_blocks, n_splits);
-  attention_decode_bf16_kernel<DCH><<<grid, kDecWarps * 32, smem, stream>>>(
-      out, q, q_row_stride, positions, token_slot, cache, n_q_heads, row_blocks,
-      scale * 1.4426950408889634f, window, n_splits, keys_per_split, part_acc, part_ml);
-  cudaError_t e = cudaGetLastError();
+  cudaError_t e = launch_pdl(attention_decode_bf16_kernel<DCH>, grid, dim3(kDecWarps * 32), smem,
+                             stream, out, q, q_row_stride, positions, token_slot, cache, n_q_heads,
+                             row_blocks, scale * 1.4426950408889634f, window, n_splits,
+                             keys_per_split, part_acc, part_ml);
   if (e != cudaSuccess || n_splits == 1) return (int)e;
   dim3 cgrid(n_tokens, n_q_heads);
-  attention_decode_combine_kernel<<<cgrid, 64, 0, stream>>>(out, part_acc, part_ml, n_q_heads, D,
-                                                            n_splits);
-  EK_RETURN_LAUNCH_STATUS();
+  return (int)launch_pdl(attention_decode_combine_kernel, cgrid, dim3(64), 0, stream, out,
+                         (const float*)part_acc, (const float*)part_ml, n_q_heads, D, n_splits);
 }
 
 }  // namespace ek

@@ -88,6 +88,32 @@ __device__ __forceinline__ size_t page_offset(const PagedKV& c, int page, int he
   return (((size_t)page * c.heads + head) * EK_PAGE + (pos & (EK_PAGE - 1))) * (size_t)c.head_dim;
 }
 
+// Programmatic dependent launch: a kernel launched with `launch_pdl` may start while the
+// kernel before it on the stream is still draining.  It must call `pdl_wait()` before it
+// reads anything that kernel wrote or writes anything that kernel reads (only constants -
+// weights, tables - may be touched earlier), and calls `pdl_launch_dependents()` at its top
+// so that its own successor can be set up early.  Both are no-ops in a plain launch.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                              cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 }  // namespace ek
 
 #define EK_RETURN_LAUNCH_STATUS() return (int)cudaGetLastError()

@@ -12,7 +12,9 @@ namespace ek {
 
 template <typename T>
 __global__ void embed_kernel(float* __restrict__ resid, const T* __restrict__ table,
-                             const int* __restrict__ ids, int hidden, int vocab) {
+                             const int* ids, int hidden, int vocab) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.x;
   int id = ids[t];
   id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
@@ -25,12 +27,13 @@ __global__ void embed_kernel(float* __restrict__ resid, const T* __restrict__ ta
 // If `add` is given, the stream first becomes stream + add (written back when
 // `write_back`).  If `rows` is given, output row i reads stream row rows[i].
 template <typename T>
-__global__ void rmsnorm_kernel(T* __restrict__ y, float* __restrict__ resid,
-                               const T* __restrict__ add, const float* __restrict__ gain,
-                               const int* __restrict__ rows, float eps, int hidden,
+__global__ void rmsnorm_kernel(T* __restrict__ y, float* resid, const T* add,
+                               const float* __restrict__ gain, const int* rows, float eps, int hidden,
                                int write_back) {
   __shared__ float scratch[33];
   extern __shared__ float row_cache[];          // `hidden` floats
+  pdl_launch_dependents();
+  pdl_wait();
   const int out_row = blockIdx.x;
   const int src_row = rows ? rows[out_row] : out_row;
   float* r = resid + (size_t)src_row * hidden;
@@ -84,9 +87,8 @@ static int launch_rmsnorm(void* y, float* resid, const void* add, const float* g
     if (e != cudaSuccess) return (int)e;
   }
   int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
-  rmsnorm_kernel<T><<<n_rows, threads, smem, stream>>>((T*)y, resid, (const T*)add, gain, rows,
-                                                       eps, hidden, write_back);
-  EK_RETURN_LAUNCH_STATUS();
+  return (int)launch_pdl(rmsnorm_kernel<T>, dim3(n_rows), dim3(threads), smem, stream, (T*)y, resid,
+                         (const T*)add, gain, rows, eps, hidden, write_back);
 }
 
 }  // namespace ek
@@ -97,8 +99,8 @@ using namespace ek;
   EK_EXPORT int ek_embed_##SUFFIX(float* resid, const void* table, const int* ids, int n_tokens, \
                                   int hidden, int vocab, cudaStream_t stream) {                 \
     if (n_tokens <= 0) return 0;                                                                \
-    embed_kernel<T><<<n_tokens, 256, 0, stream>>>(resid, (const T*)table, ids, hidden, vocab);  \
-    EK_RETURN_LAUNCH_STATUS();                                                                  \
+    return (int)ek::launch_pdl(embed_kernel<T>, dim3(n_tokens), dim3(256), 0, stream, resid,    \
+                               (const T*)table, ids, hidden, vocab);                            \
   }                                                                                             \
   EK_EXPORT int ek_rmsnorm_##SUFFIX(void* y, float* resid, const void* add, const float* gain,  \
                                     const int* rows, float eps, int n_rows, int hidden,         \

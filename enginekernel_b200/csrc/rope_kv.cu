@@ -14,15 +14,17 @@ namespace ek {
 constexpr int kRopeWarps = 4;
 
 template <typename T>
-__global__ void qk_norm_rope_kv_kernel(T* __restrict__ qkv, int row_stride,
+__global__ void qk_norm_rope_kv_kernel(T* qkv, int row_stride,
                                        const float* __restrict__ q_gain,
                                        const float* __restrict__ k_gain,
                                        const float* __restrict__ cos_tab,
                                        const float* __restrict__ sin_tab, int rot_dim,
-                                       const int* __restrict__ positions,
-                                       const int* __restrict__ token_slot, PagedKV cache,
+                                       const int* positions, const int* token_slot,
+                                       PagedKV cache,
                                        int n_q_heads, float eps, int write_kv) {
   __shared__ float buf[kRopeWarps][EK_MAX_HEAD_DIM];
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int head = blockIdx.y * kRopeWarps + warp;
@@ -93,10 +95,9 @@ static int launch(void* qkv, int row_stride, const float* q_gain, const float* k
   PagedKV cache{k_pages, v_pages, block_table, table_stride, n_kv_heads, head_dim};
   const int heads = n_q_heads + 2 * n_kv_heads;
   dim3 grid(n_tokens, (heads + kRopeWarps - 1) / kRopeWarps);
-  qk_norm_rope_kv_kernel<T><<<grid, kRopeWarps * 32, 0, stream>>>(
-      (T*)qkv, row_stride, q_gain, k_gain, cos_tab, sin_tab, rot_dim, positions, token_slot, cache,
-      n_q_heads, eps, write_kv);
-  EK_RETURN_LAUNCH_STATUS();
+  return (int)launch_pdl(qk_norm_rope_kv_kernel<T>, grid, dim3(kRopeWarps * 32), 0, stream, (T*)qkv,
+                         row_stride, q_gain, k_gain, cos_tab, sin_tab, rot_dim, positions,
+                         token_slot, cache, n_q_heads, eps, write_kv);
 }
 
 }  // namespace ek

@@ -67,13 +67,14 @@ __device__ Best block_best(Best v, Best* scratch) {
 // `dyn` (optional, 4 ints on the device: temperature bits, top_k, seed low, seed high)
 // replaces the by-value settings, so that a captured launch follows later changes.
 __global__ void __launch_bounds__(kSampleThreads)
-sample_kernel(int* __restrict__ out_token, const float* __restrict__ logits, long long row_stride,
-              int vocab, float temperature, int top_k, unsigned long long seed,
-              const int* __restrict__ streams, const int* __restrict__ draws,
-              const int* __restrict__ active, const int* __restrict__ dyn) {
+sample_kernel(int* __restrict__ out_token, const float* logits, long long row_stride, int vocab,
+              float temperature, int top_k, unsigned long long seed, const int* streams,
+              const int* draws, const int* active, const int* dyn) {
   __shared__ Best scratch[33];
   __shared__ unsigned int hist[256];
   __shared__ unsigned int sel_prefix, sel_remaining;
+  pdl_launch_dependents();
+  pdl_wait();
   const int row = blockIdx.x, tid = threadIdx.x;
   if (active && active[row] < 0) return;
   if (dyn) {
@@ -147,11 +148,12 @@ sample_kernel(int* __restrict__ out_token, const float* __restrict__ logits, lon
 // associative, so the result equals the one-block kernel's.
 __global__ void __launch_bounds__(256)
 sample_partial_kernel(float* __restrict__ part_score, int* __restrict__ part_index,
-                      const float* __restrict__ logits, long long row_stride, int vocab,
-                      int segments, float temperature, unsigned long long seed,
-                      const int* __restrict__ streams, const int* __restrict__ draws,
-                      const int* __restrict__ active, const int* __restrict__ dyn) {
+                      const float* logits, long long row_stride, int vocab, int segments,
+                      float temperature, unsigned long long seed, const int* streams,
+                      const int* draws, const int* active, const int* dyn) {
   __shared__ Best scratch[33];
+  pdl_launch_dependents();
+  pdl_wait();
   const int row = blockIdx.x, seg = blockIdx.y, tid = threadIdx.x;
   if (active && active[row] < 0) return;
   if (dyn) {
@@ -200,9 +202,10 @@ sample_partial_kernel(float* __restrict__ part_score, int* __restrict__ part_ind
   }
 }
 
-__global__ void sample_final_kernel(int* __restrict__ out_token, const float* __restrict__ part_score,
-                                    const int* __restrict__ part_index, int segments,
-                                    const int* __restrict__ active) {
+__global__ void sample_final_kernel(int* __restrict__ out_token, const float* part_score,
+                                    const int* part_index, int segments, const int* active) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int row = blockIdx.x;
   if (active && active[row] < 0) return;
   Best best{-INFINITY, 0x7fffffff};
@@ -218,11 +221,12 @@ __global__ void sample_final_kernel(int* __restrict__ out_token, const float* __
 
 // After sampling: record the token, count the draw, decide whether the sequence goes on.
 // A row whose position is negative is finished: it emits -1 and nothing of it changes.
-__global__ void decode_advance_kernel(const int* __restrict__ sampled, int* __restrict__ token_ids,
-                                      int* __restrict__ positions, int* __restrict__ draws,
-                                      int* __restrict__ remaining, int* __restrict__ out_tokens,
-                                      int* __restrict__ step_index, const int* __restrict__ stop_ids,
+__global__ void decode_advance_kernel(const int* sampled, int* token_ids, int* positions,
+                                      int* draws, int* remaining, int* out_tokens,
+                                      int* step_index, const int* __restrict__ stop_ids,
                                       int n_stop, int batch, int max_steps) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int b = threadIdx.x;
   const int step = *step_index;
   if (b < batch) {
@@ -255,10 +259,9 @@ EK_EXPORT int ek_sample(int* out_token, const float* logits, long long row_strid
                         const int* draws, const int* active, const int* dyn, cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (vocab <= 0 || temperature < 0.f || top_k < 0) return EK_ERR_ARG;
-  ek::sample_kernel<<<rows, ek::kSampleThreads, 0, stream>>>(out_token, logits, row_stride, vocab,
-                                                            temperature, top_k, seed, streams,
-                                                            draws, active, dyn);
-  EK_RETURN_LAUNCH_STATUS();
+  return (int)ek::launch_pdl(ek::sample_kernel, dim3(rows), dim3(ek::kSampleThreads), 0, stream,
+                             out_token, logits, row_stride, vocab, temperature, top_k, seed, streams,
+                             draws, active, dyn);
 }
 
 // Two launches over `segments` pieces of the vocabulary; top-k is not offered here.
@@ -273,14 +276,12 @@ EK_EXPORT int ek_sample_wide(int* out_token, const float* logits, long long row_
       !part_index || rows > 65535)
     return EK_ERR_ARG;
   dim3 grid(rows, segments);
-  ek::sample_partial_kernel<<<grid, 256, 0, stream>>>(part_score, part_index, logits, row_stride,
-                                                     vocab, segments, temperature, seed, streams,
-                                                     draws, active, dyn);
-  cudaError_t e = cudaGetLastError();
+  cudaError_t e = ek::launch_pdl(ek::sample_partial_kernel, grid, dim3(256), 0, stream, part_score,
+                                 part_index, logits, row_stride, vocab, segments, temperature, seed,
+                                 streams, draws, active, dyn);
   if (e != cudaSuccess) return (int)e;
-  ek::sample_final_kernel<<<rows, 32, 0, stream>>>(out_token, part_score, part_index, segments,
-                                                  active);
-  EK_RETURN_LAUNCH_STATUS();
+  return (int)ek::launch_pdl(ek::sample_final_kernel, dim3(rows), dim3(32), 0, stream, out_token,
+                             (const float*)part_score, (const int*)part_index, segments, active);
 }
 
 EK_EXPORT int ek_decode_advance(const int* sampled, int* token_ids, int* positions, int* draws,
@@ -290,8 +291,7 @@ EK_EXPORT int ek_decode_advance(const int* sampled, int* token_ids, int* positio
   if (batch <= 0) return 0;
   if (batch > 1024) return EK_ERR_ARG;
   const int threads = ((batch + 31) / 32) * 32;
-  ek::decode_advance_kernel<<<1, threads, 0, stream>>>(sampled, token_ids, positions, draws,
-                                                      remaining, out_tokens, step_index, stop_ids,
-                                                      n_stop, batch, max_steps);
-  EK_RETURN_LAUNCH_STATUS();
+  return (int)ek::launch_pdl(ek::decode_advance_kernel, dim3(1), dim3(threads), 0, stream, sampled,
+                             token_ids, positions, draws, remaining, out_tokens, step_index,
+                             stop_ids, n_stop, batch, max_steps);
 }

@@ -271,17 +271,21 @@ def gemv_scratch(device):
     return _gemv_scratch[key]
 
 
+GEMV_BLOCKS_PER_SM = 4
+
+
 def _gemv_plan(n_tiles, k, m):
-    """(warps a block, blocks along K): about four blocks an SM, each warp with at least one
-    full batch of loads."""
+    """(warps a block, blocks): a grid that is resident at once (four blocks an SM), each
+    block with at least one full batch of loads for every warp."""
     chunks = max(1, -(-k // 32))
     unroll = 4 if m <= 16 else (2 if m <= 32 else 1)
     warps = max(1, min(8, chunks // unroll))
-    splits = max(1, min(-(-4 * SM_COUNT // n_tiles), chunks // (warps * unroll)))
-    return warps, splits
+    total = n_tiles * chunks
+    blocks = max(1, min(GEMV_BLOCKS_PER_SM * SM_COUNT, total // (warps * unroll)))
+    return warps, blocks
 
 
-def gemv_bf16(out, x, w, epilogue=EPI_BF16, n_rows=None, warps=None, splits=None):
+def gemv_bf16(out, x, w, epilogue=EPI_BF16, n_rows=None, warps=None, blocks=None):
     """out = x . w^T for at most 64 rows of x, bfloat16 in, 32-bit accumulation.
 
     ``epilogue``: EPI_BF16 -> out bfloat16 [M, N]; EPI_F32 -> out float32 [M, N];
@@ -301,14 +305,13 @@ def gemv_bf16(out, x, w, epilogue=EPI_BF16, n_rows=None, warps=None, splits=None
     if epilogue == EPI_SWIGLU:
         _need(n % 2 == 0, "gemv_bf16: SwiGLU needs gate and up rows")
     tiles = -(-n_out // (8 if epilogue == EPI_SWIGLU else 16))
-    plan_warps, plan_splits = _gemv_plan(tiles, k, m)
+    plan_warps, plan_blocks = _gemv_plan(tiles, k, m)
     warps = warps or plan_warps
-    splits = splits or plan_splits
-    partials, tickets = gemv_scratch(x.device) if splits > 1 else (None, None)
+    blocks = blocks or plan_blocks
+    partials, tickets = gemv_scratch(x.device)
     _gemv_bf16(_ptr(out), _ptr(x), _ptr(w), m, n, k, x.stride(0), w.stride(0), out.stride(0),
-               epilogue, warps, splits, _ptr(partials), _ptr(tickets),
-               _GEMV_PARTIAL_FLOATS if partials is not None else 0,
-               _GEMV_TICKETS if tickets is not None else 0, _stream())
+               epilogue, warps, blocks, _ptr(partials), _ptr(tickets), _GEMV_PARTIAL_FLOATS,
+               _GEMV_TICKETS, _stream())
 
 
 # ------------------------------------------------------------------ sampling and decode state

@@ -342,16 +342,16 @@ def test_gemv_bf16_epilogues(m, n, k_):
         k.gemv_bf16(act, x, w, k.EPI_SWIGLU)
         g, u = want[:, :inter], want[:, inter:]
         assert rel(act, g / (1 + torch.exp(-g)) * u) <= 4e-3
-    for warps, splits in ((1, 1), (4, 3), (8, 7), (32, 2), (2, 64)):
+    for warps, blocks in ((1, 1), (4, 3), (8, 7), (32, 2), (2, 64), (8, 592), (3, 37)):
         o = torch.empty(m, n, device=DEV)
-        k.gemv_bf16(o, x, w, k.EPI_F32, warps=warps, splits=splits)
+        k.gemv_bf16(o, x, w, k.EPI_F32, warps=warps, blocks=blocks)
         assert rel(o, want) <= 1e-5
         again = torch.empty(m, n, device=DEV)
-        k.gemv_bf16(again, x, w, k.EPI_F32, warps=warps, splits=splits)
+        k.gemv_bf16(again, x, w, k.EPI_F32, warps=warps, blocks=blocks)
         assert torch.equal(o, again)                       # fixed summation order: bit-stable
         if n % 2 == 0:
             act2 = torch.empty(m, n // 2, dtype=torch.bfloat16, device=DEV)
-            k.gemv_bf16(act2, x, w, k.EPI_SWIGLU, warps=warps, splits=splits)
+            k.gemv_bf16(act2, x, w, k.EPI_SWIGLU, warps=warps, blocks=blocks)
             g, u = want[:, :n // 2], want[:, n // 2:]
             assert rel(act2, g / (1 + torch.exp(-g)) * u) <= 4e-3
     _, tickets = k.gemv_scratch(DEV)
