@@ -1,0 +1,519 @@
+// D = P . Q^T on the 5th-generation tensor cores: bfloat16 operands staged in shared memory
+// by TMA (cp.async.bulk.tensor, 128-byte swizzle), tcgen05.mma issued by one thread with
+// the 32-bit accumulator in tensor memory (TMEM), read back with tcgen05.ld for the
+// epilogue.  P [rows_p, K] and Q [rows_q, K] are both K-major (rows contiguous in K).
+//
+// One block computes one 128 x BN tile of D over a range of K:
+//   warp 0, one thread : TMA producer - fills a ring of STAGES (P tile, Q tile) pairs
+//   warp 1, one thread : issues 4 tcgen05.mma (K = 16 each) per stage, commits to the
+//                        stage's "empty" barrier, and finally to the accumulator barrier
+//   all 4 warps        : epilogue - each warp reads its 32 TMEM lanes (rows of the tile)
+// Two uses:
+//   * swapped (decode, 17..64 sequences): P = the weight matrix, Q = the activations, so
+//     the 128-row side of the MMA is filled with weight rows and the batch is the narrow
+//     N side; the tile is out^T and is stored transposed.  The work is bound by streaming
+//     the weights, so K is also split over blocks (grid.y); partial tiles go to scratch
+//     and the block that delivers the last partial of a tile adds them in split order.
+//   * direct (prompts): P = activations, Q = weights, BN = 128 or 256.
+// Epilogues: bfloat16, 32-bit, or SwiGLU (the tile holds gate rows/columns in its first
+// half and the matching up rows/columns in its second half).
+// The reference calls cuBLAS for these products (engine/ek_model.py:203,209,298,311) and
+// has no Blackwell path.  Every barrier wait is bounded: on a timeout the kernel records a
+// code in `status`, lets in-flight copies land, frees its TMEM and returns.
+#include <cuda.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "common.cuh"
+
+namespace ek {
+
+enum { TC_EPI_BF16 = 0, TC_EPI_F32 = 1, TC_EPI_SWIGLU = 2 };
+
+constexpr int kTcBM = 128;                    // rows of P per tile (TMEM lanes)
+constexpr int kTcBK = 64;                     // K per stage: one 128-byte swizzle row
+constexpr uint32_t kWaitLimit = 1u << 22;     // try_wait rounds before giving up (~1 s)
+
+// ---------------------------------------------------------------------------- PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok;
+}
+// Bounded wait: false (and a code in *status) if the phase never completes.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status, int code) {
+  for (uint32_t i = 0; i < kWaitLimit; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (i > 64) __nanosleep(128);
+  }
+  atomicCAS(status, 0, code);
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1,
+                                            uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem),
+               "r"(cols) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols)
+               : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t desc_a, uint64_t desc_b,
+                                       uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+      ::"r"(d_tmem), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+}
+// 16 consecutive 32-bit columns of this thread's TMEM lane
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float v[16]) {
+  uint32_t r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15},"
+      " [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr) : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes (64 bfloat16)
+// with the 128-byte swizzle TMA wrote: 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t smem_desc_k_sw128(uint32_t addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr & 0x3FFFF) >> 4);            // start address, 16-byte units
+  d |= (uint64_t)1 << 16;                            // leading byte offset (unused with swizzle)
+  d |= (uint64_t)(1024 >> 4) << 32;                  // stride byte offset between 8-row groups
+  d |= (uint64_t)1 << 46;                            // descriptor version of sm_100
+  d |= (uint64_t)2 << 61;                            // SWIZZLE_128B
+  return d;
+}
+// Instruction descriptor: bfloat16 x bfloat16 -> float, both operands K-major, M = 128.
+__host__ __device__ constexpr uint32_t tc_idesc(int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(kTcBM >> 4) << 24);
+}
+
+struct TcParams {
+  void* out;            // [M_out, N_out] row-major, ldo elements between rows
+  int ldo;
+  int rows_p;           // valid rows of P (tile rows beyond it are not stored)
+  int rows_q;           // valid rows of Q
+  int k_blocks;         // ceil(K / 64)
+  int k_blocks_per_split;
+  int swiglu_half;      // SwiGLU: second-half row offset in the weight matrix (I)
+  float* partials;      // split-K scratch [tile][split][BN][128]
+  unsigned int* tickets;
+  int* status;          // 0, or the code of the first wait that timed out
+};
+
+// --------------------------------------------------------------------------------- kernel
+template <int BN, int EPI, bool SWAP, int STAGES>
+__global__ void __launch_bounds__(128, 1)
+gemm_tc_bf16_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q,
+                    const TcParams prm) {
+  constexpr uint32_t kBytesP = kTcBM * kTcBK * 2;
+  constexpr uint32_t kBytesQ = BN * kTcBK * 2;
+  constexpr uint32_t kTmemCols = BN < 32 ? 32 : BN;
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  // 1024-byte alignment is needed by the 128-byte swizzle
+  unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  unsigned char* p_tiles = smem;
+  unsigned char* q_tiles = smem + STAGES * kBytesP;
+  uint64_t* bars = (uint64_t*)(q_tiles + STAGES * kBytesQ);   // full[STAGES], empty[STAGES], accum
+  uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES + 1);
+  __shared__ int is_last;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int tile_p = blockIdx.x;               // 128-row tile of P
+  const int tile_q = SWAP ? 0 : blockIdx.z;    // BN-row tile of Q (direct use only)
+  const int split = blockIdx.y, n_split = gridDim.y;
+  const int kb_begin = split * prm.k_blocks_per_split;
+  const int kb_end = min(prm.k_blocks, kb_begin + prm.k_blocks_per_split);
+  const int n_iter = kb_end - kb_begin;
+
+  pdl_launch_dependents();
+  const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES),
+                 accum_bar = smem_u32(bars + 2 * STAGES);
+  if (tid == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full0 + 8 * s, 1);
+      mbar_init(empty0 + 8 * s, 1);
+    }
+    mbar_init(accum_bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 0) tmem_alloc(smem_u32(tmem_slot), kTmemCols);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  pdl_wait();
+
+  bool ok = true;
+  if (tid == 0) {
+    // ---------------------------------------------------------------- TMA producer
+    int p_row0, p_row1 = 0;
+    if (EPI == TC_EPI_SWIGLU && SWAP) {        // weights on the P side: 64 gate rows + 64 up rows
+      p_row0 = tile_p * 64;
+      p_row1 = prm.swiglu_half + tile_p * 64;
+    } else {
+      p_row0 = tile_p * kTcBM;
+    }
+    int q_row0, q_row1 = 0;
+    if (EPI == TC_EPI_SWIGLU && !SWAP) {       // weights on the Q side: BN/2 gate + BN/2 up rows
+      q_row0 = tile_q * (BN / 2);
+      q_row1 = prm.swiglu_half + tile_q * (BN / 2);
+    } else {
+      q_row0 = tile_q * BN;
+    }
+    for (int it = 0; it < n_iter && ok; ++it) {
+      const int s = it % STAGES;
+      const uint32_t phase = (it / STAGES) & 1;
+      ok = mbar_wait(empty0 + 8 * s, phase ^ 1, prm.status, 1);
+      if (!ok) break;
+      const int k0 = (kb_begin + it) * kTcBK;
+      const uint32_t full = full0 + 8 * s;
+      mbar_expect_tx(full, kBytesP + kBytesQ);
+      const uint32_t pd = smem_u32(p_tiles + s * kBytesP), qd = smem_u32(q_tiles + s * kBytesQ);
+      if (EPI == TC_EPI_SWIGLU && SWAP) {
+        tma_load_2d(pd, &map_p, k0, p_row0, full);
+        tma_load_2d(pd + kBytesP / 2, &map_p, k0, p_row1, full);
+      } else {
+        tma_load_2d(pd, &map_p, k0, p_row0, full);
+      }
+      if (EPI == TC_EPI_SWIGLU && !SWAP) {
+        tma_load_2d(qd, &map_q, k0, q_row0, full);
+        tma_load_2d(qd + kBytesQ / 2, &map_q, k0, q_row1, full);
+      } else {
+        tma_load_2d(qd, &map_q, k0, q_row0, full);
+      }
+    }
+  } else if (tid == 32) {
+    // ---------------------------------------------------------------- MMA issuer
+    constexpr uint32_t idesc = tc_idesc(BN);
+    for (int it = 0; it < n_iter && ok; ++it) {
+      const int s = it % STAGES;
+      const uint32_t phase = (it / STAGES) & 1;
+      ok = mbar_wait(full0 + 8 * s, phase, prm.status, 2);
+      if (!ok) break;
+      tc_fence_after();
+      const uint64_t da = smem_desc_k_sw128(smem_u32(p_tiles + s * kBytesP));
+      const uint64_t db = smem_desc_k_sw128(smem_u32(q_tiles + s * kBytesQ));
+#pragma unroll
+      for (int k = 0; k < kTcBK / 16; ++k)       // 32 bytes further along K inside the swizzle row
+        tc_mma(tmem_base, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, (it | k) ? 1u : 0u);
+      tc_commit(empty0 + 8 * s);               // the stage is free once these MMAs have read it
+    }
+    tc_commit(accum_bar);                      // all MMAs done: the accumulator is complete
+  }
+
+  // -------------------------------------------------------------------- epilogue (all warps)
+  __syncwarp();
+  bool acc_ok = n_iter > 0 ? mbar_wait(accum_bar, 0, prm.status, 3) : true;
+  tc_fence_after();
+  // a failure anywhere in the block is everybody's failure
+  const int failed = __syncthreads_or((ok && acc_ok) ? 0 : 1);
+
+  const int row = warp * 32 + lane;            // row of the tile = TMEM lane
+  const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
+  const int tile_linear = SWAP ? tile_p : (tile_q * gridDim.x + tile_p);
+
+  if (!failed) {
+    if (n_split > 1) {
+      // partial tile -> scratch [tile][split][BN][128] (coalesced over rows)
+      float* mine = prm.partials + ((size_t)tile_linear * n_split + split) * BN * kTcBM;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 16) {
+        float v[16];
+        if (n_iter > 0) {
+          tmem_ld16(lane_addr + c0, v);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) v[i] = 0.f;
+        }
+#pragma unroll
+        for (int i = 0; i < 16; ++i) mine[(size_t)(c0 + i) * kTcBM + row] = v[i];
+      }
+      __threadfence();
+      __syncthreads();
+      if (tid == 0) {
+        const unsigned int ticket = atomicAdd(&prm.tickets[tile_linear], 1u);
+        is_last = ticket == (unsigned int)(n_split - 1);
+        if (is_last) prm.tickets[tile_linear] = 0;
+      }
+      __syncthreads();
+    }
+    if (n_split == 1 || is_last) {
+      if (n_split > 1) __threadfence();
+      const float* all = prm.partials + (size_t)tile_linear * n_split * BN * kTcBM;
+      float* xch = (float*)smem;               // SwiGLU exchange buffer (operand tiles are dead)
+      constexpr int kCols = (EPI == TC_EPI_SWIGLU && !SWAP) ? BN / 2 : BN;
+#pragma unroll 1
+      for (int c0 = 0; c0 < kCols; c0 += 16) {
+        float v[16], u[16];
+        auto fetch = [&](int col, float dst[16]) {
+          if (n_split == 1) {
+            tmem_ld16(lane_addr + col, dst);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) dst[i] = 0.f;
+            for (int sp = 0; sp < n_split; ++sp)
+#pragma unroll
+              for (int i = 0; i < 16; ++i)
+                dst[i] += __ldcg(&all[((size_t)sp * BN + col + i) * kTcBM + row]);
+          }
+        };
+        fetch(c0, v);
+        if (EPI == TC_EPI_SWIGLU && !SWAP) {
+          fetch(c0 + BN / 2, u);               // the matching up columns
+#pragma unroll
+          for (int i = 0; i < 16; ++i) v[i] = v[i] / (1.f + __expf(-v[i])) * u[i];
+        }
+        if (EPI == TC_EPI_SWIGLU && SWAP) {
+          // rows 64..127 hold the up rows of the gate rows 0..63: pass them through shared memory
+          __syncthreads();
+          if (row >= 64) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) xch[(row - 64) * 16 + i] = v[i];
+          }
+          __syncthreads();
+          if (row < 64) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) v[i] = v[i] / (1.f + __expf(-v[i])) * xch[row * 16 + i];
+          }
+        }
+        if (SWAP) {
+          // tile row = output column (weight row), tile column = output row (sequence)
+          int n_out;
+          bool row_ok;
+          if (EPI == TC_EPI_SWIGLU) {
+            n_out = tile_p * 64 + row;
+            row_ok = row < 64 && n_out < prm.swiglu_half;
+          } else {
+            n_out = tile_p * kTcBM + row;
+            row_ok = n_out < prm.rows_p;
+          }
+          if (row_ok) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const int m = c0 + i;
+              if (m < prm.rows_q) {
+                if (EPI == TC_EPI_F32) ((float*)prm.out)[(size_t)m * prm.ldo + n_out] = v[i];
+                else ((bf16*)prm.out)[(size_t)m * prm.ldo + n_out] = __float2bfloat16_rn(v[i]);
+              }
+            }
+          }
+        } else {
+          const int m = tile_p * kTcBM + row;
+          const int n0 = tile_q * kCols + c0;
+          const int n_limit = EPI == TC_EPI_SWIGLU ? prm.swiglu_half : prm.rows_q;
+          if (m < prm.rows_p) {
+            if (EPI == TC_EPI_F32) {
+              float* o = (float*)prm.out + (size_t)m * prm.ldo + n0;
+#pragma unroll
+              for (int i = 0; i < 16; ++i)
+                if (n0 + i < n_limit) o[i] = v[i];
+            } else {
+              bf16* o = (bf16*)prm.out + (size_t)m * prm.ldo + n0;
+              if (n0 + 16 <= n_limit && (prm.ldo % 8) == 0) {
+                uint32_t w[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                  __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+                  w[i] = *reinterpret_cast<uint32_t*>(&h);
+                }
+                *reinterpret_cast<uint4*>(o) = make_uint4(w[0], w[1], w[2], w[3]);
+                *reinterpret_cast<uint4*>(o + 8) = make_uint4(w[4], w[5], w[6], w[7]);
+              } else {
+#pragma unroll
+                for (int i = 0; i < 16; ++i)
+                  if (n0 + i < n_limit) o[i] = __float2bfloat16_rn(v[i]);
+              }
+            }
+          }
+        }
+      }
+    }
+  } else {
+    // let copies that are still in flight land before the shared memory is given up
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem_base, kTmemCols);
+}
+
+// ------------------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  });
+  return fn;
+}
+
+struct MapKey {
+  const void* ptr; long long rows, k, ld; int box_rows;
+  bool operator==(const MapKey& o) const {
+    return ptr == o.ptr && rows == o.rows && k == o.k && ld == o.ld && box_rows == o.box_rows;
+  }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& m) const {
+    size_t h = (size_t)m.ptr;
+    h = h * 1000003u ^ (size_t)m.rows;
+    h = h * 1000003u ^ (size_t)m.k;
+    h = h * 1000003u ^ (size_t)m.ld;
+    return h * 1000003u ^ (size_t)m.box_rows;
+  }
+};
+
+// Tensor map of a K-major bfloat16 matrix [rows, k] with `ld` elements between rows; boxes of
+// 64 columns x box_rows rows, 128-byte swizzle, zeros outside the matrix.
+static int tensor_map(const void* ptr, long long rows, long long k, long long ld, int box_rows,
+                      CUtensorMap* out) {
+  static std::mutex mu;
+  static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+  const MapKey key{ptr, rows, k, ld, box_rows};
+  std::lock_guard<std::mutex> lock(mu);
+  auto it = cache.find(key);
+  if (it != cache.end()) { *out = it->second; return 0; }
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return (int)cudaErrorNotSupported;
+  const cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  const cuuint32_t box[2] = {(cuuint32_t)kTcBK, (cuuint32_t)box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  CUtensorMap m;
+  const CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides,
+                        box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return EK_ERR_ARG;
+  if (cache.size() > 8192) cache.clear();
+  cache.emplace(key, m);
+  *out = m;
+  return 0;
+}
+
+template <int BN, int EPI, bool SWAP>
+static int launch_tc(const CUtensorMap& mp, const CUtensorMap& mq, const TcParams& prm, dim3 grid,
+                     cudaStream_t stream) {
+  constexpr int STAGES = BN <= 64 ? 8 : (BN <= 128 ? 6 : 4);
+  constexpr size_t smem = 1024 + (size_t)STAGES * (kTcBM * kTcBK * 2 + BN * kTcBK * 2) +
+                          (2 * STAGES + 1) * 8 + 16;
+  auto kernel = gemm_tc_bf16_kernel<BN, EPI, SWAP, STAGES>;
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return (int)e;
+  return (int)launch_pdl(kernel, grid, dim3(128), smem, stream, mp, mq, prm);
+}
+
+}  // namespace ek
+
+// out[M, N] = x[M, K] . w[N, K]^T  (epilogue 0/1) or out[M, N/2] = silu(x.wg^T) * (x.wu^T) with w =
+// [gate rows; up rows] (epilogue 2).  swap != 0: weights fill the 128-row MMA side (for
+// 1..64 rows of x); k_split blocks share a tile's K and need `partials` (at least
+// tiles * k_split * bn * 128 floats) and zeroed `tickets` (at least `tiles`).
+// K, ldx, ldw must be multiples of 8; `status` is one int on the device.
+EK_EXPORT int ek_gemm_tc_bf16(void* out, const void* x, const void* w, int M, int N, int K, int ldx,
+                              int ldw, int ldo, int epilogue, int swap, int k_split,
+                              float* partials, unsigned int* tickets, long long partial_floats,
+                              int n_tickets, int* status, cudaStream_t stream) {
+  using namespace ek;
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0 || K % 8 || ldx % 8 || ldw % 8 || !status || epilogue < 0 || epilogue > 2 ||
+      (epilogue == TC_EPI_SWIGLU && (N & 1)) || ((uintptr_t)x & 15) || ((uintptr_t)w & 15))
+    return EK_ERR_ARG;
+  const int k_blocks = (K + kTcBK - 1) / kTcBK;
+  TcParams prm{};
+  prm.out = out; prm.ldo = ldo; prm.k_blocks = k_blocks; prm.status = status;
+  prm.partials = partials; prm.tickets = tickets;
+  prm.swiglu_half = N / 2;
+  if (k_split < 1) k_split = 1;
+  if (k_split > k_blocks) k_split = k_blocks;
+  CUtensorMap mp, mq;
+  int rc;
+  if (swap) {
+    if (M > 64) return EK_ERR_ARG;
+    const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
+    const bool sw = epilogue == TC_EPI_SWIGLU;
+    const int tiles = sw ? (N / 2 + 63) / 64 : (N + kTcBM - 1) / kTcBM;
+    if (k_split > 1 && (!partials || !tickets || tiles > n_tickets ||
+                        (long long)tiles * k_split * bn * kTcBM > partial_floats))
+      k_split = 1;
+    prm.k_blocks_per_split = (k_blocks + k_split - 1) / k_split;
+    k_split = (k_blocks + prm.k_blocks_per_split - 1) / prm.k_blocks_per_split;
+    prm.rows_p = N; prm.rows_q = M;
+    if ((rc = tensor_map(w, N, K, ldw, sw ? 64 : kTcBM, &mp))) return rc;
+    if ((rc = tensor_map(x, M, K, ldx, bn, &mq))) return rc;
+    dim3 grid(tiles, k_split, 1);
+#define EK_SWAP(BN)                                                                              \
+  if (bn == BN) {                                                                                \
+    if (epilogue == TC_EPI_BF16) return launch_tc<BN, TC_EPI_BF16, true>(mp, mq, prm, grid, stream); \
+    if (epilogue == TC_EPI_F32) return launch_tc<BN, TC_EPI_F32, true>(mp, mq, prm, grid, stream);   \
+    return launch_tc<BN, TC_EPI_SWIGLU, true>(mp, mq, prm, grid, stream);                        \
+  }
+    EK_SWAP(16) EK_SWAP(32) EK_SWAP(64)
+#undef EK_SWAP
+    return EK_ERR_ARG;
+  }
+  // direct: P = x (128-row tiles), Q = w (BN-row tiles); no K split
+  prm.k_blocks_per_split = k_blocks;
+  prm.rows_p = M; prm.rows_q = N;
+  const bool sw = epilogue == TC_EPI_SWIGLU;
+  constexpr int BN = 128;
+  const int tiles_q = sw ? (N / 2 + BN / 2 - 1) / (BN / 2) : (N + BN - 1) / BN;
+  if (tiles_q > 65535) return EK_ERR_ARG;
+  if ((rc = tensor_map(x, M, K, ldx, kTcBM, &mp))) return rc;
+  if ((rc = tensor_map(w, N, K, ldw, sw ? BN / 2 : BN, &mq))) return rc;
+  dim3 grid((M + kTcBM - 1) / kTcBM, 1, tiles_q);
+  if (epilogue == TC_EPI_BF16) return launch_tc<BN, TC_EPI_BF16, false>(mp, mq, prm, grid, stream);
+  if (epilogue == TC_EPI_F32) return launch_tc<BN, TC_EPI_F32, false>(mp, mq, prm, grid, stream);
+  return launch_tc<BN, TC_EPI_SWIGLU, false>(mp, mq, prm, grid, stream);
+}

@@ -314,6 +314,62 @@ def gemv_bf16(out, x, w, epilogue=EPI_BF16, n_rows=None, warps=None, blocks=None
                _GEMV_TICKETS, _stream())
 
 
+_gemm_tc = Function("gemm_tc_bf16", "ek_gemm_tc_bf16",
+                    [_P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P,
+                     c_longlong, c_int, _P, _P])
+_tc_status = {}
+TC_SWAP_MAX_ROWS = 64
+
+
+def tc_status(device):
+    """One int per device that the tensor-core GEMM sets when a barrier wait times out."""
+    key = str(torch.device(device))
+    if key not in _tc_status:
+        _tc_status[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _tc_status[key]
+
+
+def check_tc_status(device):
+    """Synchronises; raises if a tensor-core GEMM gave up waiting (1 producer, 2 MMA, 3 epilogue)."""
+    code = int(tc_status(device).item())
+    if code:
+        tc_status(device).zero_()
+        raise KernelError(f"gemm_tc_bf16: a barrier wait timed out (code {code}); results are invalid")
+
+
+def gemm_tc_bf16(out, x, w, epilogue=EPI_BF16, n_rows=None, swap=None, k_split=None):
+    """out = x . w^T (or the SwiGLU of it) on tcgen05 tensor cores with TMA-staged operands.
+
+    ``swap`` (default: at most 64 rows) puts the weights on the 128-row side of the MMA and
+    splits K over ``k_split`` blocks; otherwise 128 x 128 tiles of the output.
+    """
+    _need_cuda(out, x, w)
+    m = n_rows if n_rows is not None else x.shape[0]
+    n, k = w.shape
+    _need(x.dtype == w.dtype == torch.bfloat16, "gemm_tc_bf16: bfloat16 operands")
+    _need(k % 8 == 0 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0,
+          f"gemm_tc_bf16: inner size {k} and row strides must be multiples of 8")
+    _need(x.stride(-1) == 1 and w.stride(-1) == 1 and out.stride(-1) == 1 and x.shape[-1] == k,
+          "gemm_tc_bf16: dense rows of matching inner size")
+    _need(x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0, "gemm_tc_bf16: 16-byte aligned operands")
+    n_out = n // 2 if epilogue == EPI_SWIGLU else n
+    _need(out.shape[-1] == n_out and out.shape[0] >= m, "gemm_tc_bf16: out shape")
+    _need(out.dtype == (torch.float32 if epilogue == EPI_F32 else torch.bfloat16), "gemm_tc_bf16: out dtype")
+    if swap is None:
+        swap = m <= TC_SWAP_MAX_ROWS
+    _need(not swap or m <= TC_SWAP_MAX_ROWS, "gemm_tc_bf16: the swapped form takes at most 64 rows")
+    partials, tickets = gemv_scratch(x.device)
+    if k_split is None:
+        k_split = 1
+        if swap:
+            tiles = -(-n_out // (64 if epilogue == EPI_SWIGLU else 128))
+            k_blocks = -(-k // 64)
+            k_split = max(1, min(-(-SM_COUNT // tiles), k_blocks // 8))
+    _gemm_tc(_ptr(out), _ptr(x), _ptr(w), m, n, k, x.stride(0), w.stride(0), out.stride(0),
+             epilogue, 1 if swap else 0, k_split, _ptr(partials), _ptr(tickets),
+             _GEMV_PARTIAL_FLOATS, _GEMV_TICKETS, _ptr(tc_status(x.device)), _stream())
+
+
 # ------------------------------------------------------------------ sampling and decode state
 _sample = Function("sampling", "ek_sample",
                    [_P, _P, c_longlong, c_int, c_int, c_float, c_int, c_ulonglong, _P, _P, _P, _P, _P])

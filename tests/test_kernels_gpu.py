@@ -358,6 +358,55 @@ def test_gemv_bf16_epilogues(m, n, k_):
     assert int(tickets.abs().sum()) == 0                   # every launch leaves the tickets zero
 
 
+@pytest.mark.parametrize("m,n,k_", [(17, 256, 128), (64, 2560, 4096), (33, 1000, 1000), (1, 128, 64),
+                                    (48, 331 * 2, 80), (64, 6144, 2560)])
+def test_gemm_tc_swapped(m, n, k_):
+    """tcgen05 + TMA product with the weights on the 128-row side (decode with many sequences)."""
+    k = K()
+    x = rnd(m, k_, dtype=torch.bfloat16, seed=1)
+    w = rnd(n, k_, dtype=torch.bfloat16, seed=2, scale=0.05)
+    want = x.double() @ w.double().t()
+    for k_split in (1, 3, None):
+        out32 = torch.full((m, n), 9.0, device=DEV)
+        k.gemm_tc_bf16(out32, x, w, k.EPI_F32, swap=True, k_split=k_split)
+        k.check_tc_status(DEV)
+        assert rel(out32, want) <= 1e-5, k_split
+        out16 = torch.empty(m, n, dtype=torch.bfloat16, device=DEV)
+        k.gemm_tc_bf16(out16, x, w, k.EPI_BF16, swap=True, k_split=k_split)
+        assert rel(out16, want) <= 4e-3
+        inter = n // 2
+        act = torch.empty(m, inter, dtype=torch.bfloat16, device=DEV)
+        k.gemm_tc_bf16(act, x, w, k.EPI_SWIGLU, swap=True, k_split=k_split)
+        g, u = want[:, :inter], want[:, inter:]
+        assert rel(act, g / (1 + torch.exp(-g)) * u) <= 4e-3
+    k.check_tc_status(DEV)
+    _, tickets = k.gemv_scratch(DEV)
+    assert int(tickets.abs().sum()) == 0
+
+
+@pytest.mark.parametrize("m,n,k_", [(128, 128, 64), (2048, 2560, 4096), (300, 1000, 1000), (65, 662, 80),
+                                    (517, 6144, 2560)])
+def test_gemm_tc_direct(m, n, k_):
+    """tcgen05 + TMA product in 128 x 128 output tiles (prompts), edges not multiples of a tile."""
+    k = K()
+    x = rnd(m, k_, dtype=torch.bfloat16, seed=3)
+    w = rnd(n, k_, dtype=torch.bfloat16, seed=4, scale=0.05)
+    want = x.double() @ w.double().t()
+    out32 = torch.full((m, n), 9.0, device=DEV)
+    k.gemm_tc_bf16(out32, x, w, k.EPI_F32, swap=False)
+    k.check_tc_status(DEV)
+    assert rel(out32, want) <= 1e-5
+    out16 = torch.empty(m, n, dtype=torch.bfloat16, device=DEV)
+    k.gemm_tc_bf16(out16, x, w, k.EPI_BF16, swap=False)
+    assert rel(out16, want) <= 4e-3
+    inter = n // 2
+    act = torch.empty(m, inter, dtype=torch.bfloat16, device=DEV)
+    k.gemm_tc_bf16(act, x, w, k.EPI_SWIGLU, swap=False)
+    g, u = want[:, :inter], want[:, inter:]
+    assert rel(act, g / (1 + torch.exp(-g)) * u) <= 4e-3
+    k.check_tc_status(DEV)
+
+
 def test_gemv_refuses_what_it_cannot_do():
     k = K()
     from enginekernel_b200.ops.lib import KernelError
