@@ -80,8 +80,15 @@ attention_decode_bf16_kernel(bf16* __restrict__ out, const bf16* q, int q_row_st
     lo = window > 0 ? max(0, pos - window + 1) : 0;
     hi = pos;
     if (n_splits > 1) {
-      lo = max(lo, split * keys_per_split);
-      hi = min(hi, (split + 1) * keys_per_split - 1);
+      if (keys_per_split > 0) {                // fixed cut of the key axis
+        lo = max(lo, split * keys_per_split);
+        hi = min(hi, (split + 1) * keys_per_split - 1);
+      } else {                                 // cut this token's visible keys evenly
+        const int first = lo & ~(kUnit - 1);
+        const int per = max(kUnit, (((hi - first + n_splits) / n_splits) + kUnit - 1) & ~(kUnit - 1));
+        lo = max(lo, first + split * per);
+        hi = min(hi, first + (split + 1) * per - 1);
+      }
     }
   }
 
@@ -288,7 +295,8 @@ static int launch_dch(bf16* out, const bf16* q, int q_row_stride, const int* pos
 
 }  // namespace ek
 
-// head_dim must be a multiple of 32 (up to 256); keys_per_split a multiple of 16.
+// head_dim must be a multiple of 32 (up to 256); keys_per_split a multiple of 16, or 0 to cut
+// each token's visible keys into n_splits equal parts.
 EK_EXPORT int ek_attention_decode_bf16(void* out, const void* q, int q_row_stride,
                                        const int* positions, const int* token_slot,
                                        const void* k_pages, const void* v_pages,
@@ -300,7 +308,7 @@ EK_EXPORT int ek_attention_decode_bf16(void* out, const void* q, int q_row_strid
   if (n_tokens <= 0) return 0;
   if (head_dim % 32 || head_dim < 32 || head_dim > 256 || n_kv_heads <= 0 ||
       n_q_heads % n_kv_heads || n_splits < 1 || n_splits > 65535 || q_row_stride % 8 ||
-      (n_splits > 1 && (!part_acc || !part_ml || keys_per_split <= 0 || keys_per_split % kUnit)))
+      (n_splits > 1 && (!part_acc || !part_ml || keys_per_split < 0 || keys_per_split % kUnit)))
     return EK_ERR_ARG;
   PagedKV cache{(void*)k_pages, (void*)v_pages, block_table, table_stride, n_kv_heads, head_dim};
 #define EK_CASE(DCH)                                                                              \

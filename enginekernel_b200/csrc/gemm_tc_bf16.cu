@@ -34,6 +34,7 @@ enum { TC_EPI_BF16 = 0, TC_EPI_F32 = 1, TC_EPI_SWIGLU = 2 };
 constexpr int kTcBM = 128;                    // rows of P per tile (TMEM lanes)
 constexpr int kTcBK = 64;                     // K per stage: one 128-byte swizzle row
 constexpr uint32_t kWaitLimit = 1u << 22;     // try_wait rounds before giving up (~1 s)
+constexpr int kMaxDevices = 64;
 
 // ---------------------------------------------------------------------------- PTX wrappers
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -144,7 +145,7 @@ struct TcParams {
 
 // --------------------------------------------------------------------------------- kernel
 template <int BN, int EPI, bool SWAP, int STAGES>
-__global__ void __launch_bounds__(128, 1)
+__global__ void __launch_bounds__(128, SWAP ? 2 : 1)
 gemm_tc_bf16_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q,
                     const TcParams prm) {
   constexpr uint32_t kBytesP = kTcBM * kTcBK * 2;
@@ -183,7 +184,6 @@ gemm_tc_bf16_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  pdl_wait();
 
   bool ok = true;
   if (tid == 0) {
@@ -202,27 +202,39 @@ gemm_tc_bf16_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
     } else {
       q_row0 = tile_q * BN;
     }
-    for (int it = 0; it < n_iter && ok; ++it) {
+    auto load_p = [&](int it) {
+      const int s = it % STAGES;
+      const uint32_t full = full0 + 8 * s, pd = smem_u32(p_tiles + s * kBytesP);
+      const int k0 = (kb_begin + it) * kTcBK;
+      tma_load_2d(pd, &map_p, k0, p_row0, full);
+      if (EPI == TC_EPI_SWIGLU && SWAP) tma_load_2d(pd + kBytesP / 2, &map_p, k0, p_row1, full);
+    };
+    auto load_q = [&](int it) {
+      const int s = it % STAGES;
+      const uint32_t full = full0 + 8 * s, qd = smem_u32(q_tiles + s * kBytesQ);
+      const int k0 = (kb_begin + it) * kTcBK;
+      tma_load_2d(qd, &map_q, k0, q_row0, full);
+      if (EPI == TC_EPI_SWIGLU && !SWAP) tma_load_2d(qd + kBytesQ / 2, &map_q, k0, q_row1, full);
+    };
+    // The weight operand does not depend on the kernel before this one: the first ring of
+    // weight tiles is requested before waiting for that kernel, the activations after.
+    const int first = min(n_iter, STAGES);
+    for (int it = 0; it < first; ++it) {
+      mbar_expect_tx(full0 + 8 * (it % STAGES), kBytesP + kBytesQ);
+      if (SWAP) load_p(it); else load_q(it);
+    }
+    pdl_wait();
+    for (int it = 0; it < first; ++it) {
+      if (SWAP) load_q(it); else load_p(it);
+    }
+    for (int it = first; it < n_iter; ++it) {
       const int s = it % STAGES;
       const uint32_t phase = (it / STAGES) & 1;
       ok = mbar_wait(empty0 + 8 * s, phase ^ 1, prm.status, 1);
       if (!ok) break;
-      const int k0 = (kb_begin + it) * kTcBK;
-      const uint32_t full = full0 + 8 * s;
-      mbar_expect_tx(full, kBytesP + kBytesQ);
-      const uint32_t pd = smem_u32(p_tiles + s * kBytesP), qd = smem_u32(q_tiles + s * kBytesQ);
-      if (EPI == TC_EPI_SWIGLU && SWAP) {
-        tma_load_2d(pd, &map_p, k0, p_row0, full);
-        tma_load_2d(pd + kBytesP / 2, &map_p, k0, p_row1, full);
-      } else {
-        tma_load_2d(pd, &map_p, k0, p_row0, full);
-      }
-      if (EPI == TC_EPI_SWIGLU && !SWAP) {
-        tma_load_2d(qd, &map_q, k0, q_row0, full);
-        tma_load_2d(qd + kBytesQ / 2, &map_q, k0, q_row1, full);
-      } else {
-        tma_load_2d(qd, &map_q, k0, q_row0, full);
-      }
+      mbar_expect_tx(full0 + 8 * s, kBytesP + kBytesQ);
+      load_p(it);
+      load_q(it);
     }
   } else if (tid == 32) {
     // ---------------------------------------------------------------- MMA issuer
@@ -244,6 +256,7 @@ gemm_tc_bf16_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
   }
 
   // -------------------------------------------------------------------- epilogue (all warps)
+  if (tid != 0) pdl_wait();                    // before any global write (thread 0 waited above)
   __syncwarp();
   bool acc_ok = n_iter > 0 ? mbar_wait(accum_bar, 0, prm.status, 3) : true;
   tc_fence_after();
@@ -445,12 +458,21 @@ static int tensor_map(const void* ptr, long long rows, long long k, long long ld
 template <int BN, int EPI, bool SWAP>
 static int launch_tc(const CUtensorMap& mp, const CUtensorMap& mq, const TcParams& prm, dim3 grid,
                      cudaStream_t stream) {
-  constexpr int STAGES = BN <= 64 ? 8 : (BN <= 128 ? 6 : 4);
+  // swapped: two blocks an SM (4 stages each); direct: one block an SM with a deep ring
+  constexpr int STAGES = SWAP ? 4 : (BN <= 128 ? 6 : 4);
   constexpr size_t smem = 1024 + (size_t)STAGES * (kTcBM * kTcBK * 2 + BN * kTcBK * 2) +
                           (2 * STAGES + 1) * 8 + 16;
   auto kernel = gemm_tc_bf16_kernel<BN, EPI, SWAP, STAGES>;
-  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  static bool configured[kMaxDevices] = {};     // the attribute is per device and sticks
+  int device = 0;
+  cudaError_t e = cudaGetDevice(&device);
   if (e != cudaSuccess) return (int)e;
+  if (device < 0 || device >= kMaxDevices) return EK_ERR_ARG;
+  if (!configured[device]) {
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    configured[device] = true;
+  }
   return (int)launch_pdl(kernel, grid, dim3(128), smem, stream, mp, mq, prm);
 }
 

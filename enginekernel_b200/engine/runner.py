@@ -78,7 +78,8 @@ class ModelRunner:
         self._uploaded = None          # event: the last step's host->device copies are done
         if model.dtype == torch.bfloat16:
             from ..ops import kernels
-            kernels.gemv_scratch(self.device)      # exists before any graph capture
+            kernels.gemv_scratch(self.device)      # exist before any graph capture
+            kernels.tc_status(self.device)
         model.prepare(min(cache.max_len, model.spec.max_positions))
 
     def _plan_for(self, n_tokens: int, n_seqs: int) -> PlanBuffers:

@@ -187,7 +187,8 @@ def attention_decode_bf16(out, q, n_tokens, positions, token_slot, k_pages, v_pa
                           n_q_heads, n_kv_heads, head_dim, scale, window=None, n_splits=1,
                           keys_per_split=0, part_acc=None, part_ml=None):
     """One query token per row of ``q`` (bfloat16, head_dim a multiple of 32): same contract
-    as :func:`attention_generic`; ``keys_per_split`` must be a multiple of 16."""
+    as :func:`attention_generic`; ``keys_per_split`` must be a multiple of 16, or 0 to cut
+    every token's own visible keys into ``n_splits`` equal parts."""
     _need_cuda(out, q, positions, token_slot, k_pages, v_pages, block_table, part_acc, part_ml)
     _need(attention_decode_supported(q.dtype, head_dim),
           "attention_decode_bf16: bfloat16 and a head size that is a multiple of 32")
@@ -362,9 +363,11 @@ def gemm_tc_bf16(out, x, w, epilogue=EPI_BF16, n_rows=None, swap=None, k_split=N
     if k_split is None:
         k_split = 1
         if swap:
+            # two blocks fit an SM: fill those 296 places, keep at least 8 K blocks a block, and
+            # split less when the partial tiles are wide
             tiles = -(-n_out // (64 if epilogue == EPI_SWIGLU else 128))
             k_blocks = -(-k // 64)
-            k_split = max(1, min(-(-SM_COUNT // tiles), k_blocks // 8))
+            k_split = max(1, min(2 * SM_COUNT // tiles, k_blocks // 8, 16 if m <= 16 else 4))
     _gemm_tc(_ptr(out), _ptr(x), _ptr(w), m, n, k, x.stride(0), w.stride(0), out.stride(0),
              epilogue, 1 if swap else 0, k_split, _ptr(partials), _ptr(tickets),
              _GEMV_PARTIAL_FLOATS, _GEMV_TICKETS, _ptr(tc_status(x.device)), _stream())

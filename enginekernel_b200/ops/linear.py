@@ -1,7 +1,8 @@
 """y = x . W^T for the engine's two precisions.
 
 * float32: the hand-written FFMA kernel (no tensor-core mode of reduced precision).
-* bfloat16, at most 64 rows (decode): the weight-streaming tensor-core kernel.
+* bfloat16, at most 64 rows (decode): the tcgen05 kernel in its swapped form - weights on the
+  128-row side of the MMA, TMA-streamed, K split over blocks.
 * bfloat16, more rows (prefill): the library product, where the reference also calls a
   library (``torch.matmul`` on cuBLAS, engine/ek_model.py:298,311,203-209).
 """
@@ -11,6 +12,8 @@ from __future__ import annotations
 import torch
 
 from . import kernels
+
+SMALL_ROWS = kernels.TC_SWAP_MAX_ROWS
 
 
 def linear(x, w, ctx, name: str, n_rows=None, out_dtype=None):
@@ -22,16 +25,13 @@ def linear(x, w, ctx, name: str, n_rows=None, out_dtype=None):
         kernels.gemm_f32(out, x, w, n_rows=m)
         return out
     want_f32 = out_dtype == torch.float32
-    if m <= kernels.GEMV_MAX_ROWS:
-        out = ctx.workspace.get(name, (m, n), torch.float32 if want_f32 else torch.bfloat16)
-        kernels.gemv_bf16(out, x, w, kernels.EPI_F32 if want_f32 else kernels.EPI_BF16, n_rows=m)
-        return out
-    if want_f32:
-        out = ctx.workspace.get(name, (m, n), torch.float32)
-        for r0 in range(0, m, kernels.GEMV_MAX_ROWS):
-            r1 = min(m, r0 + kernels.GEMV_MAX_ROWS)
-            kernels.gemv_bf16(out[r0:r1], x[r0:r1], w, kernels.EPI_F32, n_rows=r1 - r0)
-        return out
-    out = ctx.workspace.get(name, (m, n), torch.bfloat16)
-    torch.matmul(x[:m], w.t(), out=out)
+    epi = kernels.EPI_F32 if want_f32 else kernels.EPI_BF16
+    out = ctx.workspace.get(name, (m, n), torch.float32 if want_f32 else torch.bfloat16)
+    if m <= SMALL_ROWS:
+        kernels.gemm_tc_bf16(out, x, w, epi, n_rows=m, swap=True)
+    elif want_f32:
+        # 32-bit logits for many rows: 128 x 128 tiles with the accumulator stored as it is
+        kernels.gemm_tc_bf16(out, x, w, epi, n_rows=m, swap=False)
+    else:
+        torch.matmul(x[:m], w.t(), out=out)
     return out

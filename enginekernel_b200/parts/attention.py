@@ -98,10 +98,15 @@ class Attention(Mixer):
                 self.head_dim, self.scale, self.window)
             return
         if fast_decode:
-            # blocks = tokens x KV heads (x 16-row blocks of the group); split the keys until
-            # about four blocks per SM exist, never finer than one page
+            # blocks = tokens x KV heads (x 16-row blocks of the group); three fit an SM.  Split
+            # the keys so that the blocks just fill the machine once, or about twice when one
+            # filling cannot be approached; never finer than two pages a split.
             blocks = t * self.num_kv_heads * -(-(self.num_heads // self.num_kv_heads) // 16)
-            splits = max(1, min(-(-4 * SM_COUNT // blocks), -(-visible // 64)))
+            resident = 3 * SM_COUNT
+            splits = resident // blocks
+            if blocks * splits < 0.7 * resident:
+                splits = int(1.8 * resident / blocks + 0.5)
+            splits = max(1, min(splits, -(-visible // 128)))
             unit = 64
         else:
             blocks = t * self.num_heads
@@ -110,17 +115,18 @@ class Attention(Mixer):
                 splits = max(1, min(-(-visible // 256), -(-4 * SM_COUNT // blocks), 64))
             unit = 128
         per_split, acc, ml = 0, None, None
-        if splits > 1:
+        if splits > 1 and not fast_decode:      # the decode kernel cuts each token's own range
             per_split = -(-(-(-ctx.max_context // splits)) // unit) * unit
             splits = -(-ctx.max_context // per_split)
         if splits > 1:
             acc = ctx.workspace.get("attn_part_acc", (t, self.num_heads, splits, self.head_dim),
                                     torch.float32)
             ml = ctx.workspace.get("attn_part_ml", (t, self.num_heads, splits, 2), torch.float32)
+        args = (out, qkv, t, ctx.positions, ctx.token_slot, entry.k_pages, entry.v_pages,
+                entry.block_table, self.num_heads, self.num_kv_heads, self.head_dim, self.scale,
+                self.window, splits, per_split, acc, ml)
         fn = kernels.attention_decode_bf16 if fast_decode else kernels.attention_generic
-        fn(out, qkv, t, ctx.positions, ctx.token_slot, entry.k_pages, entry.v_pages,
-           entry.block_table, self.num_heads, self.num_kv_heads, self.head_dim, self.scale,
-           self.window, splits, per_split, acc, ml)
+        fn(*args)
 
 
 _EMPTY = {}

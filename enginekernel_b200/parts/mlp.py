@@ -43,9 +43,10 @@ class GatedMLP(FeedForward):
 
     def forward(self, x, ctx):
         t = ctx.n_tokens
-        if self.dtype == torch.bfloat16 and t <= kernels.GEMV_MAX_ROWS and self.inter % 8 == 0:
+        if self.dtype == torch.bfloat16 and t <= kernels.TC_SWAP_MAX_ROWS:
+            # gate and up rows share a tile, so silu(gate) * up is formed in the epilogue
             act = ctx.workspace.get("mlp_act", (t, self.inter), self.dtype)
-            kernels.gemv_bf16(act, x, self.w_gate_up, kernels.EPI_SWIGLU, n_rows=t)
+            kernels.gemm_tc_bf16(act, x, self.w_gate_up, kernels.EPI_SWIGLU, n_rows=t, swap=True)
         else:
             gu = linear(x, self.w_gate_up, ctx, "mlp_gate_up", n_rows=t)
             act = ctx.workspace.get("mlp_act", (t, self.inter), self.dtype)

@@ -245,7 +245,7 @@ def test_attention_decode_bf16(nq, nkv, d):
     slots = torch.tensor([s for s, _ in toks], dtype=torch.int32, device=DEV)
     scale = 1.0 / math.sqrt(d)
     for window, splits, per in ((None, 1, 0), (None, 5, 128), (None, 9, 64), (100, 1, 0), (64, 3, 192),
-                                (1, 1, 0), (17, 33, 16)):
+                                (1, 1, 0), (17, 33, 16), (None, 6, 0), (100, 4, 0), (None, 48, 0)):
         out = torch.full((t, nq * d), 7.0, dtype=dtype, device=DEV)
         acc = torch.empty(t * nq * max(splits, 1) * d, device=DEV)
         ml = torch.empty(t * nq * max(splits, 1) * 2, device=DEV)
