@@ -23,36 +23,60 @@ __global__ void embed_kernel(float* __restrict__ resid, const T* __restrict__ ta
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) out[i] = to_f<T>(row[i]);
 }
 
+
 // y = gain * x * rsqrt(mean(x^2) + eps) for each row; x is the 32-bit stream.
 // If `add` is given, the stream first becomes stream + add (written back when
 // `write_back`).  If `rows` is given, output row i reads stream row rows[i].
-template <typename T>
+// VEC: the row length is a multiple of 4 and rows are accessed four values at a time.
+template <typename T, bool VEC>
 __global__ void rmsnorm_kernel(T* __restrict__ y, float* resid, const T* add,
                                const float* __restrict__ gain, const int* rows, float eps, int hidden,
                                int write_back) {
   __shared__ float scratch[33];
-  extern __shared__ float row_cache[];          // `hidden` floats
+  extern __shared__ __align__(16) float row_cache[];          // `hidden` floats
   pdl_launch_dependents();
   pdl_wait();
   const int out_row = blockIdx.x;
   const int src_row = rows ? rows[out_row] : out_row;
   float* r = resid + (size_t)src_row * hidden;
   const T* a = add ? add + (size_t)src_row * hidden : nullptr;
+  T* out = y + (size_t)out_row * hidden;
   float ss = 0.f;
-  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
-    float v = r[i];
-    if (a) {
-      v += to_f<T>(a[i]);
-      if (write_back) r[i] = v;
+  if (VEC) {
+    for (int i = threadIdx.x * 4; i < hidden; i += blockDim.x * 4) {
+      float4 v = *reinterpret_cast<const float4*>(r + i);
+      if (a) {
+        const float4 w = Vec4<T>::load(a + i);
+        v.x += w.x; v.y += w.y; v.z += w.z; v.w += w.w;
+        if (write_back) *reinterpret_cast<float4*>(r + i) = v;
+      }
+      *reinterpret_cast<float4*>(row_cache + i) = v;
+      ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
     }
-    row_cache[i] = v;
-    ss += v * v;
+  } else {
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+      float v = r[i];
+      if (a) {
+        v += to_f<T>(a[i]);
+        if (write_back) r[i] = v;
+      }
+      row_cache[i] = v;
+      ss += v * v;
+    }
   }
   const float total = block_sum(ss, scratch);
   const float rstd = rsqrtf(total / (float)hidden + eps);
-  T* out = y + (size_t)out_row * hidden;
-  for (int i = threadIdx.x; i < hidden; i += blockDim.x)
-    out[i] = from_f<T>(row_cache[i] * rstd * gain[i]);
+  if (VEC) {
+    for (int i = threadIdx.x * 4; i < hidden; i += blockDim.x * 4) {
+      const float4 v = *reinterpret_cast<const float4*>(row_cache + i);
+      const float4 g = *reinterpret_cast<const float4*>(gain + i);
+      Vec4<T>::store(out + i, make_float4(v.x * rstd * g.x, v.y * rstd * g.y, v.z * rstd * g.z,
+                                          v.w * rstd * g.w));
+    }
+  } else {
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x)
+      out[i] = from_f<T>(row_cache[i] * rstd * gain[i]);
+  }
 }
 
 // stream += add, without a norm (the last feed-forward output when no norm follows)
@@ -63,15 +87,24 @@ __global__ void add_residual_kernel(float* __restrict__ resid, const T* __restri
 }
 
 // out[r, i] = silu(gu[r, i]) * gu[r, inter + i]    (engine/ek_kernels.py:125-143)
-template <typename T>
+// VEC: inter is a multiple of 4; a thread handles four neighbours.
+template <typename T, bool VEC>
 __global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gu, int inter) {
   const size_t r = blockIdx.y;
-  const int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= inter) return;
-  const float g = to_f<T>(gu[r * 2 * inter + i]);
-  const float u = to_f<T>(gu[r * 2 * inter + inter + i]);
-  const float s = g / (1.f + expf(-g));
-  out[r * inter + i] = from_f<T>(s * u);
+  const T* g_row = gu + r * 2 * inter;
+  T* o_row = out + r * inter;
+  if (VEC) {
+    const int i = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (i >= inter) return;
+    const float4 g = Vec4<T>::load(g_row + i), u = Vec4<T>::load(g_row + inter + i);
+    Vec4<T>::store(o_row + i, make_float4(g.x / (1.f + expf(-g.x)) * u.x, g.y / (1.f + expf(-g.y)) * u.y,
+                                          g.z / (1.f + expf(-g.z)) * u.z, g.w / (1.f + expf(-g.w)) * u.w));
+  } else {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= inter) return;
+    const float g = to_f<T>(g_row[i]), u = to_f<T>(g_row[inter + i]);
+    o_row[i] = from_f<T>(g / (1.f + expf(-g)) * u);
+  }
 }
 
 template <typename T>
@@ -81,14 +114,28 @@ static int launch_rmsnorm(void* y, float* resid, const void* add, const float* g
   if (n_rows <= 0) return 0;
   if (hidden <= 0 || (size_t)hidden * 4 > 200 * 1024) return EK_ERR_ARG;
   const size_t smem = (size_t)hidden * sizeof(float);
+  const bool vec = hidden % 4 == 0 && ((uintptr_t)y % 8) == 0 && ((uintptr_t)add % 8) == 0;
+  auto kernel = vec ? rmsnorm_kernel<T, true> : rmsnorm_kernel<T, false>;
   if (smem > 40 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(rmsnorm_kernel<T>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
-  int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
-  return (int)launch_pdl(rmsnorm_kernel<T>, dim3(n_rows), dim3(threads), smem, stream, (T*)y, resid,
+  const int per_thread = vec ? 4 : 1;
+  int threads = hidden / per_thread >= 512 ? 512 : (hidden / per_thread >= 256 ? 256 : 128);
+  return (int)launch_pdl(kernel, dim3(n_rows), dim3(threads), smem, stream, (T*)y, resid,
                          (const T*)add, gain, rows, eps, hidden, write_back);
+}
+
+template <typename T>
+static int launch_silu_mul(void* out, const void* gu, int rows, int inter, cudaStream_t stream) {
+  if (rows <= 0 || inter <= 0) return 0;
+  if (rows > 65535) return EK_ERR_ARG;
+  const bool vec = inter % 4 == 0 && ((uintptr_t)out % 8) == 0 && ((uintptr_t)gu % 8) == 0;
+  const int per_thread = vec ? 4 : 1;
+  dim3 grid((inter / per_thread + 255) / 256 + (inter % per_thread ? 1 : 0), rows);
+  if (vec) silu_mul_kernel<T, true><<<grid, 256, 0, stream>>>((T*)out, (const T*)gu, inter);
+  else silu_mul_kernel<T, false><<<grid, 256, 0, stream>>>((T*)out, (const T*)gu, inter);
+  EK_RETURN_LAUNCH_STATUS();
 }
 
 }  // namespace ek
@@ -116,11 +163,7 @@ using namespace ek;
   }                                                                                             \
   EK_EXPORT int ek_silu_mul_##SUFFIX(void* out, const void* gu, int rows, int inter,            \
                                      cudaStream_t stream) {                                     \
-    if (rows <= 0 || inter <= 0) return 0;                                                      \
-    if (rows > 65535) return EK_ERR_ARG;                                                        \
-    dim3 grid((inter + 255) / 256, rows);                                                       \
-    silu_mul_kernel<T><<<grid, 256, 0, stream>>>((T*)out, (const T*)gu, inter);                 \
-    EK_RETURN_LAUNCH_STATUS();                                                                  \
+    return launch_silu_mul<T>(out, gu, rows, inter, stream);                                    \
   }
 
 EK_INSTANTIATE(f32, float)

@@ -13,6 +13,7 @@ namespace ek {
 
 constexpr int kRopeWarps = 4;
 
+
 template <typename T>
 __global__ void qk_norm_rope_kv_kernel(T* qkv, int row_stride,
                                        const float* __restrict__ q_gain,
@@ -22,7 +23,7 @@ __global__ void qk_norm_rope_kv_kernel(T* qkv, int row_stride,
                                        const int* positions, const int* token_slot,
                                        PagedKV cache,
                                        int n_q_heads, float eps, int write_kv) {
-  __shared__ float buf[kRopeWarps][EK_MAX_HEAD_DIM];
+  __shared__ __align__(16) float buf[kRopeWarps][EK_MAX_HEAD_DIM];
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x;
@@ -45,17 +46,32 @@ __global__ void qk_norm_rope_kv_kernel(T* qkv, int row_stride,
     dst = (T*)(is_k ? cache.k : cache.v) + page_offset(cache, page, kv_head, pos);
   }
 
+  // Four neighbouring dimensions a lane when the sizes allow (head size a multiple of 4 and
+  // the rotated half a multiple of 4), else one.
+  const bool vec = (d % 4 == 0) && (rot_dim % 8 == 0) && (row_stride % 4 == 0);
   if (!is_q && !is_k) {                       // values: a copy
-    for (int i = lane; i < d; i += 32) dst[i] = src[i];
+    if (vec) {
+      for (int i = lane * 4; i < d; i += 128) Vec4<T>::store(dst + i, Vec4<T>::load(src + i));
+    } else {
+      for (int i = lane; i < d; i += 32) dst[i] = src[i];
+    }
     return;
   }
 
   const float* gain = is_q ? q_gain : k_gain;
   float ss = 0.f;
-  for (int i = lane; i < d; i += 32) {
-    const float v = to_f<T>(src[i]);
-    buf[warp][i] = v;
-    ss += v * v;
+  if (vec) {
+    for (int i = lane * 4; i < d; i += 128) {
+      const float4 v = Vec4<T>::load(src + i);
+      *reinterpret_cast<float4*>(&buf[warp][i]) = v;
+      ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    }
+  } else {
+    for (int i = lane; i < d; i += 32) {
+      const float v = to_f<T>(src[i]);
+      buf[warp][i] = v;
+      ss += v * v;
+    }
   }
   float rstd = 1.f;
   if (gain) {
@@ -66,19 +82,25 @@ __global__ void qk_norm_rope_kv_kernel(T* qkv, int row_stride,
   const int half = rot_dim >> 1;
   const float* cs = cos_tab + (size_t)pos * half;
   const float* sn = sin_tab + (size_t)pos * half;
-  for (int i = lane; i < d; i += 32) {
+  auto rotated = [&](int i) {
     const float g = gain ? gain[i] : 1.f;
     const float x = buf[warp][i] * rstd * g;
-    float out = x;
     if (i < half) {
       const float partner = buf[warp][i + half] * rstd * (gain ? gain[i + half] : 1.f);
-      out = x * cs[i] - partner * sn[i];
-    } else if (i < rot_dim) {
+      return x * cs[i] - partner * sn[i];
+    }
+    if (i < rot_dim) {
       const int j = i - half;
       const float partner = buf[warp][j] * rstd * (gain ? gain[j] : 1.f);
-      out = x * cs[j] + partner * sn[j];
+      return x * cs[j] + partner * sn[j];
     }
-    dst[i] = from_f<T>(out);
+    return x;
+  };
+  if (vec) {
+    for (int i = lane * 4; i < d; i += 128)
+      Vec4<T>::store(dst + i, make_float4(rotated(i), rotated(i + 1), rotated(i + 2), rotated(i + 3)));
+  } else {
+    for (int i = lane; i < d; i += 32) dst[i] = from_f<T>(rotated(i));
   }
 }
 

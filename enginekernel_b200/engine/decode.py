@@ -192,6 +192,7 @@ class DeviceBatchRun:
         for s in self.slots:
             cache.close(s)
         self.slots = []
+        self.backend.runner.check_kernels()
 
 
 class DeviceBackend:

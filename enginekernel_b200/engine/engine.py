@@ -99,6 +99,7 @@ class Engine:
     def close_sequence(self, slot: int) -> None:
         torch.cuda.current_stream().synchronize()
         self.cache.close(slot)
+        self.runner.check_kernels()
 
     def step(self, entries: Sequence) -> torch.Tensor:
         """``entries``: (slot, tokens, want) triples or :class:`StepEntry`.  Returns 32-bit

@@ -82,6 +82,13 @@ class ModelRunner:
             kernels.tc_status(self.device)
         model.prepare(min(cache.max_len, model.spec.max_positions))
 
+    def check_kernels(self) -> None:
+        """Raise if a kernel reported a failure (a tensor-core GEMM whose bounded barrier wait
+        ran out).  Synchronises the device; called where the host waits anyway."""
+        if self.model.dtype == torch.bfloat16 and self.device.type == "cuda":
+            from ..ops import kernels
+            kernels.check_tc_status(self.device)
+
     def _plan_for(self, n_tokens: int, n_seqs: int) -> PlanBuffers:
         p = self.plan
         if p is None or p.max_tokens < n_tokens or p.max_seqs < n_seqs:

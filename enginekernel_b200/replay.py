@@ -61,6 +61,7 @@ def main(argv=None) -> int:
             with open(path + ".tmp", "wb") as f:
                 f.write(arr.tobytes())
             os.replace(path + ".tmp", path)
+        engine.runner.check_kernels()
         for rid in step.get("end", []):
             if rid in slots:
                 engine.close_sequence(slots.pop(rid))
