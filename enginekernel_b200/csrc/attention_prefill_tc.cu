@@ -1,0 +1,346 @@
+// Causal prompt attention on the 5th-generation tensor cores (head sizes 64 and 128).
+//
+// A block owns 128 rows - (token, query head of one GQA group) pairs of consecutive new
+// tokens of one sequence - and one KV head, like the mma.sync kernel in
+// attention_prefill_bf16.cu, and walks the sequence's cache pages (64 keys each):
+//   S  = Q . K^T      tcgen05.mma, Q and the K page in shared memory (K by TMA), S in TMEM
+//   P  = softmax step  128 threads, one row each: the row's 64 scores come into registers with
+//                      one tcgen05.ld round trip, running max and sum stay in registers, P is
+//                      rounded to bfloat16 and written to shared memory in the 128-byte-swizzle
+//                      layout the MMA reads
+//   PV = P . V         tcgen05.mma into a second TMEM region, V page by TMA used as it lies
+//                      (rows = keys, i.e. an MN-major operand)
+//   O  = O * alpha + PV in registers (each thread keeps its row of O)
+// Warp 4 (one thread) is the TMA producer, warp 5 (one thread) issues the MMAs; mbarriers
+// order the phases so that S of the next page is computed while this page's softmax runs.
+// One block an SM (the row of O and the row of S live in registers).  Every wait is bounded
+// and reports through `status`.
+// Formula and rounding points as in the mma.sync kernel (scores and softmax in 32-bit, P in
+// bfloat16 before P.V; engine/ek_kernels.py:166-221 is the reference's Triton counterpart).
+#include "tc_common.cuh"
+
+namespace ek {
+
+constexpr int kFaRows = 128;
+constexpr int kFaKeys = EK_PAGE;             // 64
+constexpr int kFaThreads = 192;
+
+template <int D>
+__global__ void __launch_bounds__(kFaThreads, 1)
+attention_prefill_tc_kernel(bf16* __restrict__ out, const bf16* q, int q_row_stride,
+                            const int* positions, const int* token_slot, const int* cu_seqlens,
+                            int n_seqs, const __grid_constant__ CUtensorMap map_k,
+                            const __grid_constant__ CUtensorMap map_v, const int* block_table,
+                            int table_stride, int n_kv_heads, int n_q_heads, float scale_log2,
+                            int window, int tok_per_tile, int* status) {
+  constexpr int DB = D / 64;                       // 64-wide blocks of the head dimension
+  constexpr uint32_t kSub = kFaKeys * 128;         // one [64 x 64] bfloat16 sub-tile: 8 KB
+  constexpr uint32_t kTmemCols = D == 128 ? 256 : 128;
+  constexpr uint32_t kColS = 0, kColPV = 64;
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  unsigned char* q_s = smem;                                   // DB x [128 x 64]
+  unsigned char* k_s = q_s + DB * 2 * kSub;                    // 2 stages x DB x [64 x 64]
+  unsigned char* v_s = k_s + 2 * DB * kSub;                    // 2 stages x DB x [64 x 64]
+  unsigned char* p_s = v_s + 2 * DB * kSub;                    // [128 x 64]
+  uint64_t* bars = (uint64_t*)(p_s + 2 * kSub);
+  uint32_t* tmem_slot = (uint32_t*)(bars + 16);
+  __shared__ int tile_info[3];
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int kv_head = blockIdx.y;
+  const int group = n_q_heads / n_kv_heads;
+
+  pdl_launch_dependents();
+  pdl_wait();
+  if (tid == 0) {
+    int idx = blockIdx.x, found = -1, first = 0, count = 0;
+    for (int b = 0; b < n_seqs; ++b) {
+      const int n = cu_seqlens[b + 1] - cu_seqlens[b];
+      const int tiles = (n + tok_per_tile - 1) / tok_per_tile;
+      if (idx < tiles) {
+        const int tile = tiles - 1 - idx;          // long key ranges first
+        found = b;
+        first = cu_seqlens[b] + tile * tok_per_tile;
+        count = min(tok_per_tile, n - tile * tok_per_tile);
+        break;
+      }
+      idx -= tiles;
+    }
+    tile_info[0] = first; tile_info[1] = count; tile_info[2] = found;
+  }
+  __syncthreads();
+  if (tile_info[2] < 0) return;
+  const int t_first = tile_info[0], n_tok = tile_info[1];
+  const int pos0 = positions[t_first];
+  const int n_rows = n_tok * group;
+  if (pos0 < 0) {                                  // rows of a finished sequence: zeros
+    for (int i = tid; i < n_rows * D; i += kFaThreads) {
+      const int r = i / D, d = i % D;
+      out[((size_t)(t_first + r / group) * n_q_heads + kv_head * group + r % group) * D + d] =
+          __float2bfloat16_rn(0.f);
+    }
+    return;
+  }
+  const int* table = block_table + (size_t)token_slot[t_first] * table_stride;
+  const int hi_tile = pos0 + n_tok - 1;
+  const int lo_tile = window > 0 ? max(0, pos0 - window + 1) : 0;
+  const int kt_lo = lo_tile / kFaKeys, kt_hi = hi_tile / kFaKeys;
+  const int n_iter = kt_hi - kt_lo + 1;
+
+  // barriers: 0,1 k_full  2,3 k_empty  4,5 v_full  6,7 v_empty  8 s_full  9 s_empty
+  //           10 p_full  11 pv_full  12 pv_empty
+  const uint32_t bar0 = smem_u32(bars);
+  auto bar = [&](int i) { return bar0 + 8u * i; };
+  if (tid == 0) {
+    for (int i = 0; i < 9; ++i) mbar_init(bar(i), 1);
+    mbar_init(bar(9), 4);
+    mbar_init(bar(10), 4);
+    mbar_init(bar(11), 1);
+    mbar_init(bar(12), 4);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 4) tmem_alloc(smem_u32(tmem_slot), kTmemCols);
+
+  // Q -> shared memory in the K-major 128-byte-swizzle layout (rows beyond the real ones: 0)
+  for (int i = tid; i < kFaRows * (D / 8); i += kFaThreads) {
+    const int r = i / (D / 8), c = i % (D / 8);            // 16-byte piece c of row r
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (r < n_rows)
+      v = *reinterpret_cast<const uint4*>(q + (size_t)(t_first + r / group) * q_row_stride +
+                                          (size_t)(kv_head * group + r % group) * D + c * 8);
+    *reinterpret_cast<uint4*>(q_s + (c / 8) * 2 * kSub + r * 128 + (((c & 7) ^ (r & 7)) << 4)) = v;
+  }
+  fence_proxy_async_smem();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  bool ok = true;
+  if (tid == 128) {
+    // ------------------------------------------------------------------- TMA producer
+    for (int it = 0; it < n_iter; ++it) {
+      const int s = it & 1;
+      const uint32_t phase = (it >> 1) & 1;
+      const int row = (table[kt_lo + it] * n_kv_heads + kv_head) * kFaKeys;
+      ok = mbar_wait(bar(2 + s), phase ^ 1, status, 11);
+      if (!ok) break;
+      mbar_expect_tx(bar(0 + s), DB * kSub);
+#pragma unroll
+      for (int j = 0; j < DB; ++j)
+        tma_load_2d(smem_u32(k_s + (s * DB + j) * kSub), &map_k, 64 * j, row, bar(0 + s));
+      ok = mbar_wait(bar(6 + s), phase ^ 1, status, 12);
+      if (!ok) break;
+      mbar_expect_tx(bar(4 + s), DB * kSub);
+#pragma unroll
+      for (int j = 0; j < DB; ++j)
+        tma_load_2d(smem_u32(v_s + (s * DB + j) * kSub), &map_v, 64 * j, row, bar(4 + s));
+    }
+  } else if (tid == 160) {
+    // ------------------------------------------------------------------- MMA issuer
+    constexpr uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kFaKeys >> 3) << 17) |
+                                 ((uint32_t)(kFaRows >> 4) << 24);
+    constexpr uint32_t idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) |
+                                  ((uint32_t)(D >> 3) << 17) | ((uint32_t)(kFaRows >> 4) << 24);
+    for (int it = 0; it < n_iter; ++it) {
+      const int s = it & 1;
+      const uint32_t phase = (it >> 1) & 1;
+      // S = Q . K^T
+      ok = mbar_wait(bar(0 + s), phase, status, 21);
+      if (ok && it > 0) ok = mbar_wait(bar(9), (it - 1) & 1, status, 22);
+      if (!ok) break;
+      tc_fence_after();
+#pragma unroll
+      for (int j = 0; j < DB; ++j) {
+        const uint64_t dq = smem_desc_k_sw128(smem_u32(q_s + j * 2 * kSub));
+        const uint64_t dk = smem_desc_k_sw128(smem_u32(k_s + (s * DB + j) * kSub));
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          tc_mma(tmem_base + kColS, dq + (uint64_t)(2 * k), dk + (uint64_t)(2 * k), idesc_s,
+                 (j | k) ? 1u : 0u);
+      }
+      tc_commit(bar(2 + s));                       // the K stage is free when these are done
+      tc_commit(bar(8));                           // S is complete
+      // PV = P . V
+      ok = mbar_wait(bar(10), it & 1, status, 23);
+      if (ok) ok = mbar_wait(bar(4 + s), phase, status, 24);
+      if (ok && it > 0) ok = mbar_wait(bar(12), (it - 1) & 1, status, 25);
+      if (!ok) break;
+      tc_fence_after();
+      const uint64_t dp = smem_desc_k_sw128(smem_u32(p_s));
+      const uint64_t dv = smem_desc_mn_sw128(smem_u32(v_s + s * DB * kSub), kSub, 1024);
+#pragma unroll
+      for (int k = 0; k < 4; ++k)                  // 16 keys a step: 32 bytes along P's rows,
+        tc_mma(tmem_base + kColPV, dp + (uint64_t)(2 * k), dv + (uint64_t)(128 * k), idesc_pv,
+               k ? 1u : 0u);                       // 16 rows (2048 bytes) down V
+      tc_commit(bar(6 + s));
+      tc_commit(bar(11));
+    }
+  }
+
+  // ------------------------------------------------------------------------ softmax rows
+  float o_acc[D];
+  float m_run = -INFINITY, l_run = 0.f;
+  if (tid < kFaRows) {
+#pragma unroll
+    for (int i = 0; i < D; ++i) o_acc[i] = 0.f;
+    const int r = tid;
+    const int pos_r = pos0 + min(r / group, n_tok - 1);
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
+    for (int it = 0; it < n_iter && ok; ++it) {
+      const int key0 = (kt_lo + it) * kFaKeys;
+      ok = mbar_wait(bar(8), it & 1, status, 31);
+      if (!ok) break;
+      tc_fence_after();
+      // the row's 64 scores in registers; interior pages need no mask
+      float sc[kFaKeys];
+      tmem_ld32_nowait(lane_addr + kColS, sc);
+      tmem_ld32_nowait(lane_addr + kColS + 32, sc + 32);
+      tmem_ld_wait();
+      const bool full = key0 + kFaKeys - 1 <= pos_r && (window <= 0 || key0 > pos_r - window);
+      float mx = -INFINITY;
+      if (full) {
+#pragma unroll
+        for (int i = 0; i < kFaKeys; ++i) {
+          sc[i] *= scale_log2;
+          mx = fmaxf(mx, sc[i]);
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < kFaKeys; ++i) {
+          const int key = key0 + i;
+          const bool seen = key <= pos_r && (window <= 0 || key > pos_r - window);
+          sc[i] = seen ? sc[i] * scale_log2 : -INFINITY;
+          mx = fmaxf(mx, sc[i]);
+        }
+      }
+      const float m_new = fmaxf(m_run, mx);
+      const float m_use = m_new == -INFINITY ? 0.f : m_new;
+      const float alpha = exp2f(m_run - m_use);
+      m_run = m_new;
+      // probabilities, their sum, and P (bfloat16) into shared memory
+      float psum = 0.f;
+#pragma unroll
+      for (int c = 0; c < kFaKeys; c += 8) {
+        uint32_t w[4];
+#pragma unroll
+        for (int i = 0; i < 8; i += 2) {
+          const float p0 = exp2f(sc[c + i] - m_use), p1 = exp2f(sc[c + i + 1] - m_use);
+          psum += p0 + p1;
+          __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+          w[i / 2] = *reinterpret_cast<uint32_t*>(&h);
+        }
+        *reinterpret_cast<uint4*>(p_s + r * 128 + ((((c / 8)) ^ (r & 7)) << 4)) =
+            make_uint4(w[0], w[1], w[2], w[3]);
+      }
+      l_run = l_run * alpha + psum;
+      // S has been read: the next page's scores may overwrite it; P is ready for the MMA
+      tc_fence_before();
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(bar(9));
+        mbar_arrive(bar(10));
+      }
+      // O = O * alpha + P.V
+      ok = mbar_wait(bar(11), it & 1, status, 32);
+      if (!ok) break;
+      tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < D; c += 64) {
+        float v[64];
+        tmem_ld32_nowait(lane_addr + kColPV + c, v);
+        tmem_ld32_nowait(lane_addr + kColPV + c + 32, v + 32);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 64; ++i) o_acc[c + i] = o_acc[c + i] * alpha + v[i];
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(12));
+    }
+  }
+
+  const int failed = __syncthreads_or(ok ? 0 : 1);
+  if (!failed) {
+    if (tid < n_rows) {
+      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+      bf16* o = out + ((size_t)(t_first + tid / group) * n_q_heads + kv_head * group + tid % group) * D;
+#pragma unroll
+      for (int c = 0; c < D; c += 8) {
+        uint32_t w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          __nv_bfloat162 h = __floats2bfloat162_rn(o_acc[c + 2 * i] * inv, o_acc[c + 2 * i + 1] * inv);
+          w[i] = *reinterpret_cast<uint32_t*>(&h);
+        }
+        *reinterpret_cast<uint4*>(o + c) = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+    }
+  } else {
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);   // let copies in flight land
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 4) tmem_dealloc(tmem_base, kTmemCols);
+}
+
+template <int D>
+static int launch_fa(bf16* out, const bf16* q, int q_row_stride, const int* positions,
+                     const int* token_slot, const int* cu_seqlens, int n_seqs, int n_tokens,
+                     const void* k_pages, const void* v_pages, long long page_rows,
+                     const int* block_table, int table_stride, int n_q_heads, int n_kv_heads,
+                     float scale, int window, int* status, cudaStream_t stream) {
+  const int group = n_q_heads / n_kv_heads;
+  const int tok_per_tile = kFaRows / group;
+  CUtensorMap mk, mv;
+  int rc;
+  if ((rc = tensor_map(k_pages, page_rows, D, D, kFaKeys, &mk))) return rc;
+  if ((rc = tensor_map(v_pages, page_rows, D, D, kFaKeys, &mv))) return rc;
+  constexpr int DB = D / 64;
+  constexpr size_t smem = 1024 + (size_t)(2 * DB + 4 * DB + 2) * kFaKeys * 128 + 16 * 8 + 16;
+  auto kernel = attention_prefill_tc_kernel<D>;
+  static bool configured[kMaxDevices] = {};
+  int device = 0;
+  cudaError_t e = cudaGetDevice(&device);
+  if (e != cudaSuccess) return (int)e;
+  if (device < 0 || device >= kMaxDevices) return EK_ERR_ARG;
+  if (!configured[device]) {
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    configured[device] = true;
+  }
+  const int tiles = (n_tokens + tok_per_tile - 1) / tok_per_tile + n_seqs;   // upper bound
+  dim3 grid(tiles, n_kv_heads);
+  return (int)launch_pdl(kernel, grid, dim3(kFaThreads), smem, stream, out, q, q_row_stride, positions,
+                         token_slot, cu_seqlens, n_seqs, mk, mv, block_table, table_stride, n_kv_heads,
+                         n_q_heads, scale * 1.4426950408889634f, window, tok_per_tile, status);
+}
+
+}  // namespace ek
+
+// head_dim 64 or 128; the group (query heads per KV head) must divide 128; q rows 16-byte
+// aligned; n_pages = number of pages in k_pages / v_pages ([pages, kv heads, 64, head_dim]).
+EK_EXPORT int ek_attention_prefill_tc(void* out, const void* q, int q_row_stride,
+                                      const int* positions, const int* token_slot,
+                                      const int* cu_seqlens, int n_seqs, int n_tokens,
+                                      const void* k_pages, const void* v_pages, int n_pages,
+                                      const int* block_table, int table_stride, int n_q_heads,
+                                      int n_kv_heads, int head_dim, float scale, int window,
+                                      int* status, cudaStream_t stream) {
+  using namespace ek;
+  if (n_tokens <= 0 || n_seqs <= 0) return 0;
+  if ((head_dim != 64 && head_dim != 128) || n_kv_heads <= 0 || n_q_heads % n_kv_heads ||
+      kFaRows % (n_q_heads / n_kv_heads) || q_row_stride % 8 || ((uintptr_t)q & 15) || !status ||
+      n_kv_heads > 65535 || n_pages <= 0)
+    return EK_ERR_ARG;
+  const long long page_rows = (long long)n_pages * n_kv_heads * EK_PAGE;
+  if (head_dim == 64)
+    return launch_fa<64>((bf16*)out, (const bf16*)q, q_row_stride, positions, token_slot, cu_seqlens,
+                         n_seqs, n_tokens, k_pages, v_pages, page_rows, block_table, table_stride,
+                         n_q_heads, n_kv_heads, scale, window, status, stream);
+  return launch_fa<128>((bf16*)out, (const bf16*)q, q_row_stride, positions, token_slot, cu_seqlens,
+                        n_seqs, n_tokens, k_pages, v_pages, page_rows, block_table, table_stride,
+                        n_q_heads, n_kv_heads, scale, window, status, stream);
+}

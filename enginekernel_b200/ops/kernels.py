@@ -235,6 +235,37 @@ def attention_prefill_bf16(out, q, n_tokens, positions, token_slot, cu_seqlens, 
                        float(scale), int(window or 0), _stream())
 
 
+_attn_prefill_tc = Function("attention_prefill_tc", "ek_attention_prefill_tc",
+                            [_P, _P, c_int, _P, _P, _P, c_int, c_int, _P, _P, c_int, _P, c_int, c_int,
+                             c_int, c_int, c_float, c_int, _P, _P])
+
+
+def attention_prefill_tc_supported(dtype, head_dim, n_q_heads, n_kv_heads):
+    group = n_q_heads // n_kv_heads
+    return dtype == torch.bfloat16 and head_dim in (64, 128) and 128 % group == 0
+
+
+def attention_prefill_tc(out, q, n_tokens, positions, token_slot, cu_seqlens, n_seqs, k_pages,
+                         v_pages, block_table, n_q_heads, n_kv_heads, head_dim, scale, window=None):
+    """:func:`attention_prefill_bf16` on tcgen05 tensor cores (head sizes 64 and 128, groups
+    that divide 128): TMA-fed pages, scores and P.V in TMEM."""
+    _need_cuda(out, q, positions, token_slot, cu_seqlens, k_pages, v_pages, block_table)
+    _need(attention_prefill_tc_supported(q.dtype, head_dim, n_q_heads, n_kv_heads),
+          "attention_prefill_tc: bfloat16, head size 64 or 128, a group size that divides 128")
+    _need(out.dtype == q.dtype == k_pages.dtype, "attention: one dtype for q, cache and out")
+    _need(out.is_contiguous() and out.shape[-1] == n_q_heads * head_dim, "attention: out [T, NQ*D]")
+    _need(q.stride(-1) == 1 and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0,
+          "attention: dense, 16-byte aligned q rows")
+    _need(k_pages.is_contiguous() and v_pages.is_contiguous() and k_pages.dim() == 4
+          and k_pages.shape[1:] == (n_kv_heads, PAGE, head_dim), "attention: pages [P, NKV, 64, D]")
+    _need(cu_seqlens.dtype == torch.int32 and cu_seqlens.numel() >= n_seqs + 1, "attention: cu_seqlens")
+    _attn_prefill_tc(_ptr(out), _ptr(q), q.stride(0), _ptr(positions), _ptr(token_slot),
+                     _ptr(cu_seqlens), n_seqs, n_tokens, _ptr(k_pages), _ptr(v_pages),
+                     k_pages.shape[0], _ptr(block_table), block_table.stride(0), n_q_heads,
+                     n_kv_heads, head_dim, float(scale), int(window or 0),
+                     _ptr(tc_status(q.device)), _stream())
+
+
 # ------------------------------------------------------------------ matrix products
 _gemm_f32 = Function("gemm_f32", "ek_gemm_nt_f32",
                      [_P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P])

@@ -92,7 +92,11 @@ class Attention(Mixer):
         fast_decode = ctx.is_decode and kernels.attention_decode_supported(self.dtype, self.head_dim)
         if not ctx.is_decode and kernels.attention_prefill_supported(
                 self.dtype, self.head_dim, self.num_heads, self.num_kv_heads):
-            kernels.attention_prefill_bf16(
+            prefill = kernels.attention_prefill_bf16
+            if kernels.attention_prefill_tc_supported(self.dtype, self.head_dim, self.num_heads,
+                                                      self.num_kv_heads):
+                prefill = kernels.attention_prefill_tc      # tcgen05: head sizes 64 and 128
+            prefill(
                 out, qkv, t, ctx.positions, ctx.token_slot, ctx.cu_seqlens, ctx.n_seqs,
                 entry.k_pages, entry.v_pages, entry.block_table, self.num_heads, self.num_kv_heads,
                 self.head_dim, self.scale, self.window)

@@ -261,7 +261,7 @@ def test_attention_decode_bf16(nq, nkv, d):
 
 
 @pytest.mark.parametrize("nq,nkv,d", [(4, 2, 16), (6, 2, 48), (32, 8, 128), (5, 5, 80), (16, 1, 256),
-                                      (3, 1, 64), (8, 2, 128)])
+                                      (3, 1, 64), (8, 2, 128), (16, 2, 64), (4, 4, 128), (64, 1, 64)])
 def test_attention_prefill_bf16(nq, nkv, d):
     """The prompt kernel: several sequences of unequal lengths in one launch, some of them
     continuing after tokens already in the cache, groups that do not divide 128, windows."""
@@ -288,10 +288,15 @@ def test_attention_prefill_bf16(nq, nkv, d):
     slots = torch.tensor(slots, dtype=torch.int32, device=DEV)
     cu_t = torch.tensor(cu, dtype=torch.int32, device=DEV)
     scale = 1.0 / math.sqrt(d)
-    for window in (None, 100, 1, 64):
+    variants = [k.attention_prefill_bf16]
+    if k.attention_prefill_tc_supported(dtype, d, nq, nkv):
+        variants.append(k.attention_prefill_tc)          # the tcgen05 kernel, same contract
+    for window, fn in [(w, f) for f in variants for w in (None, 100, 1, 64)]:
         out = torch.full((t, nq * d), 7.0, dtype=dtype, device=DEV)
-        k.attention_prefill_bf16(out, q, t, positions, slots, cu_t, len(seqs), pages.k, pages.v,
-                                 pages.table, nq, nkv, d, scale, window)
+        fn(out, q, t, positions, slots, cu_t, len(seqs), pages.k, pages.v, pages.table, nq, nkv, d,
+           scale, window)
+        if fn is k.attention_prefill_tc:
+            k.check_tc_status(DEV)
         outc, qc = out.cpu(), q.cpu()
         worst = 0.0
         for i in range(0, t, 7 if t > 200 else 1):
@@ -302,7 +307,7 @@ def test_attention_prefill_bf16(nq, nkv, d):
             s, p = rows[i]
             want = ref_attention(qc[i, :nq * d].view(nq, d), kv[s][0].cpu(), kv[s][1].cpu(), p, scale, window)
             worst = max(worst, rel(outc[i], want))
-        assert worst <= TOL[dtype], (window, worst)
+        assert worst <= TOL[dtype], (window, fn.__name__, worst)
 
 
 # ------------------------------------------------------------------ matrix products
