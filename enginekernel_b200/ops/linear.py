@@ -16,6 +16,12 @@ from . import kernels
 SMALL_ROWS = kernels.TC_SWAP_MAX_ROWS
 
 
+def tc_takes(x, w) -> bool:
+    """Whether the tcgen05 kernel can read these operands (16-byte aligned rows)."""
+    return (w.shape[1] % 8 == 0 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
+            and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
 def linear(x, w, ctx, name: str, n_rows=None, out_dtype=None):
     """``x`` [M, K] (dense rows), ``w`` [N, K] -> [M, N] from the step's workspace."""
     m = n_rows if n_rows is not None else x.shape[0]
@@ -27,6 +33,14 @@ def linear(x, w, ctx, name: str, n_rows=None, out_dtype=None):
     want_f32 = out_dtype == torch.float32
     epi = kernels.EPI_F32 if want_f32 else kernels.EPI_BF16
     out = ctx.workspace.get(name, (m, n), torch.float32 if want_f32 else torch.bfloat16)
+    if not tc_takes(x, w):
+        # rows that TMA cannot address (inner size or stride not a multiple of 8 values): the
+        # library product, rounded once from its 32-bit accumulator
+        if want_f32:
+            torch.matmul(x[:m].float(), w.float().t(), out=out)
+        else:
+            torch.matmul(x[:m], w.t(), out=out)
+        return out
     if m <= SMALL_ROWS:
         kernels.gemm_tc_bf16(out, x, w, epi, n_rows=m, swap=True)
     elif want_f32:

@@ -11,7 +11,7 @@ from __future__ import annotations
 import torch
 
 from ..ops import kernels
-from ..ops.linear import linear
+from ..ops.linear import linear, tc_takes
 from ..registry import register_part
 from .base import FeedForward
 from .spec import TensorSpec
@@ -43,7 +43,7 @@ class GatedMLP(FeedForward):
 
     def forward(self, x, ctx):
         t = ctx.n_tokens
-        if self.dtype == torch.bfloat16 and t <= kernels.TC_SWAP_MAX_ROWS:
+        if self.dtype == torch.bfloat16 and t <= kernels.TC_SWAP_MAX_ROWS and tc_takes(x, self.w_gate_up):
             # gate and up rows share a tile, so silu(gate) * up is formed in the epilogue
             act = ctx.workspace.get("mlp_act", (t, self.inter), self.dtype)
             kernels.gemm_tc_bf16(act, x, self.w_gate_up, kernels.EPI_SWIGLU, n_rows=t, swap=True)

@@ -189,3 +189,54 @@ def test_stop_tokens_and_early_end(engines, plains):
     steps = list(eng.generate(prompts, 8, stop_token_ids=[stop]))
     col = [s[1] for s in steps]
     assert col[:first + 1] == free[:first + 1] and all(t == -1 for t in col[first + 1:])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_step_larger_than_one_pass_is_cut_into_pieces(folders, plains, dtype):
+    """More tokens than one pass takes: sequences are cut inside, later pieces read the cache
+    the earlier ones left, and the wanted rows come back in the caller's order."""
+    from enginekernel_b200 import Engine
+    tag = "C"
+    cfg = CONFIGS[tag][0]
+    eng = Engine(folders[tag], dtype, max_tokens=2048, max_batch=4, max_step_tokens=50)
+    seqs = tiny_models.random_prompts(cfg, [120, 7, 77], seed=91)
+    slots = [eng.open_sequence() for _ in seqs]
+    wants = [[0, 119, 60, 49, 50], [6], list(range(77))[::-1]]
+    logits = eng.step([(s, q, w) for s, q, w in zip(slots, seqs, wants)]).cpu()
+    r = 0
+    for q, w in zip(seqs, wants):
+        ref = plain.logits(plains[tag], q)
+        for place in w:
+            err = (logits[r] - ref[place]).abs().max().item() / ref.abs().max().item()
+            assert err <= helpers.TOL[dtype], (len(q), place, err)
+            r += 1
+    assert r == logits.shape[0]
+    for s in slots:
+        eng.close_sequence(s)
+
+
+def test_more_than_64_sequences_decode_together(folders, plains):
+    """A decode step wider than the small-batch kernels take (bfloat16)."""
+    from enginekernel_b200 import Engine
+    tag = "B"
+    cfg = CONFIGS[tag][0]
+    eng = Engine(folders[tag], "bfloat16", max_tokens=64 * 80, max_batch=80)
+    seqs = tiny_models.random_prompts(cfg, [3 + (i % 5) for i in range(70)], seed=17)
+    got = helpers.batch_then_steps(eng, seqs, [len(s) - 2 for s in seqs])
+    for i in (0, 1, 33, 69):
+        assert helpers.rel_err(got[i], plain.logits(plains[tag], seqs[i])) <= helpers.TOL["bfloat16"]
+
+
+def test_sizes_the_tensor_core_path_cannot_address_still_work(tmp_path):
+    """A width that is a multiple of 4 but not of 8: bfloat16 falls back to the library product
+    instead of refusing or computing wrong."""
+    from enginekernel_b200 import Engine
+    cfg = dict(tiny_models.TINY_A, hidden_size=68, intermediate_size=100, vocab_size=131)
+    folder = helpers.make_folder(tmp_path / "odd", cfg, 5)
+    model = helpers.plain_model(folder)
+    ids = tiny_models.random_prompts(cfg, [40], seed=2)[0]
+    want = plain.logits(model, ids)
+    for dtype in ("float32", "bfloat16"):
+        eng = Engine(folder, dtype, max_tokens=256, max_batch=2)
+        assert helpers.rel_err(helpers.whole(eng, ids), want) <= helpers.TOL[dtype]
+        assert helpers.rel_err(helpers.tail_one_by_one(eng, ids, 8), want) <= helpers.TOL[dtype]

@@ -1,0 +1,39 @@
+"""Layers of a real model family's width (Qwen3-4B shape, two layers, random weights):
+the kernels at the sizes they are tuned for, against the plain implementation."""
+
+import pytest
+import torch
+
+from tests import helpers
+from tests.plain import qwen3_plain as plain
+from tests.plain import tiny_models
+
+pytestmark = pytest.mark.gpu
+
+CFG = {
+    "architectures": ["Qwen3ForCausalLM"],
+    "num_hidden_layers": 2, "hidden_size": 2560, "num_attention_heads": 32,
+    "num_key_value_heads": 8, "head_dim": 128, "intermediate_size": 9728,
+    "vocab_size": 20011, "rope_theta": 5000000.0, "rms_norm_eps": 1e-6,
+    "max_position_embeddings": 4096, "tie_word_embeddings": True,
+}
+
+
+@pytest.fixture(scope="module")
+def folder(tmp_path_factory):
+    return helpers.make_folder(tmp_path_factory.mktemp("family"), CFG, 3)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_family_width_ragged_batch(folder, dtype):
+    from enginekernel_b200 import Engine
+    model = helpers.plain_model(folder)
+    eng = Engine(folder, dtype, max_tokens=2048, max_batch=4)
+    seqs = tiny_models.random_prompts(CFG, [150, 37, 70], seed=8)
+    got = helpers.batch_then_steps(eng, seqs, [140, 30, 70])
+    for s, g in zip(seqs, got):
+        err = helpers.rel_err(g, plain.logits(model, s))
+        assert err <= helpers.TOL[dtype], (dtype, len(s), err)
+    steps = list(eng.generate(seqs, 5))
+    if dtype == "float32":
+        assert [[st[b] for st in steps] for b in range(3)] == [plain.greedy(model, s, 5) for s in seqs]
