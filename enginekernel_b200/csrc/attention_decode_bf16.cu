@@ -283,6 +283,11 @@ static int launch_dch(bf16* out, const bf16* q, int q_row_stride, const int* pos
     if (e != cudaSuccess) return (int)e;
   }
   dim3 grid(n_tokens, cache.heads * row_blocks, n_splits);
+  // three blocks an SM (two for the largest head sizes) need this much shared memory; the rest
+  // stays L1, which the K/V stream needs for its loads in flight
+  const int blocks_per_sm = DCH <= 4 ? 3 : 2;
+  const int percent = (int)((blocks_per_sm * (smem + 1024) * 100 + 228 * 1024 - 1) / (228 * 1024));
+  prefer_carveout((const void*)attention_decode_bf16_kernel<DCH>, percent < 50 ? 50 : percent);
   cudaError_t e = launch_pdl(attention_decode_bf16_kernel<DCH>, grid, dim3(kDecWarps * 32), smem,
                              stream, out, q, q_row_stride, positions, token_slot, cache, n_q_heads,
                              row_blocks, scale * 1.4426950408889634f, window, n_splits,

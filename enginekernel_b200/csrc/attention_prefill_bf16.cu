@@ -285,6 +285,7 @@ static int launch_dmax(bf16* out, const bf16* q, int q_row_stride, const int* po
   cudaError_t e = cudaFuncSetAttribute(attention_prefill_bf16_kernel<DMAX>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
+  prefer_carveout((const void*)attention_prefill_bf16_kernel<DMAX>, 100);
   const int tiles = (n_tokens + tok_per_tile - 1) / tok_per_tile + n_seqs;   // upper bound
   dim3 grid(tiles, cache.heads);
   if (cache.heads > 65535) return EK_ERR_ARG;

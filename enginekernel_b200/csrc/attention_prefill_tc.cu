@@ -311,6 +311,7 @@ static int launch_fa(bf16* out, const bf16* q, int q_row_stride, const int* posi
     if (e != cudaSuccess) return (int)e;
     configured[device] = true;
   }
+  prefer_carveout((const void*)kernel, 100);
   const int tiles = (n_tokens + tok_per_tile - 1) / tok_per_tile + n_seqs;   // upper bound
   dim3 grid(tiles, n_kv_heads);
   return (int)launch_pdl(kernel, grid, dim3(kFaThreads), smem, stream, out, q, q_row_stride, positions,

@@ -9,6 +9,9 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <mutex>
+#include <unordered_set>
+
 #define EK_PAGE 64          // tokens per cache page (must match cache/pages.py)
 #define EK_MAX_HEAD_DIM 256
 
@@ -118,6 +121,21 @@ __device__ __forceinline__ size_t page_offset(const PagedKV& c, int page, int he
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+// Split of an SM's 256 KB between L1 and shared memory that a kernel wants, in percent of
+// shared memory (set once per kernel and device).  A kernel without a preference inherits what
+// the kernel before it left: the decode attention kernel, which streams through L1, ran 1.5x
+// slower behind the GEMM's all-shared split until it asked for its own.
+inline void prefer_carveout(const void* fn, int percent_shared) {
+  static std::mutex mu;
+  static std::unordered_set<unsigned long long> seen;
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess) return;
+  const unsigned long long key = (unsigned long long)(uintptr_t)fn * 64ull + (unsigned)device;
+  std::lock_guard<std::mutex> lock(mu);
+  if (seen.insert(key).second)
+    cudaFuncSetAttribute(fn, cudaFuncAttributePreferredSharedMemoryCarveout, percent_shared);
 }
 
 template <typename... KArgs, typename... Args>

@@ -314,6 +314,7 @@ static int launch_tc(const CUtensorMap& mp, const CUtensorMap& mq, const TcParam
     if (e != cudaSuccess) return (int)e;
     configured[device] = true;
   }
+  prefer_carveout((const void*)kernel, 100);   // the operand ring wants all the shared memory
   return (int)launch_pdl(kernel, grid, dim3(128), smem, stream, mp, mq, prm);
 }
 
