@@ -3,18 +3,21 @@
 // A block owns 128 rows - (token, query head of one GQA group) pairs of consecutive new
 // tokens of one sequence - and one KV head, like the mma.sync kernel in
 // attention_prefill_bf16.cu, and walks the sequence's cache pages (64 keys each):
-//   S  = Q . K^T      tcgen05.mma, Q and the K page in shared memory (K by TMA), S in TMEM
-//   P  = softmax step  128 threads, one row each: the row's 64 scores come into registers with
-//                      one tcgen05.ld round trip, running max and sum stay in registers, P is
-//                      rounded to bfloat16 and written to shared memory in the 128-byte-swizzle
-//                      layout the MMA reads
-//   PV = P . V         tcgen05.mma into a second TMEM region, V page by TMA used as it lies
-//                      (rows = keys, i.e. an MN-major operand)
-//   O  = O * alpha + PV in registers (each thread keeps its row of O)
-// Warp 4 (one thread) is the TMA producer, warp 5 (one thread) issues the MMAs; mbarriers
-// order the phases so that S of the next page is computed while this page's softmax runs.
-// One block an SM (the row of O and the row of S live in registers).  Every wait is bounded
-// and reports through `status`.
+//   S  = Q . K^T      tcgen05.mma, Q and the K page in shared memory (K by TMA), S in TMEM,
+//                     two S buffers so that page t+1 is scored while page t is in softmax
+//   P  = softmax step  8 warps, two threads a row (32 keys each; warps w and w + 4 reach the
+//                      same TMEM lanes): the scores come into registers with one tcgen05.ld,
+//                      the two halves exchange their maxima through shared memory, P is rounded
+//                      to bfloat16 and written to one of two shared-memory buffers in the
+//                      128-byte-swizzle layout the MMA reads
+//   O += P . V        tcgen05.mma accumulating in TMEM; the V page arrives by TMA and is used as
+//                      it lies (rows = keys, i.e. an MN-major operand)
+// The running maximum is lazy: exponentials are taken against a reference that is raised (and O
+// and the running sum rescaled, by tcgen05.ld/st of the row) only when a page's maximum exceeds
+// it by more than 2^8, which keeps every probability finite in bfloat16 and skips the rescale
+// of almost every page.  O is divided by the sum once, at the end.
+// Warp 8 (one thread) is the TMA producer, warp 9 (one thread) issues the MMAs.  One block an
+// SM.  Every wait is bounded and reports through `status`.
 // Formula and rounding points as in the mma.sync kernel (scores and softmax in 32-bit, P in
 // bfloat16 before P.V; engine/ek_kernels.py:166-221 is the reference's Triton counterpart).
 #include "tc_common.cuh"
@@ -23,7 +26,7 @@ namespace ek {
 
 constexpr int kFaRows = 128;
 constexpr int kFaKeys = EK_PAGE;             // 64
-constexpr int kFaThreads = 192;
+constexpr int kFaThreads = 320;              // 8 softmax warps, a producer warp, an MMA warp
 
 template <int D>
 __global__ void __launch_bounds__(kFaThreads, 1)
@@ -35,17 +38,18 @@ attention_prefill_tc_kernel(bf16* __restrict__ out, const bf16* q, int q_row_str
                             int window, int tok_per_tile, int* status) {
   constexpr int DB = D / 64;                       // 64-wide blocks of the head dimension
   constexpr uint32_t kSub = kFaKeys * 128;         // one [64 x 64] bfloat16 sub-tile: 8 KB
-  constexpr uint32_t kTmemCols = D == 128 ? 256 : 128;
-  constexpr uint32_t kColS = 0, kColPV = 64;
+  constexpr uint32_t kTmemCols = 256;
+  constexpr uint32_t kColS = 0, kColO = 128;        // S buffers at 0 and 64, O at 128
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   unsigned char* q_s = smem;                                   // DB x [128 x 64]
   unsigned char* k_s = q_s + DB * 2 * kSub;                    // 2 stages x DB x [64 x 64]
   unsigned char* v_s = k_s + 2 * DB * kSub;                    // 2 stages x DB x [64 x 64]
-  unsigned char* p_s = v_s + 2 * DB * kSub;                    // [128 x 64]
-  uint64_t* bars = (uint64_t*)(p_s + 2 * kSub);
-  uint32_t* tmem_slot = (uint32_t*)(bars + 16);
+  unsigned char* p_s = v_s + 2 * DB * kSub;                    // 2 buffers x [128 x 64]
+  uint64_t* bars = (uint64_t*)(p_s + 4 * kSub);
+  uint32_t* tmem_slot = (uint32_t*)(bars + 20);
   __shared__ int tile_info[3];
+  __shared__ float xch[2][2][kFaRows];             // [page parity][column half][row]
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int kv_head = blockIdx.y;
@@ -88,19 +92,19 @@ attention_prefill_tc_kernel(bf16* __restrict__ out, const bf16* q, int q_row_str
   const int kt_lo = lo_tile / kFaKeys, kt_hi = hi_tile / kFaKeys;
   const int n_iter = kt_hi - kt_lo + 1;
 
-  // barriers: 0,1 k_full  2,3 k_empty  4,5 v_full  6,7 v_empty  8 s_full  9 s_empty
-  //           10 p_full  11 pv_full  12 pv_empty
+  // barriers: 0,1 k_full  2,3 k_empty  4,5 v_full  6,7 v_empty  8,9 s_full  10,11 s_empty
+  //           12,13 p_full  14,15 pv_done  16..19 the two halves of a row quarter
   const uint32_t bar0 = smem_u32(bars);
   auto bar = [&](int i) { return bar0 + 8u * i; };
   if (tid == 0) {
-    for (int i = 0; i < 9; ++i) mbar_init(bar(i), 1);
-    mbar_init(bar(9), 4);
-    mbar_init(bar(10), 4);
-    mbar_init(bar(11), 1);
-    mbar_init(bar(12), 4);
+    for (int i = 0; i < 10; ++i) mbar_init(bar(i), 1);
+    for (int i = 10; i < 14; ++i) mbar_init(bar(i), 8);
+    mbar_init(bar(14), 1);
+    mbar_init(bar(15), 1);
+    for (int i = 16; i < 20; ++i) mbar_init(bar(i), 2);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 4) tmem_alloc(smem_u32(tmem_slot), kTmemCols);
+  if (warp == 8) tmem_alloc(smem_u32(tmem_slot), kTmemCols);
 
   // Q -> shared memory in the K-major 128-byte-swizzle layout (rows beyond the real ones: 0)
   for (int i = tid; i < kFaRows * (D / 8); i += kFaThreads) {
@@ -118,7 +122,7 @@ attention_prefill_tc_kernel(bf16* __restrict__ out, const bf16* q, int q_row_str
   const uint32_t tmem_base = *tmem_slot;
 
   bool ok = true;
-  if (tid == 128) {
+  if (tid == 256) {
     // ------------------------------------------------------------------- TMA producer
     for (int it = 0; it < n_iter; ++it) {
       const int s = it & 1;
@@ -137,92 +141,136 @@ attention_prefill_tc_kernel(bf16* __restrict__ out, const bf16* q, int q_row_str
       for (int j = 0; j < DB; ++j)
         tma_load_2d(smem_u32(v_s + (s * DB + j) * kSub), &map_v, 64 * j, row, bar(4 + s));
     }
-  } else if (tid == 160) {
+  } else if (tid == 288) {
     // ------------------------------------------------------------------- MMA issuer
     constexpr uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kFaKeys >> 3) << 17) |
                                  ((uint32_t)(kFaRows >> 4) << 24);
     constexpr uint32_t idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) |
                                   ((uint32_t)(D >> 3) << 17) | ((uint32_t)(kFaRows >> 4) << 24);
-    for (int it = 0; it < n_iter; ++it) {
-      const int s = it & 1;
-      const uint32_t phase = (it >> 1) & 1;
-      // S = Q . K^T
-      ok = mbar_wait(bar(0 + s), phase, status, 21);
-      if (ok && it > 0) ok = mbar_wait(bar(9), (it - 1) & 1, status, 22);
-      if (!ok) break;
-      tc_fence_after();
+    // page t is scored (into S buffer t & 1) before page t-1's P.V is issued, so the tensor
+    // pipe works on the next scores while the softmax warps work on the current ones
+    for (int it = 0; it <= n_iter && ok; ++it) {
+      if (it < n_iter) {
+        const int s = it & 1;
+        const uint32_t phase = (it >> 1) & 1;
+        ok = mbar_wait(bar(0 + s), phase, status, 21);
+        if (ok && it >= 2) ok = mbar_wait(bar(10 + s), phase ^ 1, status, 22);   // S buffer read
+        if (!ok) break;
+        tc_fence_after();
 #pragma unroll
-      for (int j = 0; j < DB; ++j) {
-        const uint64_t dq = smem_desc_k_sw128(smem_u32(q_s + j * 2 * kSub));
-        const uint64_t dk = smem_desc_k_sw128(smem_u32(k_s + (s * DB + j) * kSub));
+        for (int j = 0; j < DB; ++j) {
+          const uint64_t dq = smem_desc_k_sw128(smem_u32(q_s + j * 2 * kSub));
+          const uint64_t dk = smem_desc_k_sw128(smem_u32(k_s + (s * DB + j) * kSub));
 #pragma unroll
-        for (int k = 0; k < 4; ++k)
-          tc_mma(tmem_base + kColS, dq + (uint64_t)(2 * k), dk + (uint64_t)(2 * k), idesc_s,
-                 (j | k) ? 1u : 0u);
+          for (int k = 0; k < 4; ++k)
+            tc_mma(tmem_base + kColS + 64 * s, dq + (uint64_t)(2 * k), dk + (uint64_t)(2 * k), idesc_s,
+                   (j | k) ? 1u : 0u);
+        }
+        tc_commit(bar(2 + s));                     // the K stage is free when these are done
+        tc_commit(bar(8 + s));                     // S is complete
       }
-      tc_commit(bar(2 + s));                       // the K stage is free when these are done
-      tc_commit(bar(8));                           // S is complete
-      // PV = P . V
-      ok = mbar_wait(bar(10), it & 1, status, 23);
-      if (ok) ok = mbar_wait(bar(4 + s), phase, status, 24);
-      if (ok && it > 0) ok = mbar_wait(bar(12), (it - 1) & 1, status, 25);
-      if (!ok) break;
-      tc_fence_after();
-      const uint64_t dp = smem_desc_k_sw128(smem_u32(p_s));
-      const uint64_t dv = smem_desc_mn_sw128(smem_u32(v_s + s * DB * kSub), kSub, 1024);
+      if (it >= 1) {
+        const int u = it - 1, s = u & 1;
+        const uint32_t phase = (u >> 1) & 1;
+        ok = mbar_wait(bar(12 + s), phase, status, 23);               // P written (O rescaled)
+        if (ok) ok = mbar_wait(bar(4 + s), phase, status, 24);        // V landed
+        if (!ok) break;
+        tc_fence_after();
+        const uint64_t dp = smem_desc_k_sw128(smem_u32(p_s + s * 2 * kSub));
+        const uint64_t dv = smem_desc_mn_sw128(smem_u32(v_s + s * DB * kSub), kSub, 1024);
 #pragma unroll
-      for (int k = 0; k < 4; ++k)                  // 16 keys a step: 32 bytes along P's rows,
-        tc_mma(tmem_base + kColPV, dp + (uint64_t)(2 * k), dv + (uint64_t)(128 * k), idesc_pv,
-               k ? 1u : 0u);                       // 16 rows (2048 bytes) down V
-      tc_commit(bar(6 + s));
-      tc_commit(bar(11));
+        for (int k = 0; k < 4; ++k)                // 16 keys a step: 32 bytes along P's rows,
+          tc_mma(tmem_base + kColO, dp + (uint64_t)(2 * k), dv + (uint64_t)(128 * k), idesc_pv,
+                 (u | k) ? 1u : 0u);               // 16 rows (2048 bytes) down V
+        tc_commit(bar(6 + s));                     // the V stage is free
+        tc_commit(bar(14 + s));                    // P buffer free, O holds pages 0..u
+      }
     }
   }
 
   // ------------------------------------------------------------------------ softmax rows
-  float o_acc[D];
-  float m_run = -INFINITY, l_run = 0.f;
-  if (tid < kFaRows) {
-#pragma unroll
-    for (int i = 0; i < D; ++i) o_acc[i] = 0.f;
-    const int r = tid;
+  constexpr int DH = D / 2;                        // this thread's share of the head dimension
+  constexpr int KH = kFaKeys / 2;                  // and of a page's keys
+  constexpr float kLazy = 8.f;                     // raise the reference maximum above 2^8 only
+  float m_ref = -INFINITY, l_run = 0.f;
+  const int r = (warp & 3) * 32 + lane;            // row = TMEM lane
+  const int half = (warp >> 2) & 1;                // which half of the columns
+  const uint32_t pair_bar = bar(16 + (warp & 3));  // warps w and w + 4 meet here once a page
+  const uint32_t lane_addr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
+  if (tid < 2 * kFaRows) {
     const int pos_r = pos0 + min(r / group, n_tok - 1);
-    const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
     for (int it = 0; it < n_iter && ok; ++it) {
-      const int key0 = (kt_lo + it) * kFaKeys;
-      ok = mbar_wait(bar(8), it & 1, status, 31);
+      const int s = it & 1;
+      const uint32_t phase = (it >> 1) & 1;
+      const int key0 = (kt_lo + it) * kFaKeys + KH * half;
+      ok = mbar_wait(bar(8 + s), phase, status, 31);
       if (!ok) break;
       tc_fence_after();
-      // the row's 64 scores in registers; interior pages need no mask
-      float sc[kFaKeys];
-      tmem_ld32_nowait(lane_addr + kColS, sc);
-      tmem_ld32_nowait(lane_addr + kColS + 32, sc + 32);
+      float sc[KH];
+      tmem_ld32_nowait(lane_addr + kColS + 64 * s + KH * half, sc);
       tmem_ld_wait();
-      const bool full = key0 + kFaKeys - 1 <= pos_r && (window <= 0 || key0 > pos_r - window);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(10 + s));     // this S buffer may be overwritten
+      const bool full = key0 + KH - 1 <= pos_r && (window <= 0 || key0 > pos_r - window);
       float mx = -INFINITY;
       if (full) {
 #pragma unroll
-        for (int i = 0; i < kFaKeys; ++i) {
+        for (int i = 0; i < KH; ++i) {
           sc[i] *= scale_log2;
           mx = fmaxf(mx, sc[i]);
         }
       } else {
 #pragma unroll
-        for (int i = 0; i < kFaKeys; ++i) {
+        for (int i = 0; i < KH; ++i) {
           const int key = key0 + i;
           const bool seen = key <= pos_r && (window <= 0 || key > pos_r - window);
           sc[i] = seen ? sc[i] * scale_log2 : -INFINITY;
           mx = fmaxf(mx, sc[i]);
         }
       }
-      const float m_new = fmaxf(m_run, mx);
-      const float m_use = m_new == -INFINITY ? 0.f : m_new;
-      const float alpha = exp2f(m_run - m_use);
-      m_run = m_new;
-      // probabilities, their sum, and P (bfloat16) into shared memory
-      float psum = 0.f;
+      // the row's maximum is over both halves
+      xch[s][half][r] = mx;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(pair_bar);
+      ok = mbar_wait(pair_bar, it & 1, status, 33);
+      if (!ok) break;
+      mx = fmaxf(mx, xch[s][half ^ 1][r]);
+      // tcgen05.ld/st are warp-wide: if any row of the warp raises its reference, the whole warp
+      // rescales (rows that keep theirs multiply by 1)
+      const bool raise = mx > m_ref + kLazy;       // also the first page with a visible key
+      const float alpha = raise ? exp2f(m_ref - mx) : 1.f;   // 0 while the reference is -inf
+      if (it > 0 && __any_sync(0xffffffffu, raise)) {
+        // O holds pages 0..it-1 once their last P.V is done; scale this thread's half of the row
+        const int u = it - 1;
+        ok = mbar_wait(bar(14 + (u & 1)), (u >> 1) & 1, status, 34);
+        if (!ok) break;
+        tc_fence_after();
 #pragma unroll
-      for (int c = 0; c < kFaKeys; c += 8) {
+        for (int c = 0; c < DH; c += 32) {
+          float v[32];
+          tmem_ld32_nowait(lane_addr + kColO + DH * half + c, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] *= alpha;
+          tmem_st32(lane_addr + kColO + DH * half + c, v);
+        }
+        tmem_st_wait();
+      }
+      if (raise) {
+        l_run *= alpha;
+        m_ref = mx;
+      }
+      const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
+      // the P buffer is free once the P.V of page it-2 is done
+      if (it >= 2) {
+        ok = mbar_wait(bar(14 + s), phase ^ 1, status, 35);
+        if (!ok) break;
+      }
+      float psum = 0.f;
+      unsigned char* p_row = p_s + s * 2 * kSub + r * 128;
+#pragma unroll
+      for (int c = 0; c < KH; c += 8) {
         uint32_t w[4];
 #pragma unroll
         for (int i = 0; i < 8; i += 2) {
@@ -231,51 +279,49 @@ attention_prefill_tc_kernel(bf16* __restrict__ out, const bf16* q, int q_row_str
           __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
           w[i / 2] = *reinterpret_cast<uint32_t*>(&h);
         }
-        *reinterpret_cast<uint4*>(p_s + r * 128 + ((((c / 8)) ^ (r & 7)) << 4)) =
+        *reinterpret_cast<uint4*>(p_row + (((4 * half + c / 8) ^ (r & 7)) << 4)) =
             make_uint4(w[0], w[1], w[2], w[3]);
       }
-      l_run = l_run * alpha + psum;
-      // S has been read: the next page's scores may overwrite it; P is ready for the MMA
+      l_run += psum;
       tc_fence_before();
       fence_proxy_async_smem();
       __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(bar(9));
-        mbar_arrive(bar(10));
-      }
-      // O = O * alpha + P.V
-      ok = mbar_wait(bar(11), it & 1, status, 32);
-      if (!ok) break;
+      if (lane == 0) mbar_arrive(bar(12 + s));     // P (and any rescale of O) is in place
+    }
+    if (ok) {                                      // the last P.V
+      const int u = n_iter - 1;
+      ok = mbar_wait(bar(14 + (u & 1)), (u >> 1) & 1, status, 36);
       tc_fence_after();
-#pragma unroll
-      for (int c = 0; c < D; c += 64) {
-        float v[64];
-        tmem_ld32_nowait(lane_addr + kColPV + c, v);
-        tmem_ld32_nowait(lane_addr + kColPV + c + 32, v + 32);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 64; ++i) o_acc[c + i] = o_acc[c + i] * alpha + v[i];
-      }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar(12));
     }
   }
 
   const int failed = __syncthreads_or(ok ? 0 : 1);
   if (!failed) {
-    if (tid < n_rows) {
-      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-      bf16* o = out + ((size_t)(t_first + tid / group) * n_q_heads + kv_head * group + tid % group) * D;
+    if (tid < 2 * kFaRows) xch[0][half][r] = l_run;            // the two halves' sums
+    __syncthreads();
+    if (tid < 2 * kFaRows) {                       // whole warps: tcgen05.ld is warp-wide
+      const float l = xch[0][0][r] + xch[0][1][r];
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      const int row = min(r, n_rows - 1);
+      bf16* o = out + ((size_t)(t_first + row / group) * n_q_heads + kv_head * group + row % group) * D +
+                DH * half;
 #pragma unroll
-      for (int c = 0; c < D; c += 8) {
-        uint32_t w[4];
+      for (int c = 0; c < DH; c += 32) {
+        float v[32];
+        tmem_ld32_nowait(lane_addr + kColO + DH * half + c, v);
+        tmem_ld_wait();
+        if (r < n_rows) {
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          __nv_bfloat162 h = __floats2bfloat162_rn(o_acc[c + 2 * i] * inv, o_acc[c + 2 * i + 1] * inv);
-          w[i] = *reinterpret_cast<uint32_t*>(&h);
+          for (int j = 0; j < 32; j += 8) {
+            uint32_t w[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              __nv_bfloat162 h = __floats2bfloat162_rn(v[j + 2 * i] * inv, v[j + 2 * i + 1] * inv);
+              w[i] = *reinterpret_cast<uint32_t*>(&h);
+            }
+            *reinterpret_cast<uint4*>(o + c + j) = make_uint4(w[0], w[1], w[2], w[3]);
+          }
         }
-        *reinterpret_cast<uint4*>(o + c) = make_uint4(w[0], w[1], w[2], w[3]);
       }
     }
   } else {
@@ -283,7 +329,7 @@ attention_prefill_tc_kernel(bf16* __restrict__ out, const bf16* q, int q_row_str
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 4) tmem_dealloc(tmem_base, kTmemCols);
+  if (warp == 8) tmem_dealloc(tmem_base, kTmemCols);
 }
 
 template <int D>
@@ -299,7 +345,7 @@ static int launch_fa(bf16* out, const bf16* q, int q_row_stride, const int* posi
   if ((rc = tensor_map(k_pages, page_rows, D, D, kFaKeys, &mk))) return rc;
   if ((rc = tensor_map(v_pages, page_rows, D, D, kFaKeys, &mv))) return rc;
   constexpr int DB = D / 64;
-  constexpr size_t smem = 1024 + (size_t)(2 * DB + 4 * DB + 2) * kFaKeys * 128 + 16 * 8 + 16;
+  constexpr size_t smem = 1024 + (size_t)(2 * DB + 4 * DB + 4) * kFaKeys * 128 + 20 * 8 + 16;
   auto kernel = attention_prefill_tc_kernel<D>;
   static bool configured[kMaxDevices] = {};
   int device = 0;
