@@ -104,6 +104,144 @@ __global__ void qk_norm_rope_kv_kernel(T* qkv, int row_stride,
   }
 }
 
+
+// Wide form for 16-bit rows whose head size is 64, 128 or 256 and fully rotated: a lane holds
+// 8 neighbouring dimensions (one 16-byte load), D/8 lanes a head, and a block takes every
+// head of one token, all loads issued before the first use.  The rotation partner (j + D/2)
+// sits in the lane D/16 further on, so it comes by shuffle; nothing goes through shared
+// memory.  Same arithmetic and rounding as the kernel above.
+constexpr int kWideThreads = 256;
+constexpr int kWidePasses = 4;
+
+template <int D>
+__global__ void __launch_bounds__(kWideThreads)
+qk_norm_rope_kv_wide_kernel(bf16* qkv, int row_stride, const float* __restrict__ q_gain,
+                            const float* __restrict__ k_gain, const float* __restrict__ cos_tab,
+                            const float* __restrict__ sin_tab, const int* positions,
+                            const int* token_slot, PagedKV cache, int n_q_heads, float eps,
+                            int write_kv) {
+  constexpr int LPH = D / 8;                       // lanes a head
+  constexpr int HPP = kWideThreads / LPH;          // heads a pass
+  constexpr int half = D / 2;
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const int pos = positions[t];
+  if (pos < 0) return;
+  const int n_kv = cache.heads;
+  const int n_heads = write_kv ? n_q_heads + 2 * n_kv : n_q_heads;
+  const int lih = threadIdx.x % LPH;               // lane in head
+  const int head0 = threadIdx.x / LPH;
+  const bool low = lih < LPH / 2;
+  // the lanes of this head within the warp: heads of one warp may take different branches
+  const unsigned seg = LPH == 32 ? 0xffffffffu
+                                 : ((1u << (LPH & 31)) - 1u) << ((threadIdx.x & 31) / LPH * LPH);
+  const int j0 = (lih % (LPH / 2)) * 8;            // angle index of this lane's first pair
+  bf16* row = qkv + (size_t)t * row_stride;
+  size_t page_base = 0;
+  if (write_kv) {
+    const int page = cache.block_table[(size_t)token_slot[t] * cache.table_stride + pos / EK_PAGE];
+    page_base = page_offset(cache, page, 0, pos);
+  }
+  float cs[8], sn[8];
+  {
+    const float4* c4 = reinterpret_cast<const float4*>(cos_tab + (size_t)pos * half + j0);
+    const float4* s4 = reinterpret_cast<const float4*>(sin_tab + (size_t)pos * half + j0);
+    const float4 a = c4[0], b = c4[1], c = s4[0], d = s4[1];
+    cs[0] = a.x; cs[1] = a.y; cs[2] = a.z; cs[3] = a.w; cs[4] = b.x; cs[5] = b.y; cs[6] = b.z; cs[7] = b.w;
+    sn[0] = c.x; sn[1] = c.y; sn[2] = c.z; sn[3] = c.w; sn[4] = d.x; sn[5] = d.y; sn[6] = d.z; sn[7] = d.w;
+  }
+  for (int base = 0; base < n_heads; base += HPP * kWidePasses) {
+    uint4 raw[kWidePasses];
+#pragma unroll
+    for (int p = 0; p < kWidePasses; ++p) {
+      const int head = base + p * HPP + head0;
+      if (head < n_heads) raw[p] = *reinterpret_cast<const uint4*>(row + (size_t)head * D + lih * 8);
+    }
+#pragma unroll
+    for (int p = 0; p < kWidePasses; ++p) {
+      const int head = base + p * HPP + head0;
+      // shuffles below are among the D/8 lanes of a head, which are all in or all out
+      if (head >= n_heads) continue;
+      const bool is_q = head < n_q_heads;
+      const bool is_k = !is_q && head < n_q_heads + n_kv;
+      bf16* dst = row + (size_t)head * D + lih * 8;
+      if (!is_q) {
+        const int kv_head = is_k ? head - n_q_heads : head - n_q_heads - n_kv;
+        dst = (bf16*)(is_k ? cache.k : cache.v) + page_base + (size_t)kv_head * EK_PAGE * D + lih * 8;
+      }
+      if (!is_q && !is_k) {
+        *reinterpret_cast<uint4*>(dst) = raw[p];
+        continue;
+      }
+      const float* gain = is_q ? q_gain : k_gain;
+      float x[8];
+      {
+        const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw[p]);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float2 f = __bfloat1622float2(h2[i]);
+          x[2 * i] = f.x;
+          x[2 * i + 1] = f.y;
+        }
+      }
+      if (gain) {
+        float ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) ss += x[i] * x[i];
+#pragma unroll
+        for (int o = LPH / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(seg, ss, o, LPH);
+        const float rstd = rsqrtf(ss / (float)D + eps);
+        const float4 g0 = *reinterpret_cast<const float4*>(gain + lih * 8);
+        const float4 g1 = *reinterpret_cast<const float4*>(gain + lih * 8 + 4);
+        const float g[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+#pragma unroll
+        for (int i = 0; i < 8; ++i) x[i] = x[i] * rstd * g[i];
+      }
+      uint32_t w[4];
+      float y[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float partner = __shfl_xor_sync(seg, x[i], LPH / 2, LPH);
+        y[i] = low ? x[i] * cs[i] - partner * sn[i] : x[i] * cs[i] + partner * sn[i];
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        __nv_bfloat162 h = __floats2bfloat162_rn(y[2 * i], y[2 * i + 1]);
+        w[i] = *reinterpret_cast<uint32_t*>(&h);
+      }
+      *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+  }
+}
+
+template <int D>
+static int launch_wide(bf16* qkv, int row_stride, const float* q_gain, const float* k_gain,
+                       const float* cos_tab, const float* sin_tab, const int* positions,
+                       const int* token_slot, PagedKV cache, int n_tokens, int n_q_heads, float eps,
+                       int write_kv, cudaStream_t stream) {
+  return (int)launch_pdl(qk_norm_rope_kv_wide_kernel<D>, dim3(n_tokens), dim3(kWideThreads), 0, stream,
+                         qkv, row_stride, q_gain, k_gain, cos_tab, sin_tab, positions, token_slot, cache,
+                         n_q_heads, eps, write_kv);
+}
+
+// The wide form needs 16-byte rows and tables; one token a block pays once there are enough
+// tokens to fill the machine.
+template <typename T>
+static bool wide_takes(const void*, int, const float*, const float*, const float*, const float*, int,
+                       const void*, const void*, int, int) {
+  return false;
+}
+template <>
+bool wide_takes<bf16>(const void* qkv, int row_stride, const float* q_gain, const float* k_gain,
+                      const float* cos_tab, const float* sin_tab, int rot_dim, const void* k_pages,
+                      const void* v_pages, int n_tokens, int head_dim) {
+  auto aligned = [](const void* p) { return ((uintptr_t)p & 15) == 0; };
+  return (head_dim == 64 || head_dim == 128 || head_dim == 256) && rot_dim == head_dim &&
+         n_tokens >= 128 && row_stride % 8 == 0 && aligned(qkv) && aligned(q_gain) && aligned(k_gain) &&
+         aligned(cos_tab) && aligned(sin_tab) && aligned(k_pages) && aligned(v_pages);
+}
+
 template <typename T>
 static int launch(void* qkv, int row_stride, const float* q_gain, const float* k_gain,
                   const float* cos_tab, const float* sin_tab, int rot_dim, const int* positions,
@@ -115,6 +253,18 @@ static int launch(void* qkv, int row_stride, const float* q_gain, const float* k
       rot_dim > head_dim || (rot_dim & 1) || n_tokens > 2147483647 / 2)
     return EK_ERR_ARG;
   PagedKV cache{k_pages, v_pages, block_table, table_stride, n_kv_heads, head_dim};
+  if (wide_takes<T>(qkv, row_stride, q_gain, k_gain, cos_tab, sin_tab, rot_dim, k_pages, v_pages,
+                    n_tokens, head_dim)) {
+    bf16* rows = (bf16*)qkv;
+    if (head_dim == 64)
+      return launch_wide<64>(rows, row_stride, q_gain, k_gain, cos_tab, sin_tab, positions, token_slot,
+                             cache, n_tokens, n_q_heads, eps, write_kv, stream);
+    if (head_dim == 128)
+      return launch_wide<128>(rows, row_stride, q_gain, k_gain, cos_tab, sin_tab, positions, token_slot,
+                              cache, n_tokens, n_q_heads, eps, write_kv, stream);
+    return launch_wide<256>(rows, row_stride, q_gain, k_gain, cos_tab, sin_tab, positions, token_slot,
+                            cache, n_tokens, n_q_heads, eps, write_kv, stream);
+  }
   const int heads = n_q_heads + 2 * n_kv_heads;
   dim3 grid(n_tokens, (heads + kRopeWarps - 1) / kRopeWarps);
   return (int)launch_pdl(qk_norm_rope_kv_kernel<T>, grid, dim3(kRopeWarps * 32), 0, stream, (T*)qkv,

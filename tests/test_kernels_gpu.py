@@ -184,6 +184,70 @@ def test_qk_norm_rope_kv(dtype, nq, nkv, d, rot):
     assert torch.equal(q2[:, :nq * d], qkv[:, :nq * d])
 
 
+@pytest.mark.parametrize("nq,nkv,d,gains", [(5, 1, 64, True), (120, 8, 64, True), (12, 3, 128, True),
+                                            (60, 4, 128, False), (3, 2, 256, True), (8, 2, 128, True)])
+def test_qk_norm_rope_kv_many_tokens(nq, nkv, d, gains):
+    """The 16-bit form that takes a whole token a block (128 tokens and more): more heads than one
+    pass holds, q and k heads sharing a warp, finished rows in between, with and without gains."""
+    k = K()
+    dtype = torch.bfloat16
+    eps, theta, n_slots, per_slot = 1e-6, 10000.0, 3, 100
+    t = n_slots * per_slot
+    pages = Pages(n_slots, per_slot + 30, nkv, d, dtype, seed=d + nq)
+    before_k, before_v = pages.k.clone(), pages.v.clone()
+    g = torch.Generator().manual_seed(5)
+    slot_of = torch.arange(t) // per_slot
+    pos_of = (torch.arange(t) % per_slot) + torch.tensor([0, 30, 7])[slot_of]
+    dead = torch.rand(t, generator=g) < 0.1
+    pos_of = torch.where(dead, torch.full_like(pos_of, -1), pos_of)
+    width = (nq + 2 * nkv) * d
+    buf = rnd(t, width + 8, dtype=dtype, seed=11)
+    qkv = buf[:, :width]                                  # rows with a stride that is not the width
+    orig = qkv.clone()
+    qg = 1 + 0.1 * rnd(d, seed=8) if gains else None
+    kg = 1 + 0.1 * rnd(d, seed=9) if gains else None
+    inv = 1.0 / (theta ** (torch.arange(0, d, 2, dtype=torch.float32) / d))
+    freqs = torch.outer(torch.arange(per_slot + 30, dtype=torch.float32), inv)
+    positions = pos_of.to(torch.int32).to(DEV)
+    slots = slot_of.to(torch.int32).to(DEV)
+    k.qk_norm_rope_kv(qkv, t, qg, kg, freqs.cos().to(DEV), freqs.sin().to(DEV), d, positions, slots,
+                      pages.k, pages.v, pages.table, nq, nkv, d, eps)
+
+    live = ~dead
+    x = orig.cpu().double().view(t, nq + 2 * nkv, d)
+    c = freqs[pos_of.clamp(min=0)].double().cos()[:, None, :]
+    s_ = freqs[pos_of.clamp(min=0)].double().sin()[:, None, :]
+
+    def rotate(heads, gain):
+        if gain is not None:
+            heads = heads * torch.rsqrt(heads.pow(2).mean(-1, keepdim=True) + eps) * gain.cpu().double()
+        lo, hi = heads[..., : d // 2], heads[..., d // 2:]
+        return torch.cat([lo * c - hi * s_, hi * c + lo * s_], -1)
+
+    want_q = rotate(x[:, :nq], qg)
+    want_k = rotate(x[:, nq:nq + nkv], kg)
+    got_q = qkv.cpu().view(t, nq + 2 * nkv, d)[:, :nq]
+    assert rel(got_q[live], want_q[live]) <= TOL[dtype]
+    assert torch.equal(qkv[dead.to(DEV)], orig[dead.to(DEV)])
+    assert torch.equal(qkv[:, nq * d:], orig[:, nq * d:])             # k and v parts of the rows stay
+    table = pages.table.cpu()
+    page = table[slot_of, pos_of.clamp(min=0) // 64].long()
+    off = pos_of.clamp(min=0) % 64
+    got_k, got_v = pages.k.cpu()[page, :, off], pages.v.cpu()[page, :, off]          # [t, nkv, d]
+    assert rel(got_k[live], want_k[live]) <= TOL[dtype]
+    assert torch.equal(got_v[live], orig.cpu().view(t, -1, d)[:, nq + nkv:][live])
+    mask = torch.ones(pages.k.shape[:3], dtype=torch.bool)
+    mask[page[live], :, off[live]] = False
+    assert torch.equal(pages.k.cpu()[mask], before_k.cpu()[mask])
+    assert torch.equal(pages.v.cpu()[mask], before_v.cpu()[mask])
+    # the per-head form gives the same rows (a narrow batch takes it)
+    q2 = orig[:100].clone()
+    k2, v2 = before_k.clone(), before_v.clone()
+    k.qk_norm_rope_kv(q2, 100, qg, kg, freqs.cos().to(DEV), freqs.sin().to(DEV), d, positions[:100],
+                      slots[:100], k2, v2, pages.table, nq, nkv, d, eps)
+    assert rel(q2[:, :nq * d].float(), qkv[:100, :nq * d].float()) <= 1e-2
+
+
 # ------------------------------------------------------------------ attention
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("nq,nkv,d", [(4, 2, 16), (6, 3, 48), (8, 2, 128), (5, 5, 80), (16, 1, 256)])
