@@ -7,17 +7,20 @@
 //                     two S buffers so that page t+1 is scored while page t is in softmax
 //   P  = softmax step  8 warps, two threads a row (32 keys each; warps w and w + 4 reach the
 //                      same TMEM lanes): the scores come into registers with one tcgen05.ld,
-//                      the two halves exchange their maxima through shared memory, P is rounded
-//                      to bfloat16 and written to one of two shared-memory buffers in the
-//                      128-byte-swizzle layout the MMA reads
-//   O += P . V        tcgen05.mma accumulating in TMEM; the V page arrives by TMA and is used as
-//                      it lies (rows = keys, i.e. an MN-major operand)
+//                      the two halves exchange their maxima through shared memory, and P,
+//                      rounded to bfloat16, goes back into the first 32 columns of the S buffer
+//                      it came from (tcgen05.st, two values a column)
+//   O += P . V        tcgen05.mma with P read from TMEM, accumulating in TMEM; the V page arrives
+//                      by TMA and is used as it lies (rows = keys, i.e. an MN-major operand)
+// The MMAs of one thread run in issue order, so the scores of page t+2 overwrite an S buffer only
+// after the P.V of page t has read its P from there: the buffers need no barrier of their own.
 // The running maximum is lazy: exponentials are taken against a reference that is raised (and O
 // and the running sum rescaled, by tcgen05.ld/st of the row) only when a page's maximum exceeds
 // it by more than 2^8, which keeps every probability finite in bfloat16 and skips the rescale
 // of almost every page.  O is divided by the sum once, at the end.
-// Warp 8 (one thread) is the TMA producer, warp 9 (one thread) issues the MMAs.  One block an
-// SM.  Every wait is bounded and reports through `status`.
+// Warp 8 (one thread) is the TMA producer, warp 9 (one thread) issues the MMAs.  Shared memory
+// holds Q and two stages each of K and V (96 KB at head size 128), TMEM 256 columns (S, S, O):
+// two blocks an SM.  Every wait is bounded and reports through `status`.
 // Formula and rounding points as in the mma.sync kernel (scores and softmax in 32-bit, P in
 // bfloat16 before P.V; engine/ek_kernels.py:166-221 is the reference's Triton counterpart).
 #include "tc_common.cuh"
@@ -27,9 +30,11 @@ namespace ek {
 constexpr int kFaRows = 128;
 constexpr int kFaKeys = EK_PAGE;             // 64
 constexpr int kFaThreads = 320;              // 8 softmax warps, a producer warp, an MMA warp
+constexpr int kFaBarPair = 14;              // first of the four pair barriers (list in the kernel)
+constexpr int kFaBars = kFaBarPair + 4;
 
 template <int D>
-__global__ void __launch_bounds__(kFaThreads, 1)
+__global__ void __launch_bounds__(kFaThreads, 2)
 attention_prefill_tc_kernel(bf16* __restrict__ out, const bf16* q, int q_row_stride,
                             const int* positions, const int* token_slot, const int* cu_seqlens,
                             int n_seqs, const __grid_constant__ CUtensorMap map_k,
@@ -45,9 +50,8 @@ attention_prefill_tc_kernel(bf16* __restrict__ out, const bf16* q, int q_row_str
   unsigned char* q_s = smem;                                   // DB x [128 x 64]
   unsigned char* k_s = q_s + DB * 2 * kSub;                    // 2 stages x DB x [64 x 64]
   unsigned char* v_s = k_s + 2 * DB * kSub;                    // 2 stages x DB x [64 x 64]
-  unsigned char* p_s = v_s + 2 * DB * kSub;                    // 2 buffers x [128 x 64]
-  uint64_t* bars = (uint64_t*)(p_s + 4 * kSub);
-  uint32_t* tmem_slot = (uint32_t*)(bars + 20);
+  uint64_t* bars = (uint64_t*)(v_s + 2 * DB * kSub);
+  uint32_t* tmem_slot = (uint32_t*)(bars + kFaBars);
   __shared__ int tile_info[3];
   __shared__ float xch[2][2][kFaRows];             // [page parity][column half][row]
 
@@ -92,16 +96,17 @@ attention_prefill_tc_kernel(bf16* __restrict__ out, const bf16* q, int q_row_str
   const int kt_lo = lo_tile / kFaKeys, kt_hi = hi_tile / kFaKeys;
   const int n_iter = kt_hi - kt_lo + 1;
 
-  // barriers: 0,1 k_full  2,3 k_empty  4,5 v_full  6,7 v_empty  8,9 s_full  10,11 s_empty
-  //           12,13 p_full  14,15 pv_done  16..19 the two halves of a row quarter
+  // barriers: 0,1 k_full  2,3 k_empty  4,5 v_full  6,7 v_empty  8,9 s_full  10,11 p_full
+  //           12,13 pv_done  14..17 the two halves of a row quarter
   const uint32_t bar0 = smem_u32(bars);
   auto bar = [&](int i) { return bar0 + 8u * i; };
   if (tid == 0) {
     for (int i = 0; i < 10; ++i) mbar_init(bar(i), 1);
-    for (int i = 10; i < 14; ++i) mbar_init(bar(i), 8);
-    mbar_init(bar(14), 1);
-    mbar_init(bar(15), 1);
-    for (int i = 16; i < 20; ++i) mbar_init(bar(i), 2);
+    mbar_init(bar(10), 8);
+    mbar_init(bar(11), 8);
+    mbar_init(bar(12), 1);
+    mbar_init(bar(13), 1);
+    for (int i = kFaBarPair; i < kFaBars; ++i) mbar_init(bar(i), 2);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 8) tmem_alloc(smem_u32(tmem_slot), kTmemCols);
@@ -154,7 +159,6 @@ attention_prefill_tc_kernel(bf16* __restrict__ out, const bf16* q, int q_row_str
         const int s = it & 1;
         const uint32_t phase = (it >> 1) & 1;
         ok = mbar_wait(bar(0 + s), phase, status, 21);
-        if (ok && it >= 2) ok = mbar_wait(bar(10 + s), phase ^ 1, status, 22);   // S buffer read
         if (!ok) break;
         tc_fence_after();
 #pragma unroll
@@ -172,18 +176,17 @@ attention_prefill_tc_kernel(bf16* __restrict__ out, const bf16* q, int q_row_str
       if (it >= 1) {
         const int u = it - 1, s = u & 1;
         const uint32_t phase = (u >> 1) & 1;
-        ok = mbar_wait(bar(12 + s), phase, status, 23);               // P written (O rescaled)
+        ok = mbar_wait(bar(10 + s), phase, status, 23);               // P written (O rescaled)
         if (ok) ok = mbar_wait(bar(4 + s), phase, status, 24);        // V landed
         if (!ok) break;
         tc_fence_after();
-        const uint64_t dp = smem_desc_k_sw128(smem_u32(p_s + s * 2 * kSub));
         const uint64_t dv = smem_desc_mn_sw128(smem_u32(v_s + s * DB * kSub), kSub, 1024);
 #pragma unroll
-        for (int k = 0; k < 4; ++k)                // 16 keys a step: 32 bytes along P's rows,
-          tc_mma(tmem_base + kColO, dp + (uint64_t)(2 * k), dv + (uint64_t)(128 * k), idesc_pv,
-                 (u | k) ? 1u : 0u);               // 16 rows (2048 bytes) down V
+        for (int k = 0; k < 4; ++k)                // 16 keys a step: 8 columns of P,
+          tc_mma_ts(tmem_base + kColO, tmem_base + kColS + 64 * s + 8 * k, dv + (uint64_t)(128 * k),
+                    idesc_pv, (u | k) ? 1u : 0u);  // 16 rows (2048 bytes) down V
         tc_commit(bar(6 + s));                     // the V stage is free
-        tc_commit(bar(14 + s));                    // P buffer free, O holds pages 0..u
+        tc_commit(bar(12 + s));                    // O holds pages 0..u
       }
     }
   }
@@ -192,10 +195,10 @@ attention_prefill_tc_kernel(bf16* __restrict__ out, const bf16* q, int q_row_str
   constexpr int DH = D / 2;                        // this thread's share of the head dimension
   constexpr int KH = kFaKeys / 2;                  // and of a page's keys
   constexpr float kLazy = 8.f;                     // raise the reference maximum above 2^8 only
-  float m_ref = -INFINITY, l_run = 0.f;
+  float m_ref = -INFINITY, l_run = 0.f;            // the reference is in units of log2(e)/scale
   const int r = (warp & 3) * 32 + lane;            // row = TMEM lane
   const int half = (warp >> 2) & 1;                // which half of the columns
-  const uint32_t pair_bar = bar(16 + (warp & 3));  // warps w and w + 4 meet here once a page
+  const uint32_t pair_bar = bar(kFaBarPair + (warp & 3));  // warps w and w + 4 meet here once a page
   const uint32_t lane_addr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
   if (tid < 2 * kFaRows) {
     const int pos_r = pos0 + min(r / group, n_tok - 1);
@@ -209,88 +212,81 @@ attention_prefill_tc_kernel(bf16* __restrict__ out, const bf16* q, int q_row_str
       float sc[KH];
       tmem_ld32_nowait(lane_addr + kColS + 64 * s + KH * half, sc);
       tmem_ld_wait();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar(10 + s));     // this S buffer may be overwritten
       const bool full = key0 + KH - 1 <= pos_r && (window <= 0 || key0 > pos_r - window);
-      float mx = -INFINITY;
+      float mx0 = -INFINITY, mx1 = -INFINITY;      // of the raw scores (the scale is positive)
       if (full) {
 #pragma unroll
-        for (int i = 0; i < KH; ++i) {
-          sc[i] *= scale_log2;
-          mx = fmaxf(mx, sc[i]);
+        for (int i = 0; i < KH; i += 2) {
+          mx0 = fmaxf(mx0, sc[i]);
+          mx1 = fmaxf(mx1, sc[i + 1]);
         }
       } else {
 #pragma unroll
-        for (int i = 0; i < KH; ++i) {
+        for (int i = 0; i < KH; i += 2) {
           const int key = key0 + i;
-          const bool seen = key <= pos_r && (window <= 0 || key > pos_r - window);
-          sc[i] = seen ? sc[i] * scale_log2 : -INFINITY;
-          mx = fmaxf(mx, sc[i]);
+          const bool seen0 = key <= pos_r && (window <= 0 || key > pos_r - window);
+          const bool seen1 = key + 1 <= pos_r && (window <= 0 || key + 1 > pos_r - window);
+          sc[i] = seen0 ? sc[i] : -INFINITY;
+          sc[i + 1] = seen1 ? sc[i + 1] : -INFINITY;
+          mx0 = fmaxf(mx0, sc[i]);
+          mx1 = fmaxf(mx1, sc[i + 1]);
         }
       }
+      float mx = fmaxf(mx0, mx1);
       // the row's maximum is over both halves
       xch[s][half][r] = mx;
       __syncwarp();
       if (lane == 0) mbar_arrive(pair_bar);
       ok = mbar_wait(pair_bar, it & 1, status, 33);
       if (!ok) break;
-      mx = fmaxf(mx, xch[s][half ^ 1][r]);
+      mx = fmaxf(mx, xch[s][half ^ 1][r]) * scale_log2;
       // tcgen05.ld/st are warp-wide: if any row of the warp raises its reference, the whole warp
       // rescales (rows that keep theirs multiply by 1)
       const bool raise = mx > m_ref + kLazy;       // also the first page with a visible key
-      const float alpha = raise ? exp2f(m_ref - mx) : 1.f;   // 0 while the reference is -inf
+      const float alpha = raise ? ex2_approx(m_ref - mx) : 1.f;   // 0 while the reference is -inf
       if (it > 0 && __any_sync(0xffffffffu, raise)) {
         // O holds pages 0..it-1 once their last P.V is done; scale this thread's half of the row
         const int u = it - 1;
-        ok = mbar_wait(bar(14 + (u & 1)), (u >> 1) & 1, status, 34);
+        ok = mbar_wait(bar(12 + (u & 1)), (u >> 1) & 1, status, 34);
         if (!ok) break;
         tc_fence_after();
 #pragma unroll
-        for (int c = 0; c < DH; c += 32) {
-          float v[32];
-          tmem_ld32_nowait(lane_addr + kColO + DH * half + c, v);
+        for (int c = 0; c < DH; c += 16) {
+          float v[16];
+          tmem_ld16_nowait(lane_addr + kColO + DH * half + c, v);
           tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] *= alpha;
-          tmem_st32(lane_addr + kColO + DH * half + c, v);
+          for (int i = 0; i < 16; ++i) v[i] *= alpha;
+          tmem_st16(lane_addr + kColO + DH * half + c, reinterpret_cast<const uint32_t*>(v));
         }
-        tmem_st_wait();
       }
       if (raise) {
         l_run *= alpha;
         m_ref = mx;
       }
-      const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
-      // the P buffer is free once the P.V of page it-2 is done
-      if (it >= 2) {
-        ok = mbar_wait(bar(14 + s), phase ^ 1, status, 35);
-        if (!ok) break;
-      }
-      float psum = 0.f;
-      unsigned char* p_row = p_s + s * 2 * kSub + r * 128;
+      const float neg_m = m_ref == -INFINITY ? 0.f : -m_ref;
+      float psum0 = 0.f, psum1 = 0.f;
+      uint32_t w[KH / 2];
 #pragma unroll
-      for (int c = 0; c < KH; c += 8) {
-        uint32_t w[4];
-#pragma unroll
-        for (int i = 0; i < 8; i += 2) {
-          const float p0 = exp2f(sc[c + i] - m_use), p1 = exp2f(sc[c + i + 1] - m_use);
-          psum += p0 + p1;
-          __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
-          w[i / 2] = *reinterpret_cast<uint32_t*>(&h);
-        }
-        *reinterpret_cast<uint4*>(p_row + (((4 * half + c / 8) ^ (r & 7)) << 4)) =
-            make_uint4(w[0], w[1], w[2], w[3]);
+      for (int i = 0; i < KH; i += 2) {
+        const float p0 = ex2_approx(fmaf(sc[i], scale_log2, neg_m));
+        const float p1 = ex2_approx(fmaf(sc[i + 1], scale_log2, neg_m));
+        psum0 += p0;
+        psum1 += p1;
+        __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+        w[i / 2] = *reinterpret_cast<uint32_t*>(&h);
       }
-      l_run += psum;
+      l_run += psum0 + psum1;
+      // P over the scores it came from: this half's 32 keys are 16 columns
+      tmem_st16(lane_addr + kColS + 64 * s + (KH / 2) * half, w);
+      tmem_st_wait();
       tc_fence_before();
-      fence_proxy_async_smem();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar(12 + s));     // P (and any rescale of O) is in place
+      if (lane == 0) mbar_arrive(bar(10 + s));     // P (and any rescale of O) is in place
     }
     if (ok) {                                      // the last P.V
       const int u = n_iter - 1;
-      ok = mbar_wait(bar(14 + (u & 1)), (u >> 1) & 1, status, 36);
+      ok = mbar_wait(bar(12 + (u & 1)), (u >> 1) & 1, status, 36);
       tc_fence_after();
     }
   }
@@ -345,7 +341,7 @@ static int launch_fa(bf16* out, const bf16* q, int q_row_stride, const int* posi
   if ((rc = tensor_map(k_pages, page_rows, D, D, kFaKeys, &mk))) return rc;
   if ((rc = tensor_map(v_pages, page_rows, D, D, kFaKeys, &mv))) return rc;
   constexpr int DB = D / 64;
-  constexpr size_t smem = 1024 + (size_t)(2 * DB + 4 * DB + 4) * kFaKeys * 128 + 20 * 8 + 16;
+  constexpr size_t smem = 1024 + (size_t)(2 * DB + 4 * DB) * kFaKeys * 128 + kFaBars * 8 + 16;
   auto kernel = attention_prefill_tc_kernel<D>;
   static bool configured[kMaxDevices] = {};
   int device = 0;
@@ -380,6 +376,7 @@ EK_EXPORT int ek_attention_prefill_tc(void* out, const void* q, int q_row_stride
   if (n_tokens <= 0 || n_seqs <= 0) return 0;
   if ((head_dim != 64 && head_dim != 128) || n_kv_heads <= 0 || n_q_heads % n_kv_heads ||
       kFaRows % (n_q_heads / n_kv_heads) || q_row_stride % 8 || ((uintptr_t)q & 15) || !status ||
+      !(scale > 0.f) ||
       n_kv_heads > 65535 || n_pages <= 0)
     return EK_ERR_ARG;
   const long long page_rows = (long long)n_pages * n_kv_heads * EK_PAGE;
