@@ -5,11 +5,10 @@
 // attention_prefill_bf16.cu, and walks the sequence's cache pages (64 keys each):
 //   S  = Q . K^T      tcgen05.mma, Q and the K page in shared memory (K by TMA), S in TMEM,
 //                     two S buffers so that page t+1 is scored while page t is in softmax
-//   P  = softmax step  8 warps, two threads a row (32 keys each; warps w and w + 4 reach the
-//                      same TMEM lanes): the scores come into registers with one tcgen05.ld,
-//                      the two halves exchange their maxima through shared memory, and P,
-//                      rounded to bfloat16, goes back into the first 32 columns of the S buffer
-//                      it came from (tcgen05.st, two values a column)
+//   P  = softmax step  4 warps, a thread a row (warp w reaches TMEM lanes 32 w ...): the 64
+//                      scores come into registers by tcgen05.ld, and P, rounded to bfloat16,
+//                      goes back into the first 32 columns of the S buffer it came from
+//                      (tcgen05.st, two values a column); no thread needs another's numbers
 //   O += P . V        tcgen05.mma with P read from TMEM, accumulating in TMEM; the V page arrives
 //                      by TMA and is used as it lies (rows = keys, i.e. an MN-major operand)
 // The MMAs of one thread run in issue order, so the scores of page t+2 overwrite an S buffer only
@@ -18,7 +17,7 @@
 // and the running sum rescaled, by tcgen05.ld/st of the row) only when a page's maximum exceeds
 // it by more than 2^8, which keeps every probability finite in bfloat16 and skips the rescale
 // of almost every page.  O is divided by the sum once, at the end.
-// Warp 8 (one thread) is the TMA producer, warp 9 (one thread) issues the MMAs.  Shared memory
+// Warp 4 (one thread) is the TMA producer, warp 5 (one thread) issues the MMAs.  Shared memory
 // holds Q and two stages each of K and V (96 KB at head size 128), TMEM 256 columns (S, S, O):
 // two blocks an SM.  Every wait is bounded and reports through `status`.
 // Formula and rounding points as in the mma.sync kernel (scores and softmax in 32-bit, P in
@@ -29,9 +28,8 @@ namespace ek {
 
 constexpr int kFaRows = 128;
 constexpr int kFaKeys = EK_PAGE;             // 64
-constexpr int kFaThreads = 320;              // 8 softmax warps, a producer warp, an MMA warp
-constexpr int kFaBarPair = 14;              // first of the four pair barriers (list in the kernel)
-constexpr int kFaBars = kFaBarPair + 4;
+constexpr int kFaThreads = 192;              // 4 softmax warps, a producer warp, an MMA warp
+constexpr int kFaBars = 14;                  // the list is in the kernel
 
 template <int D>
 __global__ void __launch_bounds__(kFaThreads, 2)
@@ -53,7 +51,6 @@ attention_prefill_tc_kernel(bf16* __restrict__ out, const bf16* q, int q_row_str
   uint64_t* bars = (uint64_t*)(v_s + 2 * DB * kSub);
   uint32_t* tmem_slot = (uint32_t*)(bars + kFaBars);
   __shared__ int tile_info[3];
-  __shared__ float xch[2][2][kFaRows];             // [page parity][column half][row]
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int kv_head = blockIdx.y;
@@ -97,19 +94,18 @@ attention_prefill_tc_kernel(bf16* __restrict__ out, const bf16* q, int q_row_str
   const int n_iter = kt_hi - kt_lo + 1;
 
   // barriers: 0,1 k_full  2,3 k_empty  4,5 v_full  6,7 v_empty  8,9 s_full  10,11 p_full
-  //           12,13 pv_done  14..17 the two halves of a row quarter
+  //           12,13 pv_done
   const uint32_t bar0 = smem_u32(bars);
   auto bar = [&](int i) { return bar0 + 8u * i; };
   if (tid == 0) {
     for (int i = 0; i < 10; ++i) mbar_init(bar(i), 1);
-    mbar_init(bar(10), 8);
-    mbar_init(bar(11), 8);
+    mbar_init(bar(10), 4);
+    mbar_init(bar(11), 4);
     mbar_init(bar(12), 1);
     mbar_init(bar(13), 1);
-    for (int i = kFaBarPair; i < kFaBars; ++i) mbar_init(bar(i), 2);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 8) tmem_alloc(smem_u32(tmem_slot), kTmemCols);
+  if (warp == 4) tmem_alloc(smem_u32(tmem_slot), kTmemCols);
 
   // Q -> shared memory in the K-major 128-byte-swizzle layout (rows beyond the real ones: 0)
   for (int i = tid; i < kFaRows * (D / 8); i += kFaThreads) {
@@ -127,7 +123,7 @@ attention_prefill_tc_kernel(bf16* __restrict__ out, const bf16* q, int q_row_str
   const uint32_t tmem_base = *tmem_slot;
 
   bool ok = true;
-  if (tid == 256) {
+  if (tid == 128) {
     // ------------------------------------------------------------------- TMA producer
     for (int it = 0; it < n_iter; ++it) {
       const int s = it & 1;
@@ -146,7 +142,7 @@ attention_prefill_tc_kernel(bf16* __restrict__ out, const bf16* q, int q_row_str
       for (int j = 0; j < DB; ++j)
         tma_load_2d(smem_u32(v_s + (s * DB + j) * kSub), &map_v, 64 * j, row, bar(4 + s));
     }
-  } else if (tid == 288) {
+  } else if (tid == 160) {
     // ------------------------------------------------------------------- MMA issuer
     constexpr uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kFaKeys >> 3) << 17) |
                                  ((uint32_t)(kFaRows >> 4) << 24);
@@ -192,72 +188,56 @@ attention_prefill_tc_kernel(bf16* __restrict__ out, const bf16* q, int q_row_str
   }
 
   // ------------------------------------------------------------------------ softmax rows
-  constexpr int DH = D / 2;                        // this thread's share of the head dimension
-  constexpr int KH = kFaKeys / 2;                  // and of a page's keys
   constexpr float kLazy = 8.f;                     // raise the reference maximum above 2^8 only
   float m_ref = -INFINITY, l_run = 0.f;            // the reference is in units of log2(e)/scale
-  const int r = (warp & 3) * 32 + lane;            // row = TMEM lane
-  const int half = (warp >> 2) & 1;                // which half of the columns
-  const uint32_t pair_bar = bar(kFaBarPair + (warp & 3));  // warps w and w + 4 meet here once a page
+  const int r = tid;                               // row = TMEM lane (softmax threads)
   const uint32_t lane_addr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
-  if (tid < 2 * kFaRows) {
+  if (tid < kFaRows) {
     const int pos_r = pos0 + min(r / group, n_tok - 1);
     for (int it = 0; it < n_iter && ok; ++it) {
       const int s = it & 1;
       const uint32_t phase = (it >> 1) & 1;
-      const int key0 = (kt_lo + it) * kFaKeys + KH * half;
+      const int key0 = (kt_lo + it) * kFaKeys;
       ok = mbar_wait(bar(8 + s), phase, status, 31);
       if (!ok) break;
       tc_fence_after();
-      float sc[KH];
-      tmem_ld32_nowait(lane_addr + kColS + 64 * s + KH * half, sc);
+      float sc[kFaKeys];
+      tmem_ld32_nowait(lane_addr + kColS + 64 * s, sc);
+      tmem_ld32_nowait(lane_addr + kColS + 64 * s + 32, sc + 32);
       tmem_ld_wait();
-      const bool full = key0 + KH - 1 <= pos_r && (window <= 0 || key0 > pos_r - window);
-      float mx0 = -INFINITY, mx1 = -INFINITY;      // of the raw scores (the scale is positive)
-      if (full) {
+      const bool full = key0 + kFaKeys - 1 <= pos_r && (window <= 0 || key0 > pos_r - window);
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // of the raw scores
+      if (full) {                                  // (the scale is positive)
 #pragma unroll
-        for (int i = 0; i < KH; i += 2) {
-          mx0 = fmaxf(mx0, sc[i]);
-          mx1 = fmaxf(mx1, sc[i + 1]);
-        }
+        for (int i = 0; i < kFaKeys; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], sc[i]);
       } else {
 #pragma unroll
-        for (int i = 0; i < KH; i += 2) {
+        for (int i = 0; i < kFaKeys; ++i) {
           const int key = key0 + i;
-          const bool seen0 = key <= pos_r && (window <= 0 || key > pos_r - window);
-          const bool seen1 = key + 1 <= pos_r && (window <= 0 || key + 1 > pos_r - window);
-          sc[i] = seen0 ? sc[i] : -INFINITY;
-          sc[i + 1] = seen1 ? sc[i + 1] : -INFINITY;
-          mx0 = fmaxf(mx0, sc[i]);
-          mx1 = fmaxf(mx1, sc[i + 1]);
+          const bool seen = key <= pos_r && (window <= 0 || key > pos_r - window);
+          sc[i] = seen ? sc[i] : -INFINITY;
+          mx4[i & 3] = fmaxf(mx4[i & 3], sc[i]);
         }
       }
-      float mx = fmaxf(mx0, mx1);
-      // the row's maximum is over both halves
-      xch[s][half][r] = mx;
-      __syncwarp();
-      if (lane == 0) mbar_arrive(pair_bar);
-      ok = mbar_wait(pair_bar, it & 1, status, 33);
-      if (!ok) break;
-      mx = fmaxf(mx, xch[s][half ^ 1][r]) * scale_log2;
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;
       // tcgen05.ld/st are warp-wide: if any row of the warp raises its reference, the whole warp
       // rescales (rows that keep theirs multiply by 1)
       const bool raise = mx > m_ref + kLazy;       // also the first page with a visible key
       const float alpha = raise ? ex2_approx(m_ref - mx) : 1.f;   // 0 while the reference is -inf
       if (it > 0 && __any_sync(0xffffffffu, raise)) {
-        // O holds pages 0..it-1 once their last P.V is done; scale this thread's half of the row
+        // O holds pages 0..it-1 once their last P.V is done
         const int u = it - 1;
         ok = mbar_wait(bar(12 + (u & 1)), (u >> 1) & 1, status, 34);
         if (!ok) break;
         tc_fence_after();
 #pragma unroll
-        for (int c = 0; c < DH; c += 16) {
-          float v[16];
-          tmem_ld16_nowait(lane_addr + kColO + DH * half + c, v);
+        for (int c = 0; c < D; c += 32) {
+          float v[32];
+          tmem_ld32_nowait(lane_addr + kColO + c, v);
           tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 16; ++i) v[i] *= alpha;
-          tmem_st16(lane_addr + kColO + DH * half + c, reinterpret_cast<const uint32_t*>(v));
+          for (int i = 0; i < 32; ++i) v[i] *= alpha;
+          tmem_st32(lane_addr + kColO + c, v);
         }
       }
       if (raise) {
@@ -265,20 +245,24 @@ attention_prefill_tc_kernel(bf16* __restrict__ out, const bf16* q, int q_row_str
         m_ref = mx;
       }
       const float neg_m = m_ref == -INFINITY ? 0.f : -m_ref;
-      float psum0 = 0.f, psum1 = 0.f;
-      uint32_t w[KH / 2];
+      float psum[4] = {0.f, 0.f, 0.f, 0.f};
+      // P over the scores it came from, 32 keys (16 columns) at a time so that the first store
+      // is under way while the second half is computed
 #pragma unroll
-      for (int i = 0; i < KH; i += 2) {
-        const float p0 = ex2_approx(fmaf(sc[i], scale_log2, neg_m));
-        const float p1 = ex2_approx(fmaf(sc[i + 1], scale_log2, neg_m));
-        psum0 += p0;
-        psum1 += p1;
-        __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
-        w[i / 2] = *reinterpret_cast<uint32_t*>(&h);
+      for (int h = 0; h < 2; ++h) {
+        uint32_t w[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          const float p0 = ex2_approx(fmaf(sc[32 * h + i], scale_log2, neg_m));
+          const float p1 = ex2_approx(fmaf(sc[32 * h + i + 1], scale_log2, neg_m));
+          psum[i & 2] += p0;
+          psum[(i & 2) + 1] += p1;
+          __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);
+          w[i / 2] = *reinterpret_cast<uint32_t*>(&hh);
+        }
+        tmem_st16(lane_addr + kColS + 64 * s + 16 * h, w);
       }
-      l_run += psum0 + psum1;
-      // P over the scores it came from: this half's 32 keys are 16 columns
-      tmem_st16(lane_addr + kColS + 64 * s + (KH / 2) * half, w);
+      l_run += (psum[0] + psum[1]) + (psum[2] + psum[3]);
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
@@ -293,18 +277,14 @@ attention_prefill_tc_kernel(bf16* __restrict__ out, const bf16* q, int q_row_str
 
   const int failed = __syncthreads_or(ok ? 0 : 1);
   if (!failed) {
-    if (tid < 2 * kFaRows) xch[0][half][r] = l_run;            // the two halves' sums
-    __syncthreads();
-    if (tid < 2 * kFaRows) {                       // whole warps: tcgen05.ld is warp-wide
-      const float l = xch[0][0][r] + xch[0][1][r];
-      const float inv = l > 0.f ? 1.f / l : 0.f;
+    if (tid < kFaRows) {                           // whole warps: tcgen05.ld is warp-wide
+      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
       const int row = min(r, n_rows - 1);
-      bf16* o = out + ((size_t)(t_first + row / group) * n_q_heads + kv_head * group + row % group) * D +
-                DH * half;
+      bf16* o = out + ((size_t)(t_first + row / group) * n_q_heads + kv_head * group + row % group) * D;
 #pragma unroll
-      for (int c = 0; c < DH; c += 32) {
+      for (int c = 0; c < D; c += 32) {
         float v[32];
-        tmem_ld32_nowait(lane_addr + kColO + DH * half + c, v);
+        tmem_ld32_nowait(lane_addr + kColO + c, v);
         tmem_ld_wait();
         if (r < n_rows) {
 #pragma unroll
@@ -325,7 +305,7 @@ attention_prefill_tc_kernel(bf16* __restrict__ out, const bf16* q, int q_row_str
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 8) tmem_dealloc(tmem_base, kTmemCols);
+  if (warp == 4) tmem_dealloc(tmem_base, kTmemCols);
 }
 
 template <int D>
