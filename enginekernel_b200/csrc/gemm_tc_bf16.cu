@@ -12,8 +12,11 @@
 //   * swapped (decode, 17..64 sequences): P = the weight matrix, Q = the activations, so
 //     the 128-row side of the MMA is filled with weight rows and the batch is the narrow
 //     N side; the tile is out^T and is stored transposed.  The work is bound by streaming
-//     the weights, so K is also split over blocks (grid.y); partial tiles go to scratch
-//     and the block that delivers the last partial of a tile adds them in split order.
+//     the weights, so K is also split over blocks (grid.y).  Up to 8 blocks of a tile form
+//     a thread-block cluster: each leaves its partial tile in its own shared memory and sums
+//     its share of the tile's columns over all of them, in split order, through distributed
+//     shared memory.  More splits than that go through scratch in global memory, and the
+//     block that delivers the last partial of a tile adds them in split order.
 //   * direct (prompts): P = activations, Q = weights, BN = 128 or 256.
 // Epilogues: bfloat16, 32-bit, or SwiGLU (the tile holds gate rows/columns in its first
 // half and the matching up rows/columns in its second half).
@@ -27,6 +30,7 @@ namespace ek {
 enum { TC_EPI_BF16 = 0, TC_EPI_F32 = 1, TC_EPI_SWIGLU = 2 };
 
 constexpr int kTcBM = 128;                    // rows of P per tile (TMEM lanes)
+constexpr int kTcMaxCluster = 8;              // blocks of a cluster (the portable limit)
 
 // Instruction descriptor: bfloat16 x bfloat16 -> float, both operands K-major, M = 128.
 __host__ __device__ constexpr uint32_t tc_idesc(int n) {
@@ -47,7 +51,7 @@ struct TcParams {
 };
 
 // --------------------------------------------------------------------------------- kernel
-template <int BN, int EPI, bool SWAP, int STAGES>
+template <int BN, int EPI, bool SWAP, int STAGES, bool CL>
 __global__ void __launch_bounds__(128, SWAP ? 2 : 1)
 gemm_tc_bf16_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q,
                     const TcParams prm) {
@@ -170,7 +174,64 @@ gemm_tc_bf16_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
   const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
   const int tile_linear = SWAP ? tile_p : (tile_q * gridDim.x + tile_p);
 
-  if (!failed) {
+  if (CL) {
+    // The blocks of this tile are one cluster.  Every block passes both barriers whatever
+    // happened to it, so that none waits for one that gave up.
+    float* red = (float*)smem;                 // [BN][128]; the operand tiles are dead
+    if (!failed) {
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 16) {
+        float v[16];
+        if (n_iter > 0) {
+          tmem_ld16(lane_addr + c0, v);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) v[i] = 0.f;
+        }
+#pragma unroll
+        for (int i = 0; i < 16; ++i) red[(c0 + i) * kTcBM + row] = v[i];
+      }
+    }
+    cluster_sync();
+    if (!failed) {
+      // this block's share: columns (sequences) split, split + n_split, ...
+      for (int m = split; m < prm.rows_q; m += n_split) {
+        // all loads first, then the sum in split order
+        float part[kTcMaxCluster], part_up[kTcMaxCluster];
+#pragma unroll
+        for (int sp = 0; sp < kTcMaxCluster; ++sp) {
+          part[sp] = sp < n_split ? ld_cluster_f32(&red[m * kTcBM + row], (unsigned)sp) : 0.f;
+          part_up[sp] = (EPI == TC_EPI_SWIGLU && sp < n_split && row < 64)
+                            ? ld_cluster_f32(&red[m * kTcBM + row + 64], (unsigned)sp) : 0.f;
+        }
+        float acc = part[0], acc_up = part_up[0];
+#pragma unroll
+        for (int sp = 1; sp < kTcMaxCluster; ++sp) {
+          if (sp < n_split) {
+            acc += part[sp];
+            acc_up += part_up[sp];
+          }
+        }
+        int n_out;
+        bool row_ok;
+        if (EPI == TC_EPI_SWIGLU) {
+          n_out = tile_p * 64 + row;
+          row_ok = row < 64 && n_out < prm.swiglu_half;
+          acc = acc / (1.f + __expf(-acc)) * acc_up;
+        } else {
+          n_out = tile_p * kTcBM + row;
+          row_ok = n_out < prm.rows_p;
+        }
+        if (row_ok) {
+          if (EPI == TC_EPI_F32) ((float*)prm.out)[(size_t)m * prm.ldo + n_out] = acc;
+          else ((bf16*)prm.out)[(size_t)m * prm.ldo + n_out] = __float2bfloat16_rn(acc);
+        }
+      }
+    } else {
+      for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+    }
+    cluster_sync();                            // nobody leaves while its partial may be read
+  } else if (!failed) {
     if (n_split > 1) {
       // partial tile -> scratch [tile][split][BN][128] (coalesced over rows)
       float* mine = prm.partials + ((size_t)tile_linear * n_split + split) * BN * kTcBM;
@@ -296,14 +357,15 @@ gemm_tc_bf16_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
   if (warp == 0) tmem_dealloc(tmem_base, kTmemCols);
 }
 
-template <int BN, int EPI, bool SWAP>
+template <int BN, int EPI, bool SWAP, bool CL = false>
 static int launch_tc(const CUtensorMap& mp, const CUtensorMap& mq, const TcParams& prm, dim3 grid,
                      cudaStream_t stream) {
-  // swapped: two blocks an SM (4 stages each); direct: one block an SM with a deep ring
-  constexpr int STAGES = SWAP ? 4 : (BN <= 128 ? 6 : 4);
+  // swapped: two blocks an SM, as many stages as their shared memory holds (a stage is 16 KB of
+  // weights and BN rows of activations); direct: one block an SM with a deep ring
+  constexpr int STAGES = SWAP ? (BN <= 16 ? 6 : BN <= 32 ? 5 : 4) : (BN <= 128 ? 6 : 4);
   constexpr size_t smem = 1024 + (size_t)STAGES * (kTcBM * kTcBK * 2 + BN * kTcBK * 2) +
                           (2 * STAGES + 1) * 8 + 16;
-  auto kernel = gemm_tc_bf16_kernel<BN, EPI, SWAP, STAGES>;
+  auto kernel = gemm_tc_bf16_kernel<BN, EPI, SWAP, STAGES, CL>;
   static bool configured[kMaxDevices] = {};     // the attribute is per device and sticks
   int device = 0;
   cudaError_t e = cudaGetDevice(&device);
@@ -315,6 +377,7 @@ static int launch_tc(const CUtensorMap& mp, const CUtensorMap& mq, const TcParam
     configured[device] = true;
   }
   prefer_carveout((const void*)kernel, 100);   // the operand ring wants all the shared memory
+  if (CL) return (int)launch_pdl_cluster(kernel, grid, dim3(128), smem, stream, (int)grid.y, mp, mq, prm);
   return (int)launch_pdl(kernel, grid, dim3(128), smem, stream, mp, mq, prm);
 }
 
@@ -322,11 +385,12 @@ static int launch_tc(const CUtensorMap& mp, const CUtensorMap& mq, const TcParam
 
 // out[M, N] = x[M, K] . w[N, K]^T  (epilogue 0/1) or out[M, N/2] = silu(x.wg^T) * (x.wu^T) with w =
 // [gate rows; up rows] (epilogue 2).  swap != 0: weights fill the 128-row MMA side (for
-// 1..64 rows of x); k_split blocks share a tile's K and need `partials` (at least
-// tiles * k_split * bn * 128 floats) and zeroed `tickets` (at least `tiles`).
+// 1..64 rows of x); k_split blocks share a tile's K: as a cluster if `cluster` != 0 and k_split is
+// at most 8, else through `partials` (at least tiles * k_split * bn * 128 floats) and zeroed
+// `tickets` (at least `tiles`).
 // K, ldx, ldw must be multiples of 8; `status` is one int on the device.
 EK_EXPORT int ek_gemm_tc_bf16(void* out, const void* x, const void* w, int M, int N, int K, int ldx,
-                              int ldw, int ldo, int epilogue, int swap, int k_split,
+                              int ldw, int ldo, int epilogue, int swap, int k_split, int cluster,
                               float* partials, unsigned int* tickets, long long partial_floats,
                               int n_tickets, int* status, cudaStream_t stream) {
   using namespace ek;
@@ -348,16 +412,24 @@ EK_EXPORT int ek_gemm_tc_bf16(void* out, const void* x, const void* w, int M, in
     const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
     const bool sw = epilogue == TC_EPI_SWIGLU;
     const int tiles = sw ? (N / 2 + 63) / 64 : (N + kTcBM - 1) / kTcBM;
-    if (k_split > 1 && (!partials || !tickets || tiles > n_tickets ||
-                        (long long)tiles * k_split * bn * kTcBM > partial_floats))
-      k_split = 1;
     prm.k_blocks_per_split = (k_blocks + k_split - 1) / k_split;
     k_split = (k_blocks + prm.k_blocks_per_split - 1) / prm.k_blocks_per_split;
+    const bool clustered = cluster && k_split > 1 && k_split <= kTcMaxCluster;
+    if (k_split > 1 && !clustered && (!partials || !tickets || tiles > n_tickets ||
+                                      (long long)tiles * k_split * bn * kTcBM > partial_floats)) {
+      k_split = 1;
+      prm.k_blocks_per_split = k_blocks;
+    }
     prm.rows_p = N; prm.rows_q = M;
     if ((rc = tensor_map(w, N, K, ldw, sw ? 64 : kTcBM, &mp))) return rc;
     if ((rc = tensor_map(x, M, K, ldx, bn, &mq))) return rc;
     dim3 grid(tiles, k_split, 1);
 #define EK_SWAP(BN)                                                                              \
+  if (bn == BN && clustered) {                                                                   \
+    if (epilogue == TC_EPI_BF16) return launch_tc<BN, TC_EPI_BF16, true, true>(mp, mq, prm, grid, stream); \
+    if (epilogue == TC_EPI_F32) return launch_tc<BN, TC_EPI_F32, true, true>(mp, mq, prm, grid, stream);   \
+    return launch_tc<BN, TC_EPI_SWIGLU, true, true>(mp, mq, prm, grid, stream);                  \
+  }                                                                                              \
   if (bn == BN) {                                                                                \
     if (epilogue == TC_EPI_BF16) return launch_tc<BN, TC_EPI_BF16, true>(mp, mq, prm, grid, stream); \
     if (epilogue == TC_EPI_F32) return launch_tc<BN, TC_EPI_F32, true>(mp, mq, prm, grid, stream);   \

@@ -347,8 +347,8 @@ def gemv_bf16(out, x, w, epilogue=EPI_BF16, n_rows=None, warps=None, blocks=None
 
 
 _gemm_tc = Function("gemm_tc_bf16", "ek_gemm_tc_bf16",
-                    [_P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P,
-                     c_longlong, c_int, _P, _P])
+                    [_P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                     _P, _P, c_longlong, c_int, _P, _P])
 _tc_status = {}
 TC_SWAP_MAX_ROWS = 64
 
@@ -369,11 +369,16 @@ def check_tc_status(device):
         raise KernelError(f"gemm_tc_bf16: a barrier wait timed out (code {code}); results are invalid")
 
 
-def gemm_tc_bf16(out, x, w, epilogue=EPI_BF16, n_rows=None, swap=None, k_split=None):
+TC_MAX_CLUSTER = 8          # blocks of a thread-block cluster (the portable limit)
+
+
+def gemm_tc_bf16(out, x, w, epilogue=EPI_BF16, n_rows=None, swap=None, k_split=None, cluster=True):
     """out = x . w^T (or the SwiGLU of it) on tcgen05 tensor cores with TMA-staged operands.
 
     ``swap`` (default: at most 64 rows) puts the weights on the 128-row side of the MMA and
-    splits K over ``k_split`` blocks; otherwise 128 x 128 tiles of the output.
+    splits K over ``k_split`` blocks; otherwise 128 x 128 tiles of the output.  Up to 8 splits
+    add their partial tiles through the distributed shared memory of a thread-block cluster
+    (``cluster``), more of them through scratch in global memory.
     """
     _need_cuda(out, x, w)
     m = n_rows if n_rows is not None else x.shape[0]
@@ -394,13 +399,13 @@ def gemm_tc_bf16(out, x, w, epilogue=EPI_BF16, n_rows=None, swap=None, k_split=N
     if k_split is None:
         k_split = 1
         if swap:
-            # two blocks fit an SM: fill those 296 places, keep at least 8 K blocks a block, and
-            # split less when the partial tiles are wide
+            # two blocks fit an SM: fill those 296 places, keep at least 8 K blocks a block, stay
+            # within one cluster, and split less when the partial tiles are wide
             tiles = -(-n_out // (64 if epilogue == EPI_SWIGLU else 128))
             k_blocks = -(-k // 64)
-            k_split = max(1, min(2 * SM_COUNT // tiles, k_blocks // 8, 16 if m <= 16 else 4))
+            k_split = max(1, min(2 * SM_COUNT // tiles, k_blocks // 8, TC_MAX_CLUSTER if m <= 16 else 4))
     _gemm_tc(_ptr(out), _ptr(x), _ptr(w), m, n, k, x.stride(0), w.stride(0), out.stride(0),
-             epilogue, 1 if swap else 0, k_split, _ptr(partials), _ptr(tickets),
+             epilogue, 1 if swap else 0, k_split, 1 if cluster else 0, _ptr(partials), _ptr(tickets),
              _GEMV_PARTIAL_FLOATS, _GEMV_TICKETS, _ptr(tc_status(x.device)), _stream())
 
 

@@ -435,19 +435,26 @@ def test_gemm_tc_swapped(m, n, k_):
     x = rnd(m, k_, dtype=torch.bfloat16, seed=1)
     w = rnd(n, k_, dtype=torch.bfloat16, seed=2, scale=0.05)
     want = x.double() @ w.double().t()
-    for k_split in (1, 3, None):
+    # K split over the blocks of a cluster (up to 8), through scratch in global memory (forced, or
+    # more than 8 splits), or not at all
+    for k_split, cluster in ((1, True), (3, True), (3, False), (8, True), (11, True), (None, True)):
         out32 = torch.full((m, n), 9.0, device=DEV)
-        k.gemm_tc_bf16(out32, x, w, k.EPI_F32, swap=True, k_split=k_split)
+        k.gemm_tc_bf16(out32, x, w, k.EPI_F32, swap=True, k_split=k_split, cluster=cluster)
         k.check_tc_status(DEV)
-        assert rel(out32, want) <= 1e-5, k_split
+        assert rel(out32, want) <= 1e-5, (k_split, cluster)
         out16 = torch.empty(m, n, dtype=torch.bfloat16, device=DEV)
-        k.gemm_tc_bf16(out16, x, w, k.EPI_BF16, swap=True, k_split=k_split)
+        k.gemm_tc_bf16(out16, x, w, k.EPI_BF16, swap=True, k_split=k_split, cluster=cluster)
         assert rel(out16, want) <= 4e-3
         inter = n // 2
         act = torch.empty(m, inter, dtype=torch.bfloat16, device=DEV)
-        k.gemm_tc_bf16(act, x, w, k.EPI_SWIGLU, swap=True, k_split=k_split)
+        k.gemm_tc_bf16(act, x, w, k.EPI_SWIGLU, swap=True, k_split=k_split, cluster=cluster)
         g, u = want[:, :inter], want[:, inter:]
-        assert rel(act, g / (1 + torch.exp(-g)) * u) <= 4e-3
+        assert rel(act, g / (1 + torch.exp(-g)) * u) <= 4e-3, (k_split, cluster)
+    # the same split gives the same bits whichever way the partial tiles are added
+    a32, b32 = torch.empty(m, n, device=DEV), torch.empty(m, n, device=DEV)
+    k.gemm_tc_bf16(a32, x, w, k.EPI_F32, swap=True, k_split=3, cluster=True)
+    k.gemm_tc_bf16(b32, x, w, k.EPI_F32, swap=True, k_split=3, cluster=False)
+    assert torch.equal(a32, b32)
     k.check_tc_status(DEV)
     _, tickets = k.gemv_scratch(DEV)
     assert int(tickets.abs().sum()) == 0
