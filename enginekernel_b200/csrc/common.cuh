@@ -181,6 +181,15 @@ inline cudaError_t launch_pdl_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 
 __device__ __forceinline__ void cluster_sync() {
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
+// Four floats (16-byte aligned) at the same shared-memory offset in block `rank` of this cluster.
+__device__ __forceinline__ float4 ld_cluster_f32x4(const float* own, unsigned rank) {
+  unsigned a = (unsigned)__cvta_generic_to_shared(own), r;
+  float4 v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(rank));
+  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(r) : "memory");
+  return v;
+}
 // A 32-bit float at the same shared-memory offset in block `rank` of this cluster.
 __device__ __forceinline__ float ld_cluster_f32(const float* own, unsigned rank) {
   unsigned a = (unsigned)__cvta_generic_to_shared(own), r;

@@ -87,7 +87,15 @@ __global__ void add_residual_kernel(float* __restrict__ resid, const T* __restri
 }
 
 // out[r, i] = silu(gu[r, i]) * gu[r, inter + i]    (engine/ek_kernels.py:125-143)
-// VEC: inter is a multiple of 4; a thread handles four neighbours.
+// VEC: inter is a multiple of 4; a thread handles four neighbours.  A 16-bit result takes the
+// fast exponential and division (a few 32-bit ulps, far below its own rounding); a 32-bit
+// result the exact ones.
+template <typename T>
+__device__ __forceinline__ float silu_of(float g) {
+  if (sizeof(T) == 2) return __fdividef(g, 1.f + __expf(-g));
+  return g / (1.f + expf(-g));
+}
+
 template <typename T, bool VEC>
 __global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gu, int inter) {
   const size_t r = blockIdx.y;
@@ -97,14 +105,34 @@ __global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gu, i
     const int i = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
     if (i >= inter) return;
     const float4 g = Vec4<T>::load(g_row + i), u = Vec4<T>::load(g_row + inter + i);
-    Vec4<T>::store(o_row + i, make_float4(g.x / (1.f + expf(-g.x)) * u.x, g.y / (1.f + expf(-g.y)) * u.y,
-                                          g.z / (1.f + expf(-g.z)) * u.z, g.w / (1.f + expf(-g.w)) * u.w));
+    Vec4<T>::store(o_row + i, make_float4(silu_of<T>(g.x) * u.x, silu_of<T>(g.y) * u.y,
+                                          silu_of<T>(g.z) * u.z, silu_of<T>(g.w) * u.w));
   } else {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= inter) return;
     const float g = to_f<T>(g_row[i]), u = to_f<T>(g_row[inter + i]);
-    o_row[i] = from_f<T>(g / (1.f + expf(-g)) * u);
+    o_row[i] = from_f<T>(silu_of<T>(g) * u);
   }
+}
+
+// The same for bfloat16 rows whose halves start on 16-byte boundaries: eight neighbours a thread.
+__global__ void silu_mul_wide_kernel(bf16* __restrict__ out, const bf16* __restrict__ gu, int inter) {
+  const size_t r = blockIdx.y;
+  const int i = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  if (i >= inter) return;
+  const bf16* g_row = gu + r * 2 * inter;
+  const uint4 g = *reinterpret_cast<const uint4*>(g_row + i);
+  const uint4 u = *reinterpret_cast<const uint4*>(g_row + inter + i);
+  const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&g);
+  const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&u);
+  uint32_t w[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float2 a = __bfloat1622float2(g2[j]), b = __bfloat1622float2(u2[j]);
+    __nv_bfloat162 h = __floats2bfloat162_rn(silu_of<bf16>(a.x) * b.x, silu_of<bf16>(a.y) * b.y);
+    w[j] = *reinterpret_cast<uint32_t*>(&h);
+  }
+  *reinterpret_cast<uint4*>(out + r * inter + i) = make_uint4(w[0], w[1], w[2], w[3]);
 }
 
 template <typename T>
@@ -130,6 +158,11 @@ template <typename T>
 static int launch_silu_mul(void* out, const void* gu, int rows, int inter, cudaStream_t stream) {
   if (rows <= 0 || inter <= 0) return 0;
   if (rows > 65535) return EK_ERR_ARG;
+  if (sizeof(T) == 2 && inter % 8 == 0 && ((uintptr_t)out % 16) == 0 && ((uintptr_t)gu % 16) == 0) {
+    dim3 wide((inter / 8 + 255) / 256, rows);
+    silu_mul_wide_kernel<<<wide, 256, 0, stream>>>((bf16*)out, (const bf16*)gu, inter);
+    EK_RETURN_LAUNCH_STATUS();
+  }
   const bool vec = inter % 4 == 0 && ((uintptr_t)out % 8) == 0 && ((uintptr_t)gu % 8) == 0;
   const int per_thread = vec ? 4 : 1;
   dim3 grid((inter / per_thread + 255) / 256 + (inter % per_thread ? 1 : 0), rows);

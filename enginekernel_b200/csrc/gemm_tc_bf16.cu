@@ -37,6 +37,9 @@ __host__ __device__ constexpr uint32_t tc_idesc(int n) {
   return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(kTcBM >> 4) << 24);
 }
 
+// silu for a bfloat16 result: the fast exponential and division are good to a few 32-bit ulps
+__device__ __forceinline__ float silu_fast(float x) { return __fdividef(x, 1.f + __expf(-x)); }
+
 struct TcParams {
   void* out;            // [M_out, N_out] row-major, ldo elements between rows
   int ldo;
@@ -174,13 +177,17 @@ gemm_tc_bf16_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
   const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
   const int tile_linear = SWAP ? tile_p : (tile_q * gridDim.x + tile_p);
 
-  if (CL) {
-    // The blocks of this tile are one cluster.  Every block passes both barriers whatever
-    // happened to it, so that none waits for one that gave up.
-    float* red = (float*)smem;                 // [BN][128]; the operand tiles are dead
+  if (SWAP && (CL || n_split == 1)) {
+    // The tile goes to shared memory as [sequence][weight row] (the operand tiles are dead), and
+    // from there each output is put together: the sum over the blocks of the cluster in split
+    // order, SwiGLU of a gate row and its up row 64 further on, one rounding, one store.  A
+    // block takes the sequences split, split + n_split, ...  Every block of a cluster passes
+    // both barriers whatever happened to it, so that none waits for one that gave up.
+    float* red = (float*)smem;
+    constexpr int NS = CL ? kTcMaxCluster : 1;
     if (!failed) {
 #pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 16) {
+      for (int c0 = 0; c0 < BN && c0 < prm.rows_q; c0 += 16) {
         float v[16];
         if (n_iter > 0) {
           tmem_ld16(lane_addr + c0, v);
@@ -192,45 +199,90 @@ gemm_tc_bf16_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
         for (int i = 0; i < 16; ++i) red[(c0 + i) * kTcBM + row] = v[i];
       }
     }
-    cluster_sync();
+    if (CL) cluster_sync(); else __syncthreads();
     if (!failed) {
-      // this block's share: columns (sequences) split, split + n_split, ...
-      for (int m = split; m < prm.rows_q; m += n_split) {
-        // all loads first, then the sum in split order
-        float part[kTcMaxCluster], part_up[kTcMaxCluster];
+      // A thread takes 4 neighbouring weight rows (one 16-byte load a block of the cluster) of one
+      // sequence; a warp covers the tile's rows for one sequence (two with SwiGLU, whose outputs
+      // are the 64 gate rows), the block 4 (8) sequences a pass.  All loads of two passes are
+      // issued before the first sum.
+      constexpr int R = EPI == TC_EPI_SWIGLU ? 64 : kTcBM;     // output rows of the tile
+      constexpr int MPW = 32 / (R / 4);                         // sequences a warp and pass
+      constexpr int P = CL ? 2 : 4;                             // passes a batch
+      const int step = CL ? n_split : 1, first = CL ? split : 0;
+      const int owned = prm.rows_q > first ? (prm.rows_q - first + step - 1) / step : 0;
+      const int sub = lane / (R / 4), r0 = 4 * (lane % (R / 4));
+      const bool wide_ok = (prm.ldo & 3) == 0 && ((uintptr_t)prm.out & 15) == 0;
+      auto fetch4 = [&](const float* p, int sp) {
+        return CL ? ld_cluster_f32x4(p, (unsigned)sp) : *reinterpret_cast<const float4*>(p);
+      };
+#pragma unroll 1
+      for (int base = 0; base < owned; base += P * 4 * MPW) {
+        float4 part[P][NS], part_up[P][NS];
 #pragma unroll
-        for (int sp = 0; sp < kTcMaxCluster; ++sp) {
-          part[sp] = sp < n_split ? ld_cluster_f32(&red[m * kTcBM + row], (unsigned)sp) : 0.f;
-          part_up[sp] = (EPI == TC_EPI_SWIGLU && sp < n_split && row < 64)
-                            ? ld_cluster_f32(&red[m * kTcBM + row + 64], (unsigned)sp) : 0.f;
-        }
-        float acc = part[0], acc_up = part_up[0];
+        for (int ps = 0; ps < P; ++ps) {
+          const int idx = base + (ps * 4 + warp) * MPW + sub;
+          const int m = first + idx * step;
 #pragma unroll
-        for (int sp = 1; sp < kTcMaxCluster; ++sp) {
-          if (sp < n_split) {
-            acc += part[sp];
-            acc_up += part_up[sp];
+          for (int sp = 0; sp < NS; ++sp) {
+            const bool live = idx < owned && sp < n_split;
+            part[ps][sp] = live ? fetch4(&red[m * kTcBM + r0], sp) : make_float4(0.f, 0.f, 0.f, 0.f);
+            if (EPI == TC_EPI_SWIGLU)
+              part_up[ps][sp] = live ? fetch4(&red[m * kTcBM + r0 + 64], sp) : make_float4(0.f, 0.f, 0.f, 0.f);
           }
         }
-        int n_out;
-        bool row_ok;
-        if (EPI == TC_EPI_SWIGLU) {
-          n_out = tile_p * 64 + row;
-          row_ok = row < 64 && n_out < prm.swiglu_half;
-          acc = acc / (1.f + __expf(-acc)) * acc_up;
-        } else {
-          n_out = tile_p * kTcBM + row;
-          row_ok = n_out < prm.rows_p;
-        }
-        if (row_ok) {
-          if (EPI == TC_EPI_F32) ((float*)prm.out)[(size_t)m * prm.ldo + n_out] = acc;
-          else ((bf16*)prm.out)[(size_t)m * prm.ldo + n_out] = __float2bfloat16_rn(acc);
+#pragma unroll
+        for (int ps = 0; ps < P; ++ps) {
+          const int idx = base + (ps * 4 + warp) * MPW + sub;
+          const int m = first + idx * step;
+          float4 acc = part[ps][0];
+          float4 up = EPI == TC_EPI_SWIGLU ? part_up[ps][0] : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+          for (int sp = 1; sp < NS; ++sp) {
+            if (sp < n_split) {
+              acc.x += part[ps][sp].x; acc.y += part[ps][sp].y;
+              acc.z += part[ps][sp].z; acc.w += part[ps][sp].w;
+              if (EPI == TC_EPI_SWIGLU) {
+                up.x += part_up[ps][sp].x; up.y += part_up[ps][sp].y;
+                up.z += part_up[ps][sp].z; up.w += part_up[ps][sp].w;
+              }
+            }
+          }
+          int n_out, n_limit;
+          if (EPI == TC_EPI_SWIGLU) {
+            n_out = tile_p * 64 + r0;
+            n_limit = prm.swiglu_half;
+            acc.x = silu_fast(acc.x) * up.x; acc.y = silu_fast(acc.y) * up.y;
+            acc.z = silu_fast(acc.z) * up.z; acc.w = silu_fast(acc.w) * up.w;
+          } else {
+            n_out = tile_p * kTcBM + r0;
+            n_limit = prm.rows_p;
+          }
+          if (idx < owned && n_out < n_limit) {
+            const float v[4] = {acc.x, acc.y, acc.z, acc.w};
+            if (EPI == TC_EPI_F32) {
+              float* o = (float*)prm.out + (size_t)m * prm.ldo + n_out;
+              if (n_out + 4 <= n_limit && wide_ok) {
+                *reinterpret_cast<float4*>(o) = acc;
+              } else {
+                for (int i = 0; i < 4 && n_out + i < n_limit; ++i) o[i] = v[i];
+              }
+            } else {
+              bf16* o = (bf16*)prm.out + (size_t)m * prm.ldo + n_out;
+              if (n_out + 4 <= n_limit && wide_ok) {
+                __nv_bfloat162 lo = __floats2bfloat162_rn(v[0], v[1]), hi = __floats2bfloat162_rn(v[2], v[3]);
+                *reinterpret_cast<uint2*>(o) = make_uint2(*reinterpret_cast<uint32_t*>(&lo),
+                                                          *reinterpret_cast<uint32_t*>(&hi));
+              } else {
+                for (int i = 0; i < 4 && n_out + i < n_limit; ++i) o[i] = __float2bfloat16_rn(v[i]);
+              }
+            }
+          }
         }
       }
     } else {
       for (int i = 0; i < 2000; ++i) __nanosleep(1000);
     }
-    cluster_sync();                            // nobody leaves while its partial may be read
+    if (CL) cluster_sync();                    // nobody leaves while its partial may be read
   } else if (!failed) {
     if (n_split > 1) {
       // partial tile -> scratch [tile][split][BN][128] (coalesced over rows)
@@ -280,7 +332,7 @@ gemm_tc_bf16_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
         if (EPI == TC_EPI_SWIGLU && !SWAP) {
           fetch(c0 + BN / 2, u);               // the matching up columns
 #pragma unroll
-          for (int i = 0; i < 16; ++i) v[i] = v[i] / (1.f + __expf(-v[i])) * u[i];
+          for (int i = 0; i < 16; ++i) v[i] = silu_fast(v[i]) * u[i];
         }
         if (EPI == TC_EPI_SWIGLU && SWAP) {
           // rows 64..127 hold the up rows of the gate rows 0..63: pass them through shared memory
@@ -292,7 +344,7 @@ gemm_tc_bf16_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
           __syncthreads();
           if (row < 64) {
 #pragma unroll
-            for (int i = 0; i < 16; ++i) v[i] = v[i] / (1.f + __expf(-v[i])) * xch[row * 16 + i];
+            for (int i = 0; i < 16; ++i) v[i] = silu_fast(v[i]) * xch[row * 16 + i];
           }
         }
         if (SWAP) {

@@ -400,10 +400,10 @@ def gemm_tc_bf16(out, x, w, epilogue=EPI_BF16, n_rows=None, swap=None, k_split=N
         k_split = 1
         if swap:
             # two blocks fit an SM: fill those 296 places, keep at least 8 K blocks a block, stay
-            # within one cluster, and split less when the partial tiles are wide
+            # within one cluster
             tiles = -(-n_out // (64 if epilogue == EPI_SWIGLU else 128))
             k_blocks = -(-k // 64)
-            k_split = max(1, min(2 * SM_COUNT // tiles, k_blocks // 8, TC_MAX_CLUSTER if m <= 16 else 4))
+            k_split = max(1, min(2 * SM_COUNT // tiles, k_blocks // 8, TC_MAX_CLUSTER))
     _gemm_tc(_ptr(out), _ptr(x), _ptr(w), m, n, k, x.stride(0), w.stride(0), out.stride(0),
              epilogue, 1 if swap else 0, k_split, 1 if cluster else 0, _ptr(partials), _ptr(tickets),
              _GEMV_PARTIAL_FLOATS, _GEMV_TICKETS, _ptr(tc_status(x.device)), _stream())

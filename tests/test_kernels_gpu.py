@@ -75,7 +75,7 @@ def test_embed_and_silu_mul(dtype):
     k.embed(out, table, ids, 5)
     assert torch.equal(out[:5], table[ids.long()].float()) and out[5].abs().sum() == 0
 
-    for rows, inter in ((1, 176), (19, 9728), (4, 1001)):
+    for rows, inter in ((1, 176), (19, 9728), (4, 1001), (3, 1004)):
         gu = rnd(rows, 2 * inter, dtype=dtype, seed=5, scale=2.0)
         act = torch.empty(rows, inter, dtype=dtype, device=DEV)
         k.silu_mul(act, gu)
