@@ -206,6 +206,38 @@ def attention_decode_bf16(out, q, n_tokens, positions, token_slot, k_pages, v_pa
                       n_splits, keys_per_split, _ptr(part_acc), _ptr(part_ml), _stream())
 
 
+_attn_decode_tma = Function("attention_decode_tma", "ek_attention_decode_tma",
+                            [_P, _P, c_int, _P, _P, _P, _P, c_int, _P, c_int, c_int, c_int, c_int, c_int,
+                             c_float, c_int, c_int, _P, _P])
+DECODE_TMA_MAX_SPLITS = 8
+
+
+def attention_decode_tma_supported(dtype, head_dim, n_q_heads, n_kv_heads):
+    return dtype == torch.bfloat16 and head_dim in (64, 128) and n_q_heads // n_kv_heads <= 16
+
+
+def attention_decode_tma(out, q, n_tokens, positions, token_slot, k_pages, v_pages, block_table,
+                         n_q_heads, n_kv_heads, head_dim, scale, window=None, n_splits=1):
+    """One new token per sequence (bfloat16, head size 64 or 128, at most 16 heads a group): the
+    cache pages come by TMA, started before the kernel ahead has finished; ``n_splits`` (1 to 8)
+    blocks share a token's pages and merge inside a thread-block cluster."""
+    _need_cuda(out, q, positions, token_slot, k_pages, v_pages, block_table)
+    _need(attention_decode_tma_supported(q.dtype, head_dim, n_q_heads, n_kv_heads),
+          "attention_decode_tma: bfloat16, head size 64 or 128, at most 16 query heads a KV head")
+    _need(out.dtype == q.dtype == k_pages.dtype, "attention: one dtype for q, cache and out")
+    _need(out.is_contiguous() and out.shape[-1] == n_q_heads * head_dim, "attention: out [T, NQ*D]")
+    _need(q.stride(-1) == 1 and q.stride(0) % 2 == 0 and q.data_ptr() % 4 == 0,
+          "attention: dense, 4-byte aligned q rows")
+    _need(k_pages.is_contiguous() and v_pages.is_contiguous() and k_pages.dim() == 4
+          and k_pages.shape[1:] == (n_kv_heads, PAGE, head_dim), "attention: pages [P, NKV, 64, D]")
+    _need(1 <= n_splits <= DECODE_TMA_MAX_SPLITS, "attention_decode_tma: 1 to 8 splits")
+    _need(n_tokens <= 65535, "attention_decode_tma: at most 65535 tokens a call")
+    _attn_decode_tma(_ptr(out), _ptr(q), q.stride(0), _ptr(positions), _ptr(token_slot),
+                     _ptr(k_pages), _ptr(v_pages), k_pages.shape[0], _ptr(block_table),
+                     block_table.stride(0), n_tokens, n_q_heads, n_kv_heads, head_dim, float(scale),
+                     int(window or 0), n_splits, _ptr(tc_status(q.device)), _stream())
+
+
 _attn_prefill_bf16 = Function("attention_prefill_bf16", "ek_attention_prefill_bf16",
                               [_P, _P, c_int, _P, _P, _P, c_int, c_int, _P, _P, _P, c_int, c_int,
                                c_int, c_int, c_float, c_int, _P])

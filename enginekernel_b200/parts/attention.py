@@ -101,6 +101,18 @@ class Attention(Mixer):
                 entry.k_pages, entry.v_pages, entry.block_table, self.num_heads, self.num_kv_heads,
                 self.head_dim, self.scale, self.window)
             return
+        if ctx.is_decode and t <= 65535 and kernels.attention_decode_tma_supported(
+                self.dtype, self.head_dim, self.num_heads, self.num_kv_heads):
+            # blocks = tokens x KV heads x splits, two fit an SM; a split takes whole pages and the
+            # splits of a token are one cluster
+            blocks = t * self.num_kv_heads
+            pages = -(-visible // kernels.PAGE)
+            splits = max(1, min(2 * SM_COUNT // blocks, pages, kernels.DECODE_TMA_MAX_SPLITS))
+            kernels.attention_decode_tma(
+                out, qkv, t, ctx.positions, ctx.token_slot, entry.k_pages, entry.v_pages,
+                entry.block_table, self.num_heads, self.num_kv_heads, self.head_dim, self.scale,
+                self.window, splits)
+            return
         if fast_decode:
             # blocks = tokens x KV heads (x 16-row blocks of the group); three fit an SM.  Split
             # the keys so that the blocks just fill the machine once, or about twice when one

@@ -324,6 +324,49 @@ def test_attention_decode_bf16(nq, nkv, d):
             assert rel(out[i], want) <= TOL[dtype], (window, splits, i)
 
 
+@pytest.mark.parametrize("nq,nkv,d", [(6, 3, 64), (32, 8, 128), (5, 5, 64), (16, 1, 128), (40, 4, 128),
+                                      (3, 1, 64)])
+def test_attention_decode_tma(nq, nkv, d):
+    """The TMA-fed decode kernel: groups of 1 to 16 heads, both head sizes, windows, 1 to 8 splits
+    as clusters (more splits than a short sequence has pages), finished rows, one far key."""
+    k = K()
+    dtype = torch.bfloat16
+    lens = [1, 64, 65, 1100, 130, 16, 17]
+    pages = Pages(len(lens), max(lens), nkv, d, dtype, seed=5)
+    kv = []
+    for s, n in enumerate(lens):
+        keys, vals = rnd(n, nkv, d, dtype=dtype, seed=10 + s), rnd(n, nkv, d, dtype=dtype, seed=20 + s)
+        pages.fill(s, keys, vals)
+        kv.append((keys, vals))
+    toks = [(0, 0), (1, 63), (2, 64), (3, 1099), (3, 0), (3, 255), (4, 129), (4, 64), (2, -1),
+            (5, 15), (6, 16), (3, 300), (3, 1023), (3, 1024)]
+    t = len(toks)
+    q = rnd(t, nq * d + 2 * nkv * d, dtype=dtype, seed=30)
+    q[3, :d] = (kv[3][0][3, 0].float() * 4).to(dtype)          # one far key dominates
+    q[11, (nq - 1) * d:nq * d] = (kv[3][0][299, nkv - 1].float() * 4).to(dtype)
+    positions = torch.tensor([p for _, p in toks], dtype=torch.int32, device=DEV)
+    slots = torch.tensor([s for s, _ in toks], dtype=torch.int32, device=DEV)
+    scale = 1.0 / math.sqrt(d)
+    for window, splits in ((None, 1), (None, 2), (None, 5), (None, 8), (100, 1), (64, 3), (1, 1),
+                           (17, 8), (700, 4)):
+        out = torch.full((t, nq * d), 7.0, dtype=dtype, device=DEV)
+        k.attention_decode_tma(out, q, t, positions, slots, pages.k, pages.v, pages.table, nq, nkv, d,
+                               scale, window, splits)
+        k.check_tc_status(DEV)
+        for i, (s, p) in enumerate(toks):
+            if p < 0:
+                assert out[i].abs().max().item() == 0
+                continue
+            want = ref_attention(q[i, :nq * d].view(nq, d).cpu(), kv[s][0].cpu(), kv[s][1].cpu(), p,
+                                 scale, window)
+            assert rel(out[i], want) <= TOL[dtype], (window, splits, i)
+    # it refuses what it cannot take
+    from enginekernel_b200.ops.lib import KernelError
+    with pytest.raises(KernelError):
+        k.attention_decode_tma(out, q, t, positions, slots, pages.k, pages.v, pages.table, nq, nkv, d,
+                               scale, None, 9)
+
+
 @pytest.mark.parametrize("nq,nkv,d", [(4, 2, 16), (6, 2, 48), (32, 8, 128), (5, 5, 80), (16, 1, 256),
                                       (3, 1, 64), (8, 2, 128), (16, 2, 64), (4, 4, 128), (64, 1, 64)])
 def test_attention_prefill_bf16(nq, nkv, d):
