@@ -118,6 +118,7 @@ attention_decode_tma_kernel(bf16* __restrict__ out, const bf16* q, int q_row_str
     // ------------------------------------------------------------------- TMA producer
     const int* table = block_table + (size_t)(pos >= 0 ? token_slot[t] : 0) * table_stride;
     bool waited = false;
+    const uint64_t stream_policy = l2_policy_evict_first();   // a page is read once a step
     for (int i = 0; i < n_pages; ++i) {
       const int s = i % STAGES;
       const int pg = pg_first + i;
@@ -134,8 +135,8 @@ attention_decode_tma_kernel(bf16* __restrict__ out, const bf16* q, int q_row_str
       mbar_expect_tx(full(s), kStage);
 #pragma unroll
       for (int j = 0; j < DB; ++j) {
-        tma_load_2d(dst + j * kSub, &map_k, 64 * j, row, full(s));
-        tma_load_2d(dst + (DB + j) * kSub, &map_v, 64 * j, row, full(s));
+        tma_load_2d_hint(dst + j * kSub, &map_k, 64 * j, row, full(s), stream_policy);
+        tma_load_2d_hint(dst + (DB + j) * kSub, &map_v, 64 * j, row, full(s), stream_policy);
       }
     }
   } else if (warp < kDtWarps) {

@@ -112,12 +112,17 @@ gemm_tc_bf16_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
     } else {
       q_row0 = tile_q * BN;
     }
+    const uint64_t stream_policy = l2_policy_evict_first();
     auto load_p = [&](int it) {
       const int s = it % STAGES;
       const uint32_t full = full0 + 8 * s, pd = smem_u32(p_tiles + s * kBytesP);
       const int k0 = (kb_begin + it) * kTcBK;
-      tma_load_2d(pd, &map_p, k0, p_row0, full);
-      if (EPI == TC_EPI_SWIGLU && SWAP) tma_load_2d(pd + kBytesP / 2, &map_p, k0, p_row1, full);
+      if (SWAP) {                              // the weights are read once: first out of L2
+        tma_load_2d_hint(pd, &map_p, k0, p_row0, full, stream_policy);
+        if (EPI == TC_EPI_SWIGLU) tma_load_2d_hint(pd + kBytesP / 2, &map_p, k0, p_row1, full, stream_policy);
+      } else {
+        tma_load_2d(pd, &map_p, k0, p_row0, full);
+      }
     };
     auto load_q = [&](int it) {
       const int s = it % STAGES;
