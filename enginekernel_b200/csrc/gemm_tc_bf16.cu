@@ -51,6 +51,19 @@ struct TcParams {
   float* partials;      // split-K scratch [tile][split][BN][128]
   unsigned int* tickets;
   int* status;          // 0, or the code of the first wait that timed out
+  // A norm deferred to this product (swapped form): the activations are the residual stream
+  // times the norm's gain, and each sequence's 1/rms comes from the sums of squares that the
+  // product before left per 128-column tile.  The result is scaled by it.
+  const float* ss_in;   // [rows_q][ss_tiles], or null
+  int ss_tiles;
+  float ss_inv_size, eps;
+  // The residual add and the next norm's share moved into this product (swapped form, bfloat16
+  // result): stream += result in 32-bit; `out` gets stream * next_gain; ss_out[m][tile] gets the
+  // tile's sum of stream^2.
+  float* stream;        // [rows_q][ld_stream], or null
+  int ld_stream;
+  const float* next_gain;   // [rows_p]
+  float* ss_out;        // [rows_q][gridDim.x]
 };
 
 // --------------------------------------------------------------------------------- kernel
@@ -69,6 +82,7 @@ gemm_tc_bf16_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
   uint64_t* bars = (uint64_t*)(q_tiles + STAGES * kBytesQ);   // full[STAGES], empty[STAGES], accum
   uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES + 1);
   __shared__ int is_last;
+  __shared__ float rstd_s[64];                 // 1/rms of each sequence (a norm deferred to here)
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int tile_p = blockIdx.x;               // 128-row tile of P
@@ -173,6 +187,26 @@ gemm_tc_bf16_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
   // -------------------------------------------------------------------- epilogue (all warps)
   if (tid != 0) pdl_wait();                    // before any global write (thread 0 waited above)
   __syncwarp();
+  if (SWAP && prm.ss_in != nullptr) {
+    // two threads a sequence, 16 tiles each a round, all loads of a round in flight together; the
+    // order of the sum is fixed, so every block gets the same 1/rms
+    const int m = tid >> 1, h = tid & 1;
+    float ss = 0.f;
+    for (int t0 = 0; t0 < prm.ss_tiles; t0 += 32) {
+      float v[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const int t = t0 + 16 * h + i;
+        v[i] = (m < prm.rows_q && t < prm.ss_tiles) ? __ldcg(&prm.ss_in[(size_t)m * prm.ss_tiles + t]) : 0.f;
+      }
+      float part = 0.f;
+#pragma unroll
+      for (int i = 0; i < 16; ++i) part += v[i];
+      const float other = __shfl_xor_sync(0xffffffffu, part, 1);
+      ss += h == 0 ? part + other : other + part;
+    }
+    if (h == 0 && m < prm.rows_q && m < 64) rstd_s[m] = rsqrtf(ss * prm.ss_inv_size + prm.eps);
+  }
   bool acc_ok = n_iter > 0 ? mbar_wait(accum_bar, 0, prm.status, 3) : true;
   tc_fence_after();
   // a failure anywhere in the block is everybody's failure
@@ -223,10 +257,17 @@ gemm_tc_bf16_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
 #pragma unroll 1
       for (int base = 0; base < owned; base += P * 4 * MPW) {
         float4 part[P][NS], part_up[P][NS];
+        float4 st_old[P], gn[P];                 // the stream and the next norm's gain (residual form)
+        const bool fused_add = EPI == TC_EPI_BF16 && prm.stream != nullptr;
 #pragma unroll
         for (int ps = 0; ps < P; ++ps) {
           const int idx = base + (ps * 4 + warp) * MPW + sub;
           const int m = first + idx * step;
+          if (fused_add && idx < owned && tile_p * kTcBM + r0 < prm.rows_p) {
+            const int n_out = tile_p * kTcBM + r0;
+            st_old[ps] = __ldcg(reinterpret_cast<const float4*>(prm.stream + (size_t)m * prm.ld_stream + n_out));
+            gn[ps] = *reinterpret_cast<const float4*>(prm.next_gain + n_out);
+          }
 #pragma unroll
           for (int sp = 0; sp < NS; ++sp) {
             const bool live = idx < owned && sp < n_split;
@@ -252,6 +293,11 @@ gemm_tc_bf16_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
               }
             }
           }
+          if (prm.ss_in != nullptr && idx < owned) {
+            const float rs = rstd_s[m];
+            acc.x *= rs; acc.y *= rs; acc.z *= rs; acc.w *= rs;
+            up.x *= rs; up.y *= rs; up.z *= rs; up.w *= rs;
+          }
           int n_out, n_limit;
           if (EPI == TC_EPI_SWIGLU) {
             n_out = tile_p * 64 + r0;
@@ -262,7 +308,23 @@ gemm_tc_bf16_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
             n_out = tile_p * kTcBM + r0;
             n_limit = prm.rows_p;
           }
-          if (idx < owned && n_out < n_limit) {
+          if (fused_add) {
+            // rows_p and the strides are multiples of 4 here (checked by the launcher)
+            float ssq = 0.f;
+            if (idx < owned && n_out < n_limit) {
+              float* sp = prm.stream + (size_t)m * prm.ld_stream + n_out;
+              float4 st = st_old[ps];
+              st.x += acc.x; st.y += acc.y; st.z += acc.z; st.w += acc.w;
+              *reinterpret_cast<float4*>(sp) = st;
+              ssq = st.x * st.x + st.y * st.y + st.z * st.z + st.w * st.w;
+              __nv_bfloat162 lo = __floats2bfloat162_rn(st.x * gn[ps].x, st.y * gn[ps].y);
+              __nv_bfloat162 hi = __floats2bfloat162_rn(st.z * gn[ps].z, st.w * gn[ps].w);
+              *reinterpret_cast<uint2*>((bf16*)prm.out + (size_t)m * prm.ldo + n_out) =
+                  make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+            }
+            ssq = warp_sum(ssq);                 // a warp holds one sequence's 128 columns
+            if (lane == 0 && idx < owned) prm.ss_out[(size_t)m * gridDim.x + tile_p] = ssq;
+          } else if (idx < owned && n_out < n_limit) {
             const float v[4] = {acc.x, acc.y, acc.z, acc.w};
             if (EPI == TC_EPI_F32) {
               float* o = (float*)prm.out + (size_t)m * prm.ldo + n_out;
@@ -449,7 +511,9 @@ static int launch_tc(const CUtensorMap& mp, const CUtensorMap& mq, const TcParam
 EK_EXPORT int ek_gemm_tc_bf16(void* out, const void* x, const void* w, int M, int N, int K, int ldx,
                               int ldw, int ldo, int epilogue, int swap, int k_split, int cluster,
                               float* partials, unsigned int* tickets, long long partial_floats,
-                              int n_tickets, int* status, cudaStream_t stream) {
+                              int n_tickets, const float* ss_in, int ss_tiles, int norm_size, float eps,
+                              float* residual, int ld_residual, const float* next_gain, float* ss_out,
+                              int* status, cudaStream_t stream) {
   using namespace ek;
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0 || K % 8 || ldx % 8 || ldw % 8 || !status || epilogue < 0 || epilogue > 2 ||
@@ -460,6 +524,14 @@ EK_EXPORT int ek_gemm_tc_bf16(void* out, const void* x, const void* w, int M, in
   prm.out = out; prm.ldo = ldo; prm.k_blocks = k_blocks; prm.status = status;
   prm.partials = partials; prm.tickets = tickets;
   prm.swiglu_half = N / 2;
+  prm.ss_in = ss_in; prm.ss_tiles = ss_tiles; prm.eps = eps;
+  prm.ss_inv_size = norm_size > 0 ? 1.f / (float)norm_size : 0.f;
+  prm.stream = residual; prm.ld_stream = ld_residual; prm.next_gain = next_gain; prm.ss_out = ss_out;
+  if (ss_in && (!swap || ss_tiles <= 0 || norm_size <= 0)) return EK_ERR_ARG;
+  if (residual && (!swap || epilogue != TC_EPI_BF16 || !next_gain || !ss_out || N % 4 || ldo % 4 ||
+                   ld_residual % 4 || ((uintptr_t)residual & 15) || ((uintptr_t)next_gain & 15) ||
+                   ((uintptr_t)out & 7)))
+    return EK_ERR_ARG;
   if (k_split < 1) k_split = 1;
   if (k_split > k_blocks) k_split = k_blocks;
   CUtensorMap mp, mq;
@@ -472,9 +544,9 @@ EK_EXPORT int ek_gemm_tc_bf16(void* out, const void* x, const void* w, int M, in
     prm.k_blocks_per_split = (k_blocks + k_split - 1) / k_split;
     k_split = (k_blocks + prm.k_blocks_per_split - 1) / prm.k_blocks_per_split;
     const bool clustered = cluster && k_split > 1 && k_split <= kTcMaxCluster;
-    if (k_split > 1 && !clustered && (!partials || !tickets || tiles > n_tickets ||
+    if (k_split > 1 && !clustered && (ss_in || residual || !partials || !tickets || tiles > n_tickets ||
                                       (long long)tiles * k_split * bn * kTcBM > partial_floats)) {
-      k_split = 1;
+      k_split = 1;                             // (the deferred-norm forms have no scratch path)
       prm.k_blocks_per_split = k_blocks;
     }
     prm.rows_p = N; prm.rows_q = M;

@@ -130,10 +130,19 @@ class DecoderModel:
         stream = ctx.workspace.get("stream", (t, self.spec.hidden_size), torch.float32)
         kernels.embed(stream, self.embedding, ctx.token_ids, t)
         pending = None
-        for run in self.spec.schedule:
+        schedule = self.spec.schedule
+        for i, run in enumerate(schedule):
+            block = self.blocks[run.layer]
             entry = cache.entry(run.cache) if run.cache is not None and \
-                self.blocks[run.layer].mixer.cache_spec() is not None else None
-            pending = self.blocks[run.layer].forward(stream, pending, ctx, entry, run.writes_cache)
+                block.mixer.cache_spec() is not None else None
+            # a block that can leave its last add and the next norm to its own last product is told
+            # which norm comes next (none after the last block: the final norm picks rows)
+            follower = self.blocks[schedule[i + 1].layer] if i + 1 < len(schedule) else None
+            next_norm = getattr(follower, "first_norm", lambda: None)() if follower is not None else None
+            if next_norm is not None:
+                pending = block.forward(stream, pending, ctx, entry, run.writes_cache, next_norm=next_norm)
+            else:
+                pending = block.forward(stream, pending, ctx, entry, run.writes_cache)
         return stream, pending
 
     def logits(self, ctx: StepContext, stream, pending, rows, n_rows: int):

@@ -380,7 +380,7 @@ def gemv_bf16(out, x, w, epilogue=EPI_BF16, n_rows=None, warps=None, blocks=None
 
 _gemm_tc = Function("gemm_tc_bf16", "ek_gemm_tc_bf16",
                     [_P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                     _P, _P, c_longlong, c_int, _P, _P])
+                     _P, _P, c_longlong, c_int, _P, c_int, c_int, c_float, _P, c_int, _P, _P, _P, _P])
 _tc_status = {}
 TC_SWAP_MAX_ROWS = 64
 
@@ -404,13 +404,21 @@ def check_tc_status(device):
 TC_MAX_CLUSTER = 8          # blocks of a thread-block cluster (the portable limit)
 
 
-def gemm_tc_bf16(out, x, w, epilogue=EPI_BF16, n_rows=None, swap=None, k_split=None, cluster=True):
+def gemm_tc_bf16(out, x, w, epilogue=EPI_BF16, n_rows=None, swap=None, k_split=None, cluster=True,
+                 row_scale=None, residual=None):
     """out = x . w^T (or the SwiGLU of it) on tcgen05 tensor cores with TMA-staged operands.
 
     ``swap`` (default: at most 64 rows) puts the weights on the 128-row side of the MMA and
     splits K over ``k_split`` blocks; otherwise 128 x 128 tiles of the output.  Up to 8 splits
     add their partial tiles through the distributed shared memory of a thread-block cluster
     (``cluster``), more of them through scratch in global memory.
+
+    Two options of the swapped form carry a norm that was moved out of its own kernel.
+    ``row_scale=(ss, size, eps)``: row r of the 32-bit result is multiplied by
+    rsqrt(sum(ss[r, :]) / size + eps) before the epilogue (``ss`` [rows, tiles], 32-bit).
+    ``residual=(stream, gain, ss_out)`` (bfloat16 result, N a multiple of 4): the result is added to
+    the 32-bit ``stream`` [rows, N] in place, ``out`` gets stream * gain, and ``ss_out`` [rows,
+    ceil(N / 128)] the sum of stream^2 over each 128-column tile.
     """
     _need_cuda(out, x, w)
     m = n_rows if n_rows is not None else x.shape[0]
@@ -436,9 +444,32 @@ def gemm_tc_bf16(out, x, w, epilogue=EPI_BF16, n_rows=None, swap=None, k_split=N
             tiles = -(-n_out // (64 if epilogue == EPI_SWIGLU else 128))
             k_blocks = -(-k // 64)
             k_split = max(1, min(2 * SM_COUNT // tiles, k_blocks // 8, TC_MAX_CLUSTER))
+    if row_scale is not None or residual is not None:
+        cluster, k_split = True, min(k_split, TC_MAX_CLUSTER)     # these forms have no scratch path
+    ss_in, ss_tiles, size, eps = None, 0, 0, 0.0
+    if row_scale is not None:
+        ss_in, size, eps = row_scale
+        _need(swap and ss_in.dtype == torch.float32 and ss_in.is_contiguous() and ss_in.dim() == 2
+              and ss_in.shape[0] >= m and ss_in.is_cuda, "gemm_tc_bf16: row_scale needs 32-bit sums [rows, tiles]")
+        ss_tiles = ss_in.shape[1]
+    stream, gain, ss_out, ld_stream = None, None, None, 0
+    if residual is not None:
+        stream, gain, ss_out = residual
+        _need_cuda(stream, gain, ss_out)
+        _need(swap and epilogue == EPI_BF16 and n % 4 == 0 and out.stride(0) % 4 == 0,
+              "gemm_tc_bf16: residual needs the swapped form, a bfloat16 result and N a multiple of 4")
+        _need(stream.dtype == torch.float32 and stream.stride(-1) == 1 and stream.stride(0) % 4 == 0
+              and stream.shape[-1] == n and stream.shape[0] >= m and stream.data_ptr() % 16 == 0,
+              "gemm_tc_bf16: residual stream [rows, N] in 32-bit, 16-byte aligned rows")
+        _need(gain.dtype == torch.float32 and gain.numel() == n and gain.data_ptr() % 16 == 0,
+              "gemm_tc_bf16: gain [N] in 32-bit")
+        _need(ss_out.dtype == torch.float32 and ss_out.is_contiguous() and ss_out.shape[0] >= m
+              and ss_out.shape[1] == -(-n // 128), "gemm_tc_bf16: ss_out [rows, ceil(N/128)] in 32-bit")
+        ld_stream = stream.stride(0)
     _gemm_tc(_ptr(out), _ptr(x), _ptr(w), m, n, k, x.stride(0), w.stride(0), out.stride(0),
              epilogue, 1 if swap else 0, k_split, 1 if cluster else 0, _ptr(partials), _ptr(tickets),
-             _GEMV_PARTIAL_FLOATS, _GEMV_TICKETS, _ptr(tc_status(x.device)), _stream())
+             _GEMV_PARTIAL_FLOATS, _GEMV_TICKETS, _ptr(ss_in), ss_tiles, int(size), float(eps),
+             _ptr(stream), ld_stream, _ptr(gain), _ptr(ss_out), _ptr(tc_status(x.device)), _stream())
 
 
 # ------------------------------------------------------------------ sampling and decode state

@@ -72,7 +72,10 @@ class Attention(Mixer):
             self.k_gain = tensors[w["k_norm"]].to(torch.float32).contiguous()
 
     # ------------------------------------------------------------------
-    def forward(self, x, ctx, entry, writes_cache=True):
+    takes_deferred_norm = True
+    defers_norm = True
+
+    def forward(self, x, ctx, entry, writes_cache=True, defer=None):
         t = ctx.n_tokens
         qkv = linear(x, self.w_qkv, ctx, "qkv", n_rows=t)
         pos = self.position
@@ -84,7 +87,7 @@ class Attention(Mixer):
             self.qk_norm_eps if self.qk_norm_eps is not None else 0.0, write_kv=writes_cache)
         out = ctx.workspace.get("attn_out", (t, self.num_heads * self.head_dim), self.dtype)
         self._attend(out, qkv, ctx, entry)
-        return linear(out, self.w_o, ctx, "attn_proj", n_rows=t)
+        return linear(out, self.w_o, ctx, "attn_proj", n_rows=t, defer=defer)
 
     def _attend(self, out, qkv, ctx, entry):
         t = ctx.n_tokens

@@ -13,6 +13,12 @@ device.  It never sees the model's configuration or which model it is in.  Roles
 ``stream`` is the 32-bit residual stream ``[T, hidden]``; ``pending`` is a part's output
 that has not been added to the stream yet (the add is folded into the next norm, as the
 reference folds it into ``add_rms_norm``, engine/ek_model.py:291-296, 326-334).
+
+A norm may be *deferred*: a part that is told which norm follows it (``defer=(stream, norm)``)
+may add its output to the stream itself and return a :class:`DeferredNorm` instead of a
+tensor, and a part may be given a :class:`DeferredNorm` instead of normalised activations.
+Both are optional: a part says so with ``defers_norm`` / ``takes_deferred_norm`` and a norm
+with ``deferrable()``; everything else goes through the norm's own ``forward``.
 """
 
 from __future__ import annotations
@@ -76,6 +82,21 @@ class StepContext:
     host_cu_seqlens: Optional[List[int]] = None
 
 
+@dataclasses.dataclass
+class DeferredNorm:
+    """A norm y = gain * x * rsqrt(mean(x^2) + eps) whose work was moved into the matrix
+    products around it: the stream already holds x (the add is done), ``scaled`` is
+    x * gain rounded to the activation dtype, and ``ss`` [rows, tiles] holds the sums of x^2
+    per 128-column tile of the stream.  The product that reads ``scaled`` multiplies row r of
+    its 32-bit result by rsqrt(sum(ss[r]) / size + eps): the same y . W^T with the rounding
+    taken before the row's scale instead of after it."""
+    scaled: torch.Tensor
+    ss: torch.Tensor
+    tiles: int
+    size: int
+    eps: float
+
+
 class Part:
     """Base of all parts."""
     role = ""
@@ -102,6 +123,11 @@ class Part:
 class Norm(Part):
     role = "norm"
 
+    def deferrable(self):
+        """(gain [size] in 32-bit, eps) if this norm is gain * x * rsqrt(mean(x^2) + eps) over
+        the whole stream row and so can be a :class:`DeferredNorm`; else None."""
+        return None
+
     def forward(self, stream, ctx: StepContext, add=None, rows=None, n_rows=None,
                 write_back=True):
         raise NotImplementedError
@@ -116,6 +142,9 @@ class PositionEncoding(Part):
 
 class Mixer(Part):
     role = "mixer"
+    #: ``forward`` takes a DeferredNorm for ``x`` / takes ``defer=(stream, norm)`` and may return one
+    takes_deferred_norm = False
+    defers_norm = False
 
     def cache_spec(self) -> Optional[CacheSpec]:
         """What one cache entry of this mixer holds per sequence (None: nothing)."""
@@ -130,6 +159,8 @@ class Mixer(Part):
 
 class FeedForward(Part):
     role = "feed_forward"
+    takes_deferred_norm = False
+    defers_norm = False
 
     def forward(self, x, ctx: StepContext):
         raise NotImplementedError
@@ -147,6 +178,11 @@ class Block(Part):
     @classmethod
     def norm_names(cls, spec: PartSpec) -> List[str]:
         return []
+
+    def first_norm(self) -> Optional[Norm]:
+        """The norm that takes the incoming ``pending``, if the block can be handed a
+        :class:`DeferredNorm` made for it (then ``forward`` also takes ``next_norm=``); else None."""
+        return None
 
     def forward(self, stream, pending, ctx: StepContext, entry, writes_cache: bool):
         raise NotImplementedError

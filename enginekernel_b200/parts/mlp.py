@@ -11,9 +11,9 @@ from __future__ import annotations
 import torch
 
 from ..ops import kernels
-from ..ops.linear import linear, tc_takes
+from ..ops.linear import linear, row_scale_of, tc_takes
 from ..registry import register_part
-from .base import FeedForward
+from .base import DeferredNorm, FeedForward
 from .spec import TensorSpec
 
 
@@ -41,14 +41,23 @@ class GatedMLP(FeedForward):
             .to(self.dtype).contiguous()
         self.w_down = tensors[w["down"]].to(self.dtype).contiguous()
 
-    def forward(self, x, ctx):
+    takes_deferred_norm = True
+    defers_norm = True
+
+    def forward(self, x, ctx, defer=None):
         t = ctx.n_tokens
+        row_scale = None
+        if isinstance(x, DeferredNorm):
+            row_scale, x = row_scale_of(x), x.scaled
         if self.dtype == torch.bfloat16 and t <= kernels.TC_SWAP_MAX_ROWS and tc_takes(x, self.w_gate_up):
             # gate and up rows share a tile, so silu(gate) * up is formed in the epilogue
             act = ctx.workspace.get("mlp_act", (t, self.inter), self.dtype)
-            kernels.gemm_tc_bf16(act, x, self.w_gate_up, kernels.EPI_SWIGLU, n_rows=t, swap=True)
+            kernels.gemm_tc_bf16(act, x, self.w_gate_up, kernels.EPI_SWIGLU, n_rows=t, swap=True,
+                                 row_scale=row_scale)
         else:
+            if row_scale is not None:
+                raise kernels.KernelError("a deferred norm reached a product that cannot scale its rows")
             gu = linear(x, self.w_gate_up, ctx, "mlp_gate_up", n_rows=t)
             act = ctx.workspace.get("mlp_act", (t, self.inter), self.dtype)
             kernels.silu_mul(act, gu, n_rows=t)
-        return linear(act, self.w_down, ctx, "mlp_down", n_rows=t)
+        return linear(act, self.w_down, ctx, "mlp_down", n_rows=t, defer=defer)

@@ -29,6 +29,9 @@ class RMSNorm(Norm):
     def load(self, tensors):
         self.gain = tensors[self.spec.weights["gain"]].to(torch.float32).contiguous()
 
+    def deferrable(self):
+        return self.gain, self.eps
+
     def forward(self, stream, ctx, add=None, rows=None, n_rows=None, write_back=True):
         if n_rows is None:
             n_rows = rows.numel() if rows is not None else ctx.n_tokens

@@ -240,3 +240,36 @@ def test_sizes_the_tensor_core_path_cannot_address_still_work(tmp_path):
         eng = Engine(folder, dtype, max_tokens=256, max_batch=2)
         assert helpers.rel_err(helpers.whole(eng, ids), want) <= helpers.TOL[dtype]
         assert helpers.rel_err(helpers.tail_one_by_one(eng, ids, 8), want) <= helpers.TOL[dtype]
+
+
+@pytest.mark.parametrize("tag", ["A", "C"])
+def test_norms_moved_into_the_products_change_rounding_only(engines, plains, tag):
+    """With few rows the residual add and the norm ride on the products around them; the logits
+    must agree with the norm kernel's, and with the plain implementation, as closely as before."""
+    from enginekernel_b200.ops import linear, kernels
+    cfg = CONFIGS[tag][0]
+    ids = tiny_models.random_prompts(cfg, [min(90, cfg["max_position_embeddings"])], seed=77)[0]
+    want = plain.logits(plains[tag], ids)
+    eng = engines(tag, "bfloat16")
+    calls = []
+    real = kernels.gemm_tc_bf16
+
+    def spy(*a, **kw):
+        calls.append((kw.get("row_scale") is not None, kw.get("residual") is not None))
+        return real(*a, **kw)
+    got = {}
+    limit = linear.DEFER_NORM_ROWS
+    try:
+        kernels.gemm_tc_bf16 = spy
+        for rows in (limit, 0):
+            linear.DEFER_NORM_ROWS = rows
+            calls.clear()
+            got[rows] = helpers.tail_one_by_one(eng, ids, 32)
+            took = any(s or r for s, r in calls)
+            assert took == (rows > 0), "the deferred form runs exactly when it is allowed"
+    finally:
+        linear.DEFER_NORM_ROWS = limit
+        kernels.gemm_tc_bf16 = real
+    assert helpers.rel_err(got[limit], want) <= helpers.TOL["bfloat16"]
+    assert helpers.rel_err(got[0], want) <= helpers.TOL["bfloat16"]
+    assert helpers.rel_err(got[limit], got[0]) <= helpers.TOL["bfloat16"]

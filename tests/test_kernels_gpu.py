@@ -503,6 +503,50 @@ def test_gemm_tc_swapped(m, n, k_):
     assert int(tickets.abs().sum()) == 0
 
 
+@pytest.mark.parametrize("m,n,k_", [(8, 2560, 4096), (1, 256, 128), (33, 1000, 1000), (64, 1024, 3072),
+                                    (5, 136, 80)])
+def test_gemm_tc_deferred_norm(m, n, k_):
+    """The two halves of a norm moved into the products around it: the product before adds its
+    result to the stream, leaves stream * gain and the tiles' sums of squares; the product after
+    scales its rows by the 1/rms those sums give (also under SwiGLU)."""
+    k = K()
+    x = rnd(m, k_, dtype=torch.bfloat16, seed=1)
+    w = rnd(n, k_, dtype=torch.bfloat16, seed=2, scale=0.05)
+    stream0 = rnd(m + 2, n, seed=3, scale=2.0)
+    gain = 1 + 0.1 * rnd(n, seed=4)
+    eps = 1e-5
+    tiles = -(-n // 128)
+    for k_split in (None, 1, 3):
+        stream = stream0.clone()
+        scaled = torch.full((m, n), 7.0, dtype=torch.bfloat16, device=DEV)
+        ss = torch.full((m, tiles), -1.0, device=DEV)
+        k.gemm_tc_bf16(scaled, x, w, k.EPI_BF16, swap=True, k_split=k_split, residual=(stream, gain, ss))
+        k.check_tc_status(DEV)
+        want_stream = stream0[:m].double() + x.double() @ w.double().t()
+        assert rel(stream[:m], want_stream) <= 1e-5
+        assert torch.equal(stream[m:], stream0[m:])                   # rows beyond m are not touched
+        assert rel(scaled, want_stream * gain.double()) <= 4e-3
+        assert rel(ss.sum(1), want_stream.pow(2).sum(1)) <= 1e-5
+        pad = torch.nn.functional.pad(stream[:m].double().pow(2), (0, tiles * 128 - n))
+        assert rel(ss, pad.view(m, tiles, 128).sum(-1)) <= 1e-5
+        # the consumer: y = rmsnorm(stream) * gain, then y . w2^T, from `scaled` and `ss`
+        n2 = 384
+        w2 = rnd(n2, n, dtype=torch.bfloat16, seed=5, scale=0.05)
+        rstd = torch.rsqrt(stream[:m].double().pow(2).mean(1, keepdim=True) + eps)
+        want = (scaled.double() * rstd) @ w2.double().t()
+        out = torch.empty(m, n2, dtype=torch.bfloat16, device=DEV)
+        k.gemm_tc_bf16(out, scaled, w2, k.EPI_BF16, swap=True, k_split=k_split, row_scale=(ss, n, eps))
+        assert rel(out, want) <= 4e-3
+        out32 = torch.empty(m, n2, device=DEV)
+        k.gemm_tc_bf16(out32, scaled, w2, k.EPI_F32, swap=True, k_split=k_split, row_scale=(ss, n, eps))
+        assert rel(out32, want) <= 1e-5
+        act = torch.empty(m, n2 // 2, dtype=torch.bfloat16, device=DEV)
+        k.gemm_tc_bf16(act, scaled, w2, k.EPI_SWIGLU, swap=True, k_split=k_split, row_scale=(ss, n, eps))
+        g, u = want[:, :n2 // 2], want[:, n2 // 2:]
+        assert rel(act, g / (1 + torch.exp(-g)) * u) <= 4e-3
+    k.check_tc_status(DEV)
+
+
 @pytest.mark.parametrize("m,n,k_", [(128, 128, 64), (2048, 2560, 4096), (300, 1000, 1000), (65, 662, 80),
                                     (517, 6144, 2560)])
 def test_gemm_tc_direct(m, n, k_):
