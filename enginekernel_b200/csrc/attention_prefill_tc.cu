@@ -53,13 +53,13 @@ attention_prefill_tc_kernel(bf16* __restrict__ out, const bf16* q, int q_row_str
   __shared__ int tile_info[3];
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int kv_head = blockIdx.y;
+  const int kv_head = blockIdx.x;             // heads fastest: blocks start longest key range first
   const int group = n_q_heads / n_kv_heads;
 
   pdl_launch_dependents();
   pdl_wait();
   if (tid == 0) {
-    int idx = blockIdx.x, found = -1, first = 0, count = 0;
+    int idx = blockIdx.y, found = -1, first = 0, count = 0;
     for (int b = 0; b < n_seqs; ++b) {
       const int n = cu_seqlens[b + 1] - cu_seqlens[b];
       const int tiles = (n + tok_per_tile - 1) / tok_per_tile;
@@ -335,7 +335,8 @@ static int launch_fa(bf16* out, const bf16* q, int q_row_stride, const int* posi
   }
   prefer_carveout((const void*)kernel, 100);
   const int tiles = (n_tokens + tok_per_tile - 1) / tok_per_tile + n_seqs;   // upper bound
-  dim3 grid(tiles, n_kv_heads);
+  if (tiles > 65535) return EK_ERR_ARG;
+  dim3 grid(n_kv_heads, tiles);
   return (int)launch_pdl(kernel, grid, dim3(kFaThreads), smem, stream, out, q, q_row_stride, positions,
                          token_slot, cu_seqlens, n_seqs, mk, mv, block_table, table_stride, n_kv_heads,
                          n_q_heads, scale * 1.4426950408889634f, window, tok_per_tile, status);
@@ -357,7 +358,7 @@ EK_EXPORT int ek_attention_prefill_tc(void* out, const void* q, int q_row_stride
   if ((head_dim != 64 && head_dim != 128) || n_kv_heads <= 0 || n_q_heads % n_kv_heads ||
       kFaRows % (n_q_heads / n_kv_heads) || q_row_stride % 8 || ((uintptr_t)q & 15) || !status ||
       !(scale > 0.f) ||
-      n_kv_heads > 65535 || n_pages <= 0)
+      n_pages <= 0)
     return EK_ERR_ARG;
   const long long page_rows = (long long)n_pages * n_kv_heads * EK_PAGE;
   if (head_dim == 64)
