@@ -38,6 +38,26 @@ TINY_C = {
     "max_position_embeddings": 1024, "tie_word_embeddings": True,
 }
 
+# A fourth shape whose head size (64) and group (3 query heads a KV head, which does not divide
+# 128) send attention to the TMA-fed decode kernel and the mma.sync prompt kernel; with
+# num_key_value_heads = 3 -> group 2 it would take the tcgen05 prompt kernel (TINY_E).
+TINY_D = {
+    "architectures": ["Qwen3ForCausalLM"],
+    "num_hidden_layers": 2, "hidden_size": 136, "num_attention_heads": 6,
+    "num_key_value_heads": 2, "head_dim": 64, "intermediate_size": 200,
+    "vocab_size": 413, "rope_theta": 20000.0, "rms_norm_eps": 2e-6,
+    "max_position_embeddings": 2048, "tie_word_embeddings": False,
+}
+
+# Head size 64, two query heads a KV head: the tcgen05 prompt kernel and the TMA-fed decode kernel.
+TINY_E = {
+    "architectures": ["Qwen3ForCausalLM"],
+    "num_hidden_layers": 3, "hidden_size": 104, "num_attention_heads": 4,
+    "num_key_value_heads": 2, "head_dim": 64, "intermediate_size": 160,
+    "vocab_size": 277, "rope_theta": 300000.0, "rms_norm_eps": 1e-6,
+    "max_position_embeddings": 2048, "tie_word_embeddings": True,
+}
+
 
 def tensor_shapes(cfg):
     h, nh, nkv, d = (cfg["hidden_size"], cfg["num_attention_heads"],

@@ -9,7 +9,8 @@ from tests.plain import tiny_models
 
 pytestmark = pytest.mark.gpu
 
-CONFIGS = {"A": (tiny_models.TINY_A, 0), "B": (tiny_models.TINY_B, 1), "C": (tiny_models.TINY_C, 2)}
+CONFIGS = {"A": (tiny_models.TINY_A, 0), "B": (tiny_models.TINY_B, 1), "C": (tiny_models.TINY_C, 2),
+           "D": (tiny_models.TINY_D, 3), "E": (tiny_models.TINY_E, 4)}
 
 
 @pytest.fixture(scope="module")
@@ -43,7 +44,7 @@ def lengths_for(tag):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("tag", ["A", "B", "C"])
+@pytest.mark.parametrize("tag", ["A", "B", "C", "D", "E"])
 def test_each_request_alone_and_whole(engines, plains, tag, dtype):
     cfg = CONFIGS[tag][0]
     eng = engines(tag, dtype)
@@ -54,7 +55,7 @@ def test_each_request_alone_and_whole(engines, plains, tag, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("tag", ["A", "B", "C"])
+@pytest.mark.parametrize("tag", ["A", "B", "C", "D", "E"])
 def test_last_32_tokens_one_by_one(engines, plains, tag, dtype):
     cfg = CONFIGS[tag][0]
     eng = engines(tag, dtype)
@@ -69,7 +70,7 @@ def test_last_32_tokens_one_by_one(engines, plains, tag, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("tag", ["A", "B", "C"])
+@pytest.mark.parametrize("tag", ["A", "B", "C", "D", "E"])
 def test_unequal_batches_one_after_another(engines, plains, tag, dtype):
     """Batches of unequal lengths whose shorter requests end earlier; three batches in a
     row on an engine with few slots, so that slots and pages are used again."""
@@ -242,7 +243,7 @@ def test_sizes_the_tensor_core_path_cannot_address_still_work(tmp_path):
         assert helpers.rel_err(helpers.tail_one_by_one(eng, ids, 8), want) <= helpers.TOL[dtype]
 
 
-@pytest.mark.parametrize("tag", ["A", "C"])
+@pytest.mark.parametrize("tag", ["A", "C", "D", "E"])
 def test_norms_moved_into_the_products_change_rounding_only(engines, plains, tag):
     """With few rows the residual add and the norm ride on the products around them; the logits
     must agree with the norm kernel's, and with the plain implementation, as closely as before."""
