@@ -172,7 +172,7 @@ def main(argv=None) -> int:
     # ---- prefill of 2,048 tokens -------------------------------------------------------
     one = prompts(1)[0]
     times = []
-    for it in range(2 + 3):
+    for it in range(4 + 5):                      # 4 warm-ups (clocks, workspace), median of 5
         slot = engine.open_sequence()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         torch.cuda.synchronize()
@@ -181,7 +181,7 @@ def main(argv=None) -> int:
         b.record()
         torch.cuda.synchronize()
         engine.close_sequence(slot)
-        if it >= 2:
+        if it >= 4:
             times.append(a.elapsed_time(b))
     prefill_ms = statistics.median(times)
     L, H, NH, NKV, D, I, V = (cfg.num_hidden_layers, cfg.hidden_size, cfg.num_attention_heads,
