@@ -82,6 +82,10 @@ attention_decode_tma_kernel(bf16* __restrict__ out, const bf16* q, int q_row_str
   const int head0 = kv_head * group;
 
   pdl_launch_dependents();
+  if (tid == kDtWarps * 32) {
+    tma_prefetch_map(&map_k);
+    tma_prefetch_map(&map_v);
+  }
   // positions, slots and block tables were written before this step's kernels were launched
   const int pos = positions[t];
   int lo = 0, hi = -1, pg_first = 0, pg_last = -1;
@@ -317,13 +321,15 @@ attention_decode_tma_kernel(bf16* __restrict__ out, const bf16* q, int q_row_str
   cluster_sync();                                // nobody leaves while its result may be read
 }
 
-template <int D>
+// DEEP: a ring twice as deep (192 KB, one block an SM) for launches that leave SMs empty anyway, so
+// that more of a block's pages are on their way before the wait returns.
+template <int D, bool DEEP>
 static int launch_dt(bf16* out, const bf16* q, int q_row_stride, const int* positions,
                      const int* token_slot, const void* k_pages, const void* v_pages,
                      long long page_rows, const int* block_table, int table_stride, int n_tokens,
                      int n_q_heads, int n_kv_heads, float scale, int window, int n_splits, int* status,
                      cudaStream_t stream) {
-  constexpr int STAGES = D == 128 ? 3 : 6;
+  constexpr int STAGES = (D == 128 ? 3 : 6) * (DEEP ? 2 : 1);
   constexpr int DB = D / 64;
   constexpr size_t smem = 1024 + (size_t)STAGES * 2 * DB * EK_PAGE * 128 + 2 * STAGES * 8;
   CUtensorMap mk, mv;
@@ -371,11 +377,16 @@ EK_EXPORT int ek_attention_decode_tma(void* out, const void* q, int q_row_stride
       ((uintptr_t)q & 3) || !status || n_kv_heads > 65535 || n_tokens > 65535 || n_pages <= 0)
     return EK_ERR_ARG;
   const long long page_rows = (long long)n_pages * n_kv_heads * EK_PAGE;
-  if (head_dim == 64)
-    return launch_dt<64>((bf16*)out, (const bf16*)q, q_row_stride, positions, token_slot, k_pages,
-                         v_pages, page_rows, block_table, table_stride, n_tokens, n_q_heads,
-                         n_kv_heads, scale, window, n_splits, status, stream);
-  return launch_dt<128>((bf16*)out, (const bf16*)q, q_row_stride, positions, token_slot, k_pages,
-                        v_pages, page_rows, block_table, table_stride, n_tokens, n_q_heads,
-                        n_kv_heads, scale, window, n_splits, status, stream);
+  const bool deep = (long long)n_tokens * n_kv_heads * n_splits <= 148;     // one block an SM at most
+#define EK_DT(D_, DEEP_)                                                                          \
+  return launch_dt<D_, DEEP_>((bf16*)out, (const bf16*)q, q_row_stride, positions, token_slot,     \
+                              k_pages, v_pages, page_rows, block_table, table_stride, n_tokens,   \
+                              n_q_heads, n_kv_heads, scale, window, n_splits, status, stream)
+  if (head_dim == 64) {
+    if (deep) EK_DT(64, true);
+    EK_DT(64, false);
+  }
+  if (deep) EK_DT(128, true);
+  EK_DT(128, false);
+#undef EK_DT
 }

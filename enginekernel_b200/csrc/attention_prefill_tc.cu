@@ -57,6 +57,10 @@ attention_prefill_tc_kernel(bf16* __restrict__ out, const bf16* q, int q_row_str
   const int group = n_q_heads / n_kv_heads;
 
   pdl_launch_dependents();
+  if (tid == 128) {
+    tma_prefetch_map(&map_k);
+    tma_prefetch_map(&map_v);
+  }
   pdl_wait();
   if (tid == 0) {
     int idx = blockIdx.y, found = -1, first = 0, count = 0;

@@ -93,6 +93,10 @@ gemm_tc_bf16_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
   const int n_iter = kb_end - kb_begin;
 
   pdl_launch_dependents();
+  if (tid == 0) {
+    tma_prefetch_map(&map_p);
+    tma_prefetch_map(&map_q);
+  }
   const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES),
                  accum_bar = smem_u32(bars + 2 * STAGES);
   if (tid == 0) {
