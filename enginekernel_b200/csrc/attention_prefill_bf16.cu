@@ -68,11 +68,11 @@ attention_prefill_bf16_kernel(bf16* __restrict__ out, const bf16* __restrict__ q
   bf16* v_s = k_s + 2 * kPfKeys * LD;                       // [2][64][LD]
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, tq = lane & 3;
-  const int kv_head = blockIdx.y;
+  const int kv_head = blockIdx.x;             // heads fastest: longest key ranges start first
   const int group = n_q_heads / cache.heads;
 
   if (tid == 0) {
-    int idx = blockIdx.x, found = -1, first = 0, count = 0;
+    int idx = blockIdx.y, found = -1, first = 0, count = 0;
     for (int b = 0; b < n_seqs; ++b) {
       const int n = cu_seqlens[b + 1] - cu_seqlens[b];
       const int tiles = (n + tok_per_tile - 1) / tok_per_tile;
@@ -287,8 +287,8 @@ static int launch_dmax(bf16* out, const bf16* q, int q_row_stride, const int* po
   if (e != cudaSuccess) return (int)e;
   prefer_carveout((const void*)attention_prefill_bf16_kernel<DMAX>, 100);
   const int tiles = (n_tokens + tok_per_tile - 1) / tok_per_tile + n_seqs;   // upper bound
-  dim3 grid(tiles, cache.heads);
-  if (cache.heads > 65535) return EK_ERR_ARG;
+  dim3 grid(cache.heads, tiles);
+  if (tiles > 65535) return EK_ERR_ARG;
   attention_prefill_bf16_kernel<DMAX><<<grid, kPfWarps * 32, smem, stream>>>(
       out, q, q_row_stride, positions, token_slot, cu_seqlens, n_seqs, cache, n_q_heads,
       scale * 1.4426950408889634f, window, tok_per_tile);
