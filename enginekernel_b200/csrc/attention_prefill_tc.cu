@@ -18,8 +18,9 @@
 // it by more than 2^8, which keeps every probability finite in bfloat16 and skips the rescale
 // of almost every page.  O is divided by the sum once, at the end.
 // Warp 4 (one thread) is the TMA producer, warp 5 (one thread) issues the MMAs.  Shared memory
-// holds Q and two stages each of K and V (96 KB at head size 128), TMEM 256 columns (S, S, O):
-// two blocks an SM.  Every wait is bounded and reports through `status`.
+// holds Q, three stages of K (the scores of page t+1 need their K two softmax steps ahead of
+// time, or the softmax warps wait for it) and two of V - 112 KB at head size 128 - and TMEM 256
+// columns (S, S, O): two blocks an SM.  Every wait is bounded and reports through `status`.
 // Formula and rounding points as in the mma.sync kernel (scores and softmax in 32-bit, P in
 // bfloat16 before P.V; engine/ek_kernels.py:166-221 is the reference's Triton counterpart).
 #include "tc_common.cuh"
@@ -29,7 +30,13 @@ namespace ek {
 constexpr int kFaRows = 128;
 constexpr int kFaKeys = EK_PAGE;             // 64
 constexpr int kFaThreads = 192;              // 4 softmax warps, a producer warp, an MMA warp
-constexpr int kFaBars = 14;                  // the list is in the kernel
+constexpr int kFaKStages = 3;                // K pages in flight: two pages of lookahead for the scores
+constexpr int kFaVStages = 2;
+// mbarriers: K full / empty per K stage, V full / empty per V stage, then per S buffer (2):
+// scores complete, P written, P.V done
+constexpr int kBarKFull = 0, kBarKEmpty = kBarKFull + kFaKStages, kBarVFull = kBarKEmpty + kFaKStages,
+              kBarVEmpty = kBarVFull + kFaVStages, kBarSFull = kBarVEmpty + kFaVStages,
+              kBarPFull = kBarSFull + 2, kBarPvDone = kBarPFull + 2, kFaBars = kBarPvDone + 2;
 
 template <int D>
 __global__ void __launch_bounds__(kFaThreads, 2)
@@ -43,14 +50,15 @@ attention_prefill_tc_kernel(bf16* __restrict__ out, const bf16* q, int q_row_str
   constexpr uint32_t kSub = kFaKeys * 128;         // one [64 x 64] bfloat16 sub-tile: 8 KB
   constexpr uint32_t kTmemCols = 256;
   constexpr uint32_t kColS = 0, kColO = 128;        // S buffers at 0 and 64, O at 128
-  extern __shared__ __align__(1024) unsigned char smem_raw[];
-  unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  // No static shared memory in this kernel, so the dynamic part starts at the block's first
+  // shared byte, which is 1024-byte aligned as the 128-byte swizzle needs; the kernel checks it.
+  extern __shared__ __align__(1024) unsigned char smem[];
   unsigned char* q_s = smem;                                   // DB x [128 x 64]
-  unsigned char* k_s = q_s + DB * 2 * kSub;                    // 2 stages x DB x [64 x 64]
-  unsigned char* v_s = k_s + 2 * DB * kSub;                    // 2 stages x DB x [64 x 64]
-  uint64_t* bars = (uint64_t*)(v_s + 2 * DB * kSub);
+  unsigned char* k_s = q_s + DB * 2 * kSub;                    // K stages x DB x [64 x 64]
+  unsigned char* v_s = k_s + kFaKStages * DB * kSub;           // V stages x DB x [64 x 64]
+  uint64_t* bars = (uint64_t*)(v_s + kFaVStages * DB * kSub);
   uint32_t* tmem_slot = (uint32_t*)(bars + kFaBars);
-  __shared__ int tile_info[3];
+  int* tile_info = (int*)(tmem_slot + 1);                      // 3 ints
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int kv_head = blockIdx.x;             // heads fastest: blocks start longest key range first
@@ -79,6 +87,10 @@ attention_prefill_tc_kernel(bf16* __restrict__ out, const bf16* q, int q_row_str
     tile_info[0] = first; tile_info[1] = count; tile_info[2] = found;
   }
   __syncthreads();
+  if ((smem_u32(smem) & 1023u) != 0) {           // never seen; the swizzled tiles would be wrong
+    if (tid == 0) atomicCAS(status, 0, 19);
+    return;
+  }
   if (tile_info[2] < 0) return;
   const int t_first = tile_info[0], n_tok = tile_info[1];
   const int pos0 = positions[t_first];
@@ -97,16 +109,10 @@ attention_prefill_tc_kernel(bf16* __restrict__ out, const bf16* q, int q_row_str
   const int kt_lo = lo_tile / kFaKeys, kt_hi = hi_tile / kFaKeys;
   const int n_iter = kt_hi - kt_lo + 1;
 
-  // barriers: 0,1 k_full  2,3 k_empty  4,5 v_full  6,7 v_empty  8,9 s_full  10,11 p_full
-  //           12,13 pv_done
   const uint32_t bar0 = smem_u32(bars);
   auto bar = [&](int i) { return bar0 + 8u * i; };
   if (tid == 0) {
-    for (int i = 0; i < 10; ++i) mbar_init(bar(i), 1);
-    mbar_init(bar(10), 4);
-    mbar_init(bar(11), 4);
-    mbar_init(bar(12), 1);
-    mbar_init(bar(13), 1);
+    for (int i = 0; i < kFaBars; ++i) mbar_init(bar(i), (i == kBarPFull || i == kBarPFull + 1) ? 4 : 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 4) tmem_alloc(smem_u32(tmem_slot), kTmemCols);
@@ -130,21 +136,21 @@ attention_prefill_tc_kernel(bf16* __restrict__ out, const bf16* q, int q_row_str
   if (tid == 128) {
     // ------------------------------------------------------------------- TMA producer
     for (int it = 0; it < n_iter; ++it) {
-      const int s = it & 1;
-      const uint32_t phase = (it >> 1) & 1;
+      const int ks = it % kFaKStages, vs = it % kFaVStages;
+      const uint32_t k_phase = (it / kFaKStages) & 1, v_phase = (it / kFaVStages) & 1;
       const int row = (table[kt_lo + it] * n_kv_heads + kv_head) * kFaKeys;
-      ok = mbar_wait(bar(2 + s), phase ^ 1, status, 11);
+      ok = mbar_wait(bar(kBarKEmpty + ks), k_phase ^ 1, status, 11);
       if (!ok) break;
-      mbar_expect_tx(bar(0 + s), DB * kSub);
+      mbar_expect_tx(bar(kBarKFull + ks), DB * kSub);
 #pragma unroll
       for (int j = 0; j < DB; ++j)
-        tma_load_2d(smem_u32(k_s + (s * DB + j) * kSub), &map_k, 64 * j, row, bar(0 + s));
-      ok = mbar_wait(bar(6 + s), phase ^ 1, status, 12);
+        tma_load_2d(smem_u32(k_s + (ks * DB + j) * kSub), &map_k, 64 * j, row, bar(kBarKFull + ks));
+      ok = mbar_wait(bar(kBarVEmpty + vs), v_phase ^ 1, status, 12);
       if (!ok) break;
-      mbar_expect_tx(bar(4 + s), DB * kSub);
+      mbar_expect_tx(bar(kBarVFull + vs), DB * kSub);
 #pragma unroll
       for (int j = 0; j < DB; ++j)
-        tma_load_2d(smem_u32(v_s + (s * DB + j) * kSub), &map_v, 64 * j, row, bar(4 + s));
+        tma_load_2d(smem_u32(v_s + (vs * DB + j) * kSub), &map_v, 64 * j, row, bar(kBarVFull + vs));
     }
   } else if (tid == 160) {
     // ------------------------------------------------------------------- MMA issuer
@@ -157,36 +163,37 @@ attention_prefill_tc_kernel(bf16* __restrict__ out, const bf16* q, int q_row_str
     for (int it = 0; it <= n_iter && ok; ++it) {
       if (it < n_iter) {
         const int s = it & 1;
-        const uint32_t phase = (it >> 1) & 1;
-        ok = mbar_wait(bar(0 + s), phase, status, 21);
+        const int ks = it % kFaKStages;
+        ok = mbar_wait(bar(kBarKFull + ks), (it / kFaKStages) & 1, status, 21);
         if (!ok) break;
         tc_fence_after();
 #pragma unroll
         for (int j = 0; j < DB; ++j) {
           const uint64_t dq = smem_desc_k_sw128(smem_u32(q_s + j * 2 * kSub));
-          const uint64_t dk = smem_desc_k_sw128(smem_u32(k_s + (s * DB + j) * kSub));
+          const uint64_t dk = smem_desc_k_sw128(smem_u32(k_s + (ks * DB + j) * kSub));
 #pragma unroll
           for (int k = 0; k < 4; ++k)
             tc_mma(tmem_base + kColS + 64 * s, dq + (uint64_t)(2 * k), dk + (uint64_t)(2 * k), idesc_s,
                    (j | k) ? 1u : 0u);
         }
-        tc_commit(bar(2 + s));                     // the K stage is free when these are done
-        tc_commit(bar(8 + s));                     // S is complete
+        tc_commit(bar(kBarKEmpty + ks));           // the K stage is free when these are done
+        tc_commit(bar(kBarSFull + s));             // S is complete
       }
       if (it >= 1) {
         const int u = it - 1, s = u & 1;
         const uint32_t phase = (u >> 1) & 1;
-        ok = mbar_wait(bar(10 + s), phase, status, 23);               // P written (O rescaled)
-        if (ok) ok = mbar_wait(bar(4 + s), phase, status, 24);        // V landed
+        const int vs = u % kFaVStages;
+        ok = mbar_wait(bar(kBarPFull + s), phase, status, 23);        // P written (O rescaled)
+        if (ok) ok = mbar_wait(bar(kBarVFull + vs), (u / kFaVStages) & 1, status, 24);   // V landed
         if (!ok) break;
         tc_fence_after();
-        const uint64_t dv = smem_desc_mn_sw128(smem_u32(v_s + s * DB * kSub), kSub, 1024);
+        const uint64_t dv = smem_desc_mn_sw128(smem_u32(v_s + vs * DB * kSub), kSub, 1024);
 #pragma unroll
         for (int k = 0; k < 4; ++k)                // 16 keys a step: 8 columns of P,
           tc_mma_ts(tmem_base + kColO, tmem_base + kColS + 64 * s + 8 * k, dv + (uint64_t)(128 * k),
                     idesc_pv, (u | k) ? 1u : 0u);  // 16 rows (2048 bytes) down V
-        tc_commit(bar(6 + s));                     // the V stage is free
-        tc_commit(bar(12 + s));                    // O holds pages 0..u
+        tc_commit(bar(kBarVEmpty + vs));           // the V stage is free
+        tc_commit(bar(kBarPvDone + s));            // O holds pages 0..u
       }
     }
   }
@@ -202,7 +209,7 @@ attention_prefill_tc_kernel(bf16* __restrict__ out, const bf16* q, int q_row_str
       const int s = it & 1;
       const uint32_t phase = (it >> 1) & 1;
       const int key0 = (kt_lo + it) * kFaKeys;
-      ok = mbar_wait(bar(8 + s), phase, status, 31);
+      ok = mbar_wait(bar(kBarSFull + s), phase, status, 31);
       if (!ok) break;
       tc_fence_after();
       float sc[kFaKeys];
@@ -231,7 +238,7 @@ attention_prefill_tc_kernel(bf16* __restrict__ out, const bf16* q, int q_row_str
       if (it > 0 && __any_sync(0xffffffffu, raise)) {
         // O holds pages 0..it-1 once their last P.V is done
         const int u = it - 1;
-        ok = mbar_wait(bar(12 + (u & 1)), (u >> 1) & 1, status, 34);
+        ok = mbar_wait(bar(kBarPvDone + (u & 1)), (u >> 1) & 1, status, 34);
         if (!ok) break;
         tc_fence_after();
 #pragma unroll
@@ -270,11 +277,11 @@ attention_prefill_tc_kernel(bf16* __restrict__ out, const bf16* q, int q_row_str
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar(10 + s));     // P (and any rescale of O) is in place
+      if (lane == 0) mbar_arrive(bar(kBarPFull + s));   // P (and any rescale of O) is in place
     }
     if (ok) {                                      // the last P.V
       const int u = n_iter - 1;
-      ok = mbar_wait(bar(12 + (u & 1)), (u >> 1) & 1, status, 36);
+      ok = mbar_wait(bar(kBarPvDone + (u & 1)), (u >> 1) & 1, status, 36);
       tc_fence_after();
     }
   }
@@ -325,7 +332,7 @@ static int launch_fa(bf16* out, const bf16* q, int q_row_stride, const int* posi
   if ((rc = tensor_map(k_pages, page_rows, D, D, kFaKeys, &mk))) return rc;
   if ((rc = tensor_map(v_pages, page_rows, D, D, kFaKeys, &mv))) return rc;
   constexpr int DB = D / 64;
-  constexpr size_t smem = 1024 + (size_t)(2 * DB + 4 * DB) * kFaKeys * 128 + kFaBars * 8 + 16;
+  constexpr size_t smem = (size_t)(2 * DB + (kFaKStages + kFaVStages) * DB) * kFaKeys * 128 + kFaBars * 8 + 16;
   auto kernel = attention_prefill_tc_kernel<D>;
   static bool configured[kMaxDevices] = {};
   int device = 0;
