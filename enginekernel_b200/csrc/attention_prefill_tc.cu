@@ -11,13 +11,14 @@
 //                      (tcgen05.st, two values a column); no thread needs another's numbers
 //   O += P . V        tcgen05.mma with P read from TMEM, accumulating in TMEM; the V page arrives
 //                      by TMA and is used as it lies (rows = keys, i.e. an MN-major operand)
-// The MMAs of one thread run in issue order, so the scores of page t+2 overwrite an S buffer only
-// after the P.V of page t has read its P from there: the buffers need no barrier of their own.
+// The scores of page t+2 overwrite an S buffer only after the P.V of page t, which reads its P
+// from there, is done: the S issuer waits for that page's pv_done barrier.
 // The running maximum is lazy: exponentials are taken against a reference that is raised (and O
 // and the running sum rescaled, by tcgen05.ld/st of the row) only when a page's maximum exceeds
 // it by more than 2^8, which keeps every probability finite in bfloat16 and skips the rescale
 // of almost every page.  O is divided by the sum once, at the end.
-// Warp 4 (one thread) is the TMA producer, warp 5 (one thread) issues the MMAs.  Shared memory
+// Warp 4 (one thread) is the TMA producer, warps 5 and 6 (one thread each) issue the S and the
+// P.V MMAs.  Shared memory
 // holds Q, three stages of K (the scores of page t+1 need their K two softmax steps ahead of
 // time, or the softmax warps wait for it) and two of V - 112 KB at head size 128 - and TMEM 256
 // columns (S, S, O): two blocks an SM.  Every wait is bounded and reports through `status`.
@@ -29,7 +30,7 @@ namespace ek {
 
 constexpr int kFaRows = 128;
 constexpr int kFaKeys = EK_PAGE;             // 64
-constexpr int kFaThreads = 192;              // 4 softmax warps, a producer warp, an MMA warp
+constexpr int kFaThreads = 224;              // 4 softmax warps, a producer warp, two MMA warps
 constexpr int kFaKStages = 3;                // K pages in flight: two pages of lookahead for the scores
 constexpr int kFaVStages = 2;
 // mbarriers: K full / empty per K stage, V full / empty per V stage, then per S buffer (2):
@@ -153,48 +154,50 @@ attention_prefill_tc_kernel(bf16* __restrict__ out, const bf16* q, int q_row_str
         tma_load_2d(smem_u32(v_s + (vs * DB + j) * kSub), &map_v, 64 * j, row, bar(kBarVFull + vs));
     }
   } else if (tid == 160) {
-    // ------------------------------------------------------------------- MMA issuer
+    // ------------------------------------------------------------------- issuer of S = Q.K^T
+    // Its own thread: every wait and commit costs this thread a few hundred cycles, and one
+    // thread issuing both kinds of MMA spent 2,000 cycles a page, more than the softmax needs.
     constexpr uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kFaKeys >> 3) << 17) |
                                  ((uint32_t)(kFaRows >> 4) << 24);
+    for (int it = 0; it < n_iter; ++it) {
+      const int s = it & 1;
+      const int ks = it % kFaKStages;
+      ok = mbar_wait(bar(kBarKFull + ks), (it / kFaKStages) & 1, status, 21);
+      // S buffer s still holds the P of page it-2 until that page's P.V is done (the other
+      // issuer's MMAs are not ordered against this one's)
+      if (ok && it >= 2) ok = mbar_wait(bar(kBarPvDone + s), ((it - 2) >> 1) & 1, status, 22);
+      if (!ok) break;
+      tc_fence_after();
+#pragma unroll
+      for (int j = 0; j < DB; ++j) {
+        const uint64_t dq = smem_desc_k_sw128(smem_u32(q_s + j * 2 * kSub));
+        const uint64_t dk = smem_desc_k_sw128(smem_u32(k_s + (ks * DB + j) * kSub));
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          tc_mma(tmem_base + kColS + 64 * s, dq + (uint64_t)(2 * k), dk + (uint64_t)(2 * k), idesc_s,
+                 (j | k) ? 1u : 0u);
+      }
+      tc_commit(bar(kBarKEmpty + ks));             // the K stage is free when these are done
+      tc_commit(bar(kBarSFull + s));               // S is complete
+    }
+  } else if (tid == 192) {
+    // ------------------------------------------------------------------- issuer of O += P.V
     constexpr uint32_t idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) |
                                   ((uint32_t)(D >> 3) << 17) | ((uint32_t)(kFaRows >> 4) << 24);
-    // page t is scored (into S buffer t & 1) before page t-1's P.V is issued, so the tensor
-    // pipe works on the next scores while the softmax warps work on the current ones
-    for (int it = 0; it <= n_iter && ok; ++it) {
-      if (it < n_iter) {
-        const int s = it & 1;
-        const int ks = it % kFaKStages;
-        ok = mbar_wait(bar(kBarKFull + ks), (it / kFaKStages) & 1, status, 21);
-        if (!ok) break;
-        tc_fence_after();
+    for (int u = 0; u < n_iter; ++u) {
+      const int s = u & 1;
+      const int vs = u % kFaVStages;
+      ok = mbar_wait(bar(kBarPFull + s), (u >> 1) & 1, status, 23);   // P written (O rescaled)
+      if (ok) ok = mbar_wait(bar(kBarVFull + vs), (u / kFaVStages) & 1, status, 24);   // V landed
+      if (!ok) break;
+      tc_fence_after();
+      const uint64_t dv = smem_desc_mn_sw128(smem_u32(v_s + vs * DB * kSub), kSub, 1024);
 #pragma unroll
-        for (int j = 0; j < DB; ++j) {
-          const uint64_t dq = smem_desc_k_sw128(smem_u32(q_s + j * 2 * kSub));
-          const uint64_t dk = smem_desc_k_sw128(smem_u32(k_s + (ks * DB + j) * kSub));
-#pragma unroll
-          for (int k = 0; k < 4; ++k)
-            tc_mma(tmem_base + kColS + 64 * s, dq + (uint64_t)(2 * k), dk + (uint64_t)(2 * k), idesc_s,
-                   (j | k) ? 1u : 0u);
-        }
-        tc_commit(bar(kBarKEmpty + ks));           // the K stage is free when these are done
-        tc_commit(bar(kBarSFull + s));             // S is complete
-      }
-      if (it >= 1) {
-        const int u = it - 1, s = u & 1;
-        const uint32_t phase = (u >> 1) & 1;
-        const int vs = u % kFaVStages;
-        ok = mbar_wait(bar(kBarPFull + s), phase, status, 23);        // P written (O rescaled)
-        if (ok) ok = mbar_wait(bar(kBarVFull + vs), (u / kFaVStages) & 1, status, 24);   // V landed
-        if (!ok) break;
-        tc_fence_after();
-        const uint64_t dv = smem_desc_mn_sw128(smem_u32(v_s + vs * DB * kSub), kSub, 1024);
-#pragma unroll
-        for (int k = 0; k < 4; ++k)                // 16 keys a step: 8 columns of P,
-          tc_mma_ts(tmem_base + kColO, tmem_base + kColS + 64 * s + 8 * k, dv + (uint64_t)(128 * k),
-                    idesc_pv, (u | k) ? 1u : 0u);  // 16 rows (2048 bytes) down V
-        tc_commit(bar(kBarVEmpty + vs));           // the V stage is free
-        tc_commit(bar(kBarPvDone + s));            // O holds pages 0..u
-      }
+      for (int k = 0; k < 4; ++k)                  // 16 keys a step: 8 columns of P,
+        tc_mma_ts(tmem_base + kColO, tmem_base + kColS + 64 * s + 8 * k, dv + (uint64_t)(128 * k),
+                  idesc_pv, (u | k) ? 1u : 0u);    // 16 rows (2048 bytes) down V
+      tc_commit(bar(kBarVEmpty + vs));             // the V stage is free
+      tc_commit(bar(kBarPvDone + s));              // O holds pages 0..u
     }
   }
 
@@ -212,24 +215,31 @@ attention_prefill_tc_kernel(bf16* __restrict__ out, const bf16* q, int q_row_str
       ok = mbar_wait(bar(kBarSFull + s), phase, status, 31);
       if (!ok) break;
       tc_fence_after();
-      float sc[kFaKeys];
-      tmem_ld32_nowait(lane_addr + kColS + 64 * s, sc);
-      tmem_ld32_nowait(lane_addr + kColS + 64 * s + 32, sc + 32);
-      tmem_ld_wait();
+      // Two passes over the 64 scores keep the registers of this thread under the limit that
+      // two blocks of 7 warps an SM set: first the maximum (keys 32..63 are only looked at,
+      // keys 0..31 stay in registers), then the exponentials of keys 0..31, their P, and the
+      // same for keys 32..63, read from TMEM once more.
       const bool full = key0 + kFaKeys - 1 <= pos_r && (window <= 0 || key0 > pos_r - window);
-      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // of the raw scores
-      if (full) {                                  // (the scale is positive)
+      auto load_half = [&](int h, float* v) {      // scores of keys key0 + 32 h .., masked
+        tmem_ld32_nowait(lane_addr + kColS + 64 * s + 32 * h, v);
+        tmem_ld_wait();
+        if (!full) {
 #pragma unroll
-        for (int i = 0; i < kFaKeys; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], sc[i]);
-      } else {
-#pragma unroll
-        for (int i = 0; i < kFaKeys; ++i) {
-          const int key = key0 + i;
-          const bool seen = key <= pos_r && (window <= 0 || key > pos_r - window);
-          sc[i] = seen ? sc[i] : -INFINITY;
-          mx4[i & 3] = fmaxf(mx4[i & 3], sc[i]);
+          for (int i = 0; i < 32; ++i) {
+            const int key = key0 + 32 * h + i;
+            const bool seen = key <= pos_r && (window <= 0 || key > pos_r - window);
+            v[i] = seen ? v[i] : -INFINITY;
+          }
         }
-      }
+      };
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // of the raw scores
+      float sc[32];                                // (the scale is positive)
+      load_half(1, sc);
+#pragma unroll
+      for (int i = 0; i < 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], sc[i]);
+      load_half(0, sc);
+#pragma unroll
+      for (int i = 0; i < 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], sc[i]);
       const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;
       // tcgen05.ld/st are warp-wide: if any row of the warp raises its reference, the whole warp
       // rescales (rows that keep theirs multiply by 1)
@@ -257,15 +267,16 @@ attention_prefill_tc_kernel(bf16* __restrict__ out, const bf16* q, int q_row_str
       }
       const float neg_m = m_ref == -INFINITY ? 0.f : -m_ref;
       float psum[4] = {0.f, 0.f, 0.f, 0.f};
-      // P over the scores it came from, 32 keys (16 columns) at a time so that the first store
-      // is under way while the second half is computed
+      // P over the scores it came from: 32 keys are 16 columns; the first store is under way
+      // while the second half is read again and computed
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
+        if (h == 1) load_half(1, sc);              // columns 32..63: untouched by the P of keys 0..31
         uint32_t w[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          const float p0 = ex2_approx(fmaf(sc[32 * h + i], scale_log2, neg_m));
-          const float p1 = ex2_approx(fmaf(sc[32 * h + i + 1], scale_log2, neg_m));
+          const float p0 = ex2_approx(fmaf(sc[i], scale_log2, neg_m));
+          const float p1 = ex2_approx(fmaf(sc[i + 1], scale_log2, neg_m));
           psum[i & 2] += p0;
           psum[(i & 2) + 1] += p1;
           __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);
