@@ -219,6 +219,134 @@ __global__ void sample_final_kernel(int* __restrict__ out_token, const float* pa
   if (threadIdx.x == 0) out_token[row] = best.index == 0x7fffffff ? 0 : best.index;
 }
 
+// The one-block kernel with a row spread over the 8 blocks of a thread-block cluster (wide
+// vocabularies with top-k): every block counts the radix digits of its piece of the row, the
+// blocks read one another's 256 counters through distributed shared memory and each takes the
+// same decision, four times; then each samples its piece above the threshold and block 0 takes
+// the best of the eight.  Same keys, same threshold, same noise (keyed by vocabulary index) and
+// same tie rules as `sample_kernel`, so the token is the same.
+constexpr int kTopkSegments = 8;
+
+__device__ __forceinline__ unsigned int ld_cluster_u32(const unsigned int* own, unsigned rank) {
+  unsigned a = (unsigned)__cvta_generic_to_shared(own), r, v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(rank));
+  asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(v) : "r"(r) : "memory");
+  return v;
+}
+
+__global__ void __launch_bounds__(256)
+sample_topk_cluster_kernel(int* __restrict__ out_token, const float* logits, long long row_stride,
+                           int vocab, float temperature, int top_k, unsigned long long seed,
+                           const int* streams, const int* draws, const int* active, const int* dyn) {
+  __shared__ Best scratch[33];
+  __shared__ unsigned int hist[256];
+  __shared__ unsigned int warp_total[8];
+  __shared__ unsigned int sel[2];                // digit chosen, keys still wanted below it
+  __shared__ float mine_score;
+  __shared__ int mine_index;
+  pdl_launch_dependents();
+  pdl_wait();
+  const int row = blockIdx.x, seg = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  if (active && active[row] < 0) return;         // the whole cluster (same row) leaves together
+  if (dyn) {
+    temperature = __int_as_float(dyn[0]);
+    top_k = dyn[1];
+    seed = (unsigned long long)(uint32_t)dyn[2] | ((unsigned long long)(uint32_t)dyn[3] << 32);
+  }
+  const float* x = logits + (size_t)row * row_stride;
+  // pieces are whole groups of 4 entries, so a Philox block never straddles two of them
+  const int groups = (vocab + 3) / 4;
+  const int per = (groups + kTopkSegments - 1) / kTopkSegments;
+  const int g_begin = min(groups, seg * per), g_end = min(groups, g_begin + per);
+  const int i_begin = 4 * g_begin, i_end = min(vocab, 4 * g_end);
+
+  uint32_t threshold_key = 0;                    // keep logits whose key >= this
+  if (temperature > 0.f && top_k > 0 && top_k < vocab) {
+    uint32_t prefix = 0, remaining = (uint32_t)top_k;
+    for (int shift = 24; shift >= 0; shift -= 8) {
+      hist[tid] = 0;
+      __syncthreads();
+      const uint32_t mask = shift == 24 ? 0u : (0xFFFFFFFFu << (shift + 8));
+      for (int i = i_begin + tid; i < i_end; i += 256) {
+        const uint32_t k = order_key(x[i]);
+        if ((k & mask) == prefix) atomicAdd(&hist[(k >> shift) & 255u], 1u);
+      }
+      cluster_sync();
+      // thread t looks after digit 255 - t: keys of the whole row with that digit, and with
+      // that digit or a larger one
+      unsigned int v = 0;
+#pragma unroll
+      for (int r = 0; r < kTopkSegments; ++r) v += ld_cluster_u32(&hist[255 - tid], (unsigned)r);
+      unsigned int incl = v;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const unsigned int up = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += up;
+      }
+      if (lane == 31) warp_total[warp] = incl;
+      __syncthreads();
+      for (int w = 0; w < warp; ++w) incl += warp_total[w];
+      const unsigned int excl = incl - v;
+      // the largest digit whose count reaches what is still wanted; digit 0 if none does
+      if (excl < remaining && (incl >= remaining || tid == 255)) {
+        sel[0] = 255u - (unsigned)tid;
+        sel[1] = remaining - excl;
+      }
+      __syncthreads();
+      prefix |= sel[0] << shift;
+      remaining = sel[1];
+      cluster_sync();                            // the counters are zeroed again only after all have read them
+    }
+    threshold_key = prefix;
+  }
+
+  Best best{-INFINITY, 0x7fffffff};
+  if (temperature > 0.f) {
+    const float inv_t = 1.f / temperature;
+    const uint32_t k0 = (uint32_t)seed, k1 = (uint32_t)(seed >> 32);
+    const uint32_t stream = streams ? (uint32_t)streams[row] : (uint32_t)row;
+    const uint32_t draw = draws ? (uint32_t)draws[row] : 0u;
+    for (int g = g_begin + tid; g < g_end; g += 256) {
+      uint32_t w[4];
+      philox4x32_10((uint32_t)g, draw, stream, 0u, k0, k1, w);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int i = 4 * g + j;
+        if (i >= vocab) break;
+        const float v = x[i];
+        if (order_key(v) < threshold_key || !(v == v)) continue;
+        const float u = ((float)(w[j] >> 9) + 0.5f) * (1.0f / 8388608.0f);
+        best = better(best, Best{v * inv_t - logf(-logf(u)), i});
+      }
+    }
+  } else {
+    for (int i = i_begin + tid; i < i_end; i += 256) {
+      const float v = x[i];
+      if (v == v) best = better(best, Best{v, i});
+    }
+  }
+  best = block_best(best, scratch);
+  if (tid == 0) {
+    mine_score = best.score;
+    mine_index = best.index;
+  }
+  cluster_sync();
+  if (seg == 0 && tid < 32) {
+    Best b{-INFINITY, 0x7fffffff};
+    if (tid < kTopkSegments) {
+      b.score = ld_cluster_f32(&mine_score, (unsigned)tid);
+      b.index = (int)ld_cluster_u32(reinterpret_cast<const unsigned int*>(&mine_index), (unsigned)tid);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      Best other{__shfl_xor_sync(0xffffffffu, b.score, o), __shfl_xor_sync(0xffffffffu, b.index, o)};
+      b = better(b, other);
+    }
+    if (tid == 0) out_token[row] = b.index == 0x7fffffff ? 0 : b.index;
+  }
+  cluster_sync();                                // nobody leaves while its result may be read
+}
+
 // After sampling: record the token, count the draw, decide whether the sequence goes on.
 // A row whose position is negative is finished: it emits -1 and nothing of it changes.
 __global__ void decode_advance_kernel(const int* sampled, int* token_ids, int* positions,
@@ -262,6 +390,19 @@ EK_EXPORT int ek_sample(int* out_token, const float* logits, long long row_strid
   return (int)ek::launch_pdl(ek::sample_kernel, dim3(rows), dim3(ek::kSampleThreads), 0, stream,
                              out_token, logits, row_stride, vocab, temperature, top_k, seed, streams,
                              draws, active, dyn);
+}
+
+// One launch, 8 blocks a row as a cluster; all of `ek_sample`'s modes, the same tokens.
+EK_EXPORT int ek_sample_cluster(int* out_token, const float* logits, long long row_stride, int rows,
+                                int vocab, float temperature, int top_k, unsigned long long seed,
+                                const int* streams, const int* draws, const int* active,
+                                const int* dyn, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (vocab <= 0 || temperature < 0.f || top_k < 0 || rows > 2147483647) return EK_ERR_ARG;
+  return (int)ek::launch_pdl_cluster(ek::sample_topk_cluster_kernel, dim3(rows, ek::kTopkSegments),
+                                     dim3(256), 0, stream, ek::kTopkSegments, out_token, logits,
+                                     row_stride, vocab, temperature, top_k, seed, streams, draws, active,
+                                     dyn);
 }
 
 // Two launches over `segments` pieces of the vocabulary; top-k is not offered here.

@@ -75,9 +75,13 @@ class DecodeState:
                                                       sampling.seed, self.settings.device))
 
     def sample_and_advance(self, logits):
-        if self.top_k > 0 or logits.shape[-1] < 4096:
+        if logits.shape[-1] < 4096:
             kernels.sample(self.sampled, logits, 0.0, 0, 0, streams=self.streams, draws=self.draws,
                            active=self.positions, n_rows=self.batch, dyn=self.settings)
+        elif self.top_k > 0:
+            kernels.sample_cluster(self.sampled, logits, 0.0, 0, 0, streams=self.streams,
+                                   draws=self.draws, active=self.positions, n_rows=self.batch,
+                                   dyn=self.settings)
         else:
             kernels.sample_wide(self.sampled, logits, 0.0, 0, self.part_score, self.part_index,
                                 streams=self.streams, draws=self.draws, active=self.positions,

@@ -509,6 +509,24 @@ def sample(out_token, logits, temperature, top_k, seed, streams=None, draws=None
 SAMPLE_SEGMENTS = 32
 
 
+_sample_cluster = Function("sampling", "ek_sample_cluster",
+                           [_P, _P, c_longlong, c_int, c_int, c_float, c_int, c_ulonglong, _P, _P, _P, _P, _P])
+
+
+def sample_cluster(out_token, logits, temperature, top_k, seed, streams=None, draws=None, active=None,
+                   n_rows=None, dyn=None):
+    """:func:`sample` with each row spread over the 8 blocks of a thread-block cluster (wide
+    vocabularies with top-k: the radix digits are counted by all 8 and read through distributed
+    shared memory).  Same tokens as :func:`sample`."""
+    _need_cuda(out_token, logits, streams, draws, active, dyn)
+    _need(logits.dtype == torch.float32 and logits.stride(-1) == 1, "sample: dense 32-bit logits")
+    _need(out_token.dtype == torch.int32, "sample: int32 out")
+    rows = n_rows if n_rows is not None else logits.shape[0]
+    _sample_cluster(_ptr(out_token), _ptr(logits), logits.stride(0), rows, logits.shape[-1],
+                    float(temperature), int(top_k), int(seed) & 0xFFFFFFFFFFFFFFFF, _ptr(streams),
+                    _ptr(draws), _ptr(active), _ptr(dyn), _stream())
+
+
 def sample_wide(out_token, logits, temperature, seed, part_score, part_index, streams=None,
                 draws=None, active=None, n_rows=None, dyn=None):
     """:func:`sample` without top-k, spread over ``SAMPLE_SEGMENTS`` blocks a row (for wide

@@ -637,6 +637,34 @@ def test_sample_wide_equals_the_one_block_kernel():
             assert wide[2].item() == 5
 
 
+def test_sample_cluster_equals_the_one_block_kernel():
+    """Eight blocks a row as a cluster: the same token as the one-block kernel in every mode, with
+    ties at the top-k threshold, ties across pieces, top_k of 1 and of nearly the vocabulary, NaN
+    and -inf entries, rows switched off, settings read from the device."""
+    k = K()
+    for vocab in (4099, 151936, 50):
+        g = torch.Generator().manual_seed(vocab)
+        logits = (torch.randn(6, vocab, generator=g) * 2).to(DEV)
+        logits[2, 5] = logits[2, vocab - 1] = 40.0            # a tie across pieces
+        logits[4, :40] = 3.25                                  # many equal values around a threshold
+        logits[5, 7] = float("nan")
+        logits[5, 11] = float("-inf")
+        streams = torch.tensor([3, 1, 4, 1, 5, 9], dtype=torch.int32, device=DEV)
+        draws = torch.tensor([0, 1, 2, 3, 4, 5], dtype=torch.int32, device=DEV)
+        active = torch.tensor([1, 1, 1, -1, 1, 1], dtype=torch.int32, device=DEV)
+        for temp, topk, seed in ((0.0, 0, 0), (0.9, 0, 77), (0.9, 50, 77), (1.3, 1, 5), (0.7, 17, (1 << 35) + 1),
+                                 (1.0, vocab - 1, 9), (1.0, vocab + 5, 9), (2.0, 1000, 3)):
+            one = torch.full((6,), -5, dtype=torch.int32, device=DEV)
+            many = torch.full((6,), -5, dtype=torch.int32, device=DEV)
+            k.sample(one, logits, temp, topk, seed, streams=streams, draws=draws, active=active)
+            k.sample_cluster(many, logits, temp, topk, seed, streams=streams, draws=draws, active=active)
+            assert torch.equal(one, many) and many[3].item() == -5, (vocab, temp, topk)
+            dyn = torch.full((6,), -5, dtype=torch.int32, device=DEV)
+            k.sample_cluster(dyn, logits, 0.0, 0, 0, streams=streams, draws=draws, active=active,
+                             dyn=k.sampling_settings(temp, topk, seed, DEV))
+            assert torch.equal(dyn, many)
+
+
 def test_sample_distribution():
     """Many draws of one row follow softmax(logits / T)."""
     k = K()
