@@ -26,7 +26,8 @@ namespace ek {
 
 constexpr int kDtWarps = 4;                  // consumer warps
 constexpr int kDtThreads = (kDtWarps + 1) * 32;
-constexpr int kDtMaxSplits = 8;              // blocks of a cluster (the portable limit)
+constexpr int kDtPortableSplits = 8;         // blocks of a cluster: the portable limit
+constexpr int kDtMaxSplits = 16;             // and the limit with the attribute for larger ones
 
 __device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2,
                                         uint32_t& r3) {
@@ -323,7 +324,7 @@ attention_decode_tma_kernel(bf16* __restrict__ out, const bf16* q, int q_row_str
 
 // DEEP: a ring twice as deep (192 KB, one block an SM) for launches that leave SMs empty anyway, so
 // that more of a block's pages are on their way before the wait returns.
-template <int D, bool DEEP>
+template <int D, bool DEEP, bool QUERY = false>
 static int launch_dt(bf16* out, const bf16* q, int q_row_stride, const int* positions,
                      const int* token_slot, const void* k_pages, const void* v_pages,
                      long long page_rows, const int* block_table, int table_stride, int n_tokens,
@@ -334,8 +335,10 @@ static int launch_dt(bf16* out, const bf16* q, int q_row_stride, const int* posi
   constexpr size_t smem = 1024 + (size_t)STAGES * 2 * DB * EK_PAGE * 128 + 2 * STAGES * 8;
   CUtensorMap mk, mv;
   int rc;
-  if ((rc = tensor_map(k_pages, page_rows, D, D, EK_PAGE, &mk))) return rc;
-  if ((rc = tensor_map(v_pages, page_rows, D, D, EK_PAGE, &mv))) return rc;
+  if (!QUERY) {
+    if ((rc = tensor_map(k_pages, page_rows, D, D, EK_PAGE, &mk))) return rc;
+    if ((rc = tensor_map(v_pages, page_rows, D, D, EK_PAGE, &mv))) return rc;
+  }
   auto kernel = attention_decode_tma_kernel<D, STAGES>;
   static bool configured[kMaxDevices] = {};
   int device = 0;
@@ -345,10 +348,31 @@ static int launch_dt(bf16* out, const bf16* q, int q_row_stride, const int* posi
   if (!configured[device]) {
     e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
+    if (!DEEP) {                                 // clusters of 9 to 16 blocks (two blocks an SM only)
+      e = cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+      if (e != cudaSuccess) return (int)e;
+    }
     configured[device] = true;
   }
   prefer_carveout((const void*)kernel, 100);
   dim3 grid(n_splits, n_kv_heads, n_tokens);
+  if (QUERY) {                                   // can a cluster of 16 of these blocks run at all?
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(kDtMaxSplits, 1, 1);
+    cfg.blockDim = dim3(kDtThreads);
+    cfg.dynamicSmemBytes = smem;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = kDtMaxSplits;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int clusters = 0;
+    e = cudaOccupancyMaxActiveClusters(&clusters, kernel, &cfg);
+    if (e != cudaSuccess) { cudaGetLastError(); return 0; }
+    return clusters;
+  }
   if (n_splits > 1)
     return (int)launch_pdl_cluster_x(kernel, grid, dim3(kDtThreads), smem, stream, n_splits, out, q,
                                      q_row_stride, positions, token_slot, mk, mv, block_table,
@@ -361,7 +385,23 @@ static int launch_dt(bf16* out, const bf16* q, int q_row_stride, const int* posi
 
 }  // namespace ek
 
-// head_dim 64 or 128; at most 16 query heads a KV head; 1 to 8 splits (each takes whole pages of
+// How many blocks may share a token on this device: 16 if clusters of that size can be
+// scheduled for this head size, else 8 (0: the head size has no such kernel).
+EK_EXPORT int ek_attention_decode_tma_max_splits(int head_dim) {
+  using namespace ek;
+  int clusters = 0;
+  if (head_dim == 64)
+    clusters = launch_dt<64, false, true>(nullptr, nullptr, 0, nullptr, nullptr, &clusters, &clusters, 64,
+                                          nullptr, 0, 1, 1, 1, 1.f, 0, 1, nullptr, nullptr);
+  else if (head_dim == 128)
+    clusters = launch_dt<128, false, true>(nullptr, nullptr, 0, nullptr, nullptr, &clusters, &clusters, 64,
+                                           nullptr, 0, 1, 1, 1, 1.f, 0, 1, nullptr, nullptr);
+  else
+    return 0;
+  return clusters >= 1 ? kDtMaxSplits : kDtPortableSplits;
+}
+
+// head_dim 64 or 128; at most 16 query heads a KV head; 1 to 16 splits (each takes whole pages of
 // the token's visible range); q rows 4-byte aligned; n_pages = pages in k_pages / v_pages
 // ([pages, kv heads, 64, head_dim]); `status` is one int on the device.
 EK_EXPORT int ek_attention_decode_tma(void* out, const void* q, int q_row_stride,
@@ -377,7 +417,8 @@ EK_EXPORT int ek_attention_decode_tma(void* out, const void* q, int q_row_stride
       ((uintptr_t)q & 3) || !status || n_kv_heads > 65535 || n_tokens > 65535 || n_pages <= 0)
     return EK_ERR_ARG;
   const long long page_rows = (long long)n_pages * n_kv_heads * EK_PAGE;
-  const bool deep = (long long)n_tokens * n_kv_heads * n_splits <= 148;     // one block an SM at most
+  // one block an SM at most, and a cluster of the portable size (a deep ring is one block an SM)
+  const bool deep = (long long)n_tokens * n_kv_heads * n_splits <= 148 && n_splits <= kDtPortableSplits;
 #define EK_DT(D_, DEEP_)                                                                          \
   return launch_dt<D_, DEEP_>((bf16*)out, (const bf16*)q, q_row_stride, positions, token_slot,     \
                               k_pages, v_pages, page_rows, block_table, table_stride, n_tokens,   \

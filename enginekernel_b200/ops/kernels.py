@@ -209,7 +209,21 @@ def attention_decode_bf16(out, q, n_tokens, positions, token_slot, k_pages, v_pa
 _attn_decode_tma = Function("attention_decode_tma", "ek_attention_decode_tma",
                             [_P, _P, c_int, _P, _P, _P, _P, c_int, _P, c_int, c_int, c_int, c_int, c_int,
                              c_float, c_int, c_int, _P, _P])
-DECODE_TMA_MAX_SPLITS = 8
+_attn_decode_tma_max = Function("attention_decode_tma", "ek_attention_decode_tma_max_splits", [c_int],
+                                check_status=False)
+DECODE_TMA_PORTABLE_SPLITS = 8
+_decode_tma_max_splits = {}
+
+
+def decode_tma_max_splits(head_dim, device=None):
+    """Blocks that may share one token's pages in :func:`attention_decode_tma`: 16 where the device
+    schedules thread-block clusters of that size for this head size, else the portable 8."""
+    key = (head_dim, torch.cuda.current_device() if device is None else torch.device(device).index)
+    if key not in _decode_tma_max_splits:
+        with torch.cuda.device(key[1] if key[1] is not None else torch.cuda.current_device()):
+            n = int(_attn_decode_tma_max(head_dim))
+        _decode_tma_max_splits[key] = n if n in (8, 16) else DECODE_TMA_PORTABLE_SPLITS
+    return _decode_tma_max_splits[key]
 
 
 def attention_decode_tma_supported(dtype, head_dim, n_q_heads, n_kv_heads):
@@ -220,7 +234,8 @@ def attention_decode_tma(out, q, n_tokens, positions, token_slot, k_pages, v_pag
                          n_q_heads, n_kv_heads, head_dim, scale, window=None, n_splits=1):
     """One new token per sequence (bfloat16, head size 64 or 128, at most 16 heads a group): the
     cache pages come by TMA, started before the kernel ahead has finished; ``n_splits`` (1 to 8)
-    blocks share a token's pages and merge inside a thread-block cluster."""
+    blocks (16 where :func:`decode_tma_max_splits` says so) share a token's pages and merge inside
+    a thread-block cluster."""
     _need_cuda(out, q, positions, token_slot, k_pages, v_pages, block_table)
     _need(attention_decode_tma_supported(q.dtype, head_dim, n_q_heads, n_kv_heads),
           "attention_decode_tma: bfloat16, head size 64 or 128, at most 16 query heads a KV head")
@@ -230,7 +245,8 @@ def attention_decode_tma(out, q, n_tokens, positions, token_slot, k_pages, v_pag
           "attention: dense, 4-byte aligned q rows")
     _need(k_pages.is_contiguous() and v_pages.is_contiguous() and k_pages.dim() == 4
           and k_pages.shape[1:] == (n_kv_heads, PAGE, head_dim), "attention: pages [P, NKV, 64, D]")
-    _need(1 <= n_splits <= DECODE_TMA_MAX_SPLITS, "attention_decode_tma: 1 to 8 splits")
+    _need(1 <= n_splits <= decode_tma_max_splits(head_dim, q.device),
+          f"attention_decode_tma: 1 to {decode_tma_max_splits(head_dim, q.device)} splits on this device")
     _need(n_tokens <= 65535, "attention_decode_tma: at most 65535 tokens a call")
     _attn_decode_tma(_ptr(out), _ptr(q), q.stride(0), _ptr(positions), _ptr(token_slot),
                      _ptr(k_pages), _ptr(v_pages), k_pages.shape[0], _ptr(block_table),

@@ -60,8 +60,10 @@ def check(status: int, what: str) -> None:
 class Function:
     """A C entry point with its argument types bound once."""
 
-    def __init__(self, module: str, name: str, argtypes):
+    def __init__(self, module: str, name: str, argtypes, check_status: bool = True):
+        """``check_status`` False: the entry point launches nothing and returns a value, not a status."""
         self.module, self.name, self.argtypes = module, name, argtypes
+        self.check_status = check_status
         self._fn = None
 
     def _bind(self):
@@ -78,5 +80,7 @@ class Function:
     def __call__(self, *args):
         global _launch_calls
         fn = self._fn or self._bind()
+        if not self.check_status:
+            return fn(*args)
         _launch_calls += 1
         check(fn(*args), self.name)

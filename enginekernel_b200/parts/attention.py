@@ -110,7 +110,10 @@ class Attention(Mixer):
             # splits of a token are one cluster
             blocks = t * self.num_kv_heads
             pages = -(-visible // kernels.PAGE)
-            splits = max(1, min(2 * SM_COUNT // blocks, pages, kernels.DECODE_TMA_MAX_SPLITS))
+            # (more than 8 blocks a token only pay with many pages each: long contexts, few sequences)
+            limit = kernels.decode_tma_max_splits(self.head_dim, self.device) if pages >= 64 else \
+                kernels.DECODE_TMA_PORTABLE_SPLITS
+            splits = max(1, min(2 * SM_COUNT // blocks, pages, limit))
             kernels.attention_decode_tma(
                 out, qkv, t, ctx.positions, ctx.token_slot, entry.k_pages, entry.v_pages,
                 entry.block_table, self.num_heads, self.num_kv_heads, self.head_dim, self.scale,

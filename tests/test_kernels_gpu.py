@@ -347,8 +347,11 @@ def test_attention_decode_tma(nq, nkv, d):
     positions = torch.tensor([p for _, p in toks], dtype=torch.int32, device=DEV)
     slots = torch.tensor([s for s, _ in toks], dtype=torch.int32, device=DEV)
     scale = 1.0 / math.sqrt(d)
-    for window, splits in ((None, 1), (None, 2), (None, 5), (None, 8), (100, 1), (64, 3), (1, 1),
-                           (17, 8), (700, 4)):
+    cases = [(None, 1), (None, 2), (None, 5), (None, 8), (100, 1), (64, 3), (1, 1), (17, 8), (700, 4)]
+    most = k.decode_tma_max_splits(d, DEV)
+    if most > 8:                                   # clusters of more than the portable 8 blocks
+        cases += [(None, 16), (None, 11), (300, 13)]
+    for window, splits in cases:
         out = torch.full((t, nq * d), 7.0, dtype=dtype, device=DEV)
         k.attention_decode_tma(out, q, t, positions, slots, pages.k, pages.v, pages.table, nq, nkv, d,
                                scale, window, splits)
@@ -364,7 +367,7 @@ def test_attention_decode_tma(nq, nkv, d):
     from enginekernel_b200.ops.lib import KernelError
     with pytest.raises(KernelError):
         k.attention_decode_tma(out, q, t, positions, slots, pages.k, pages.v, pages.table, nq, nkv, d,
-                               scale, None, 9)
+                               scale, None, most + 1)
 
 
 @pytest.mark.parametrize("nq,nkv,d", [(4, 2, 16), (6, 2, 48), (32, 8, 128), (5, 5, 80), (16, 1, 256),
