@@ -274,3 +274,22 @@ def test_norms_moved_into_the_products_change_rounding_only(engines, plains, tag
     assert helpers.rel_err(got[limit], want) <= helpers.TOL["bfloat16"]
     assert helpers.rel_err(got[0], want) <= helpers.TOL["bfloat16"]
     assert helpers.rel_err(got[limit], got[0]) <= helpers.TOL["bfloat16"]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_context_decode(tmp_path, dtype):
+    """4,200 cached tokens for one sequence: 66 cache pages, so the decode attention cuts them
+    over as many blocks as the device allows a cluster (16 where it can); a second, shorter
+    sequence decodes beside it and ends earlier."""
+    from enginekernel_b200 import Engine
+    cfg = dict(tiny_models.TINY_E, max_position_embeddings=8192, num_hidden_layers=2)
+    folder = helpers.make_folder(tmp_path, cfg, 5)
+    model = helpers.plain_model(folder)
+    eng = Engine(folder, dtype, max_tokens=2 * 4352, max_batch=2)
+    seqs = tiny_models.random_prompts(cfg, [4208, 1300], seed=9)
+    got = helpers.batch_then_steps(eng, seqs, [4200, 1296])
+    for s, g in zip(seqs, got):
+        want = plain.logits(model, s)
+        tail = slice(len(s) - 12, len(s))
+        err = helpers.rel_err(g[tail], want[tail])
+        assert err <= helpers.TOL[dtype], (dtype, len(s), err)
