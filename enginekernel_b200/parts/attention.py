@@ -114,6 +114,7 @@ class Attention(Mixer):
             limit = kernels.decode_tma_max_splits(self.head_dim, self.device) if pages >= 64 else \
                 kernels.DECODE_TMA_PORTABLE_SPLITS
             splits = max(1, min(2 * SM_COUNT // blocks, pages, limit))
+            splits = 1 << (splits.bit_length() - 1)      # clusters of 3, 5, 6, 7 pack the GPCs badly
             kernels.attention_decode_tma(
                 out, qkv, t, ctx.positions, ctx.token_slot, entry.k_pages, entry.v_pages,
                 entry.block_table, self.num_heads, self.num_kv_heads, self.head_dim, self.scale,
