@@ -64,6 +64,20 @@ struct TcParams {
   int ld_stream;
   const float* next_gain;   // [rows_p]
   float* ss_out;        // [rows_q][gridDim.x]
+  // The q/k/v product of an attention layer with heads of 128 (swapped form, bfloat16 result): a
+  // 128-row tile is one head, so the per-head RMSNorm of q and k, the rotation by the token's
+  // position and the write of k and v into the paged cache are done on the 32-bit sums, with one
+  // rounding; q goes to `out`.  Same arithmetic as qk_norm_rope_kv_kernel.
+  const int* qkv_positions;   // [rows_q], or null: not this form
+  const int* qkv_slots;
+  const float* q_gain;        // [128] or null
+  const float* k_gain;
+  const float* cos_tab;       // [positions][64]
+  const float* sin_tab;
+  PagedKV cache;
+  int n_q_heads;
+  int write_kv;
+  float qk_eps;
 };
 
 // --------------------------------------------------------------------------------- kernel
@@ -312,7 +326,46 @@ gemm_tc_bf16_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
             n_out = tile_p * kTcBM + r0;
             n_limit = prm.rows_p;
           }
-          if (fused_add) {
+          if (EPI == TC_EPI_BF16 && prm.qkv_positions != nullptr) {
+            // head = tile; everything below is uniform over the warp except the lane's 4 dimensions
+            const int head = tile_p, n_kv = prm.cache.heads;
+            const int pos = idx < owned ? prm.qkv_positions[m] : -1;
+            const bool is_q = head < prm.n_q_heads, is_k = !is_q && head < prm.n_q_heads + n_kv;
+            if (pos >= 0 && (is_q || prm.write_kv) && head < prm.n_q_heads + 2 * n_kv) {
+              float y[4] = {acc.x, acc.y, acc.z, acc.w};
+              if (is_q || is_k) {
+                const float* gain = is_q ? prm.q_gain : prm.k_gain;
+                if (gain != nullptr) {
+                  const float ss = warp_sum(y[0] * y[0] + y[1] * y[1] + y[2] * y[2] + y[3] * y[3]);
+                  const float rstd = rsqrtf(ss / 128.f + prm.qk_eps);
+                  const float4 g4 = *reinterpret_cast<const float4*>(gain + r0);
+                  y[0] = y[0] * rstd * g4.x; y[1] = y[1] * rstd * g4.y;
+                  y[2] = y[2] * rstd * g4.z; y[3] = y[3] * rstd * g4.w;
+                }
+                // dimension d pairs with d + 64: 16 lanes further on, same place in the lane
+                const float4 cs = *reinterpret_cast<const float4*>(prm.cos_tab + (size_t)pos * 64 + (r0 & 63));
+                const float4 sn = *reinterpret_cast<const float4*>(prm.sin_tab + (size_t)pos * 64 + (r0 & 63));
+                const float c[4] = {cs.x, cs.y, cs.z, cs.w}, sv[4] = {sn.x, sn.y, sn.z, sn.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  const float partner = __shfl_xor_sync(0xffffffffu, y[i], 16);
+                  y[i] = lane < 16 ? y[i] * c[i] - partner * sv[i] : y[i] * c[i] + partner * sv[i];
+                }
+              }
+              bf16* dst;
+              if (is_q) {
+                dst = (bf16*)prm.out + (size_t)m * prm.ldo + n_out;
+              } else {
+                const int page = prm.cache.block_table[(size_t)prm.qkv_slots[m] * prm.cache.table_stride +
+                                                       pos / EK_PAGE];
+                const int kv_head = is_k ? head - prm.n_q_heads : head - prm.n_q_heads - n_kv;
+                dst = (bf16*)(is_k ? prm.cache.k : prm.cache.v) + page_offset(prm.cache, page, kv_head, pos) + r0;
+              }
+              __nv_bfloat162 lo = __floats2bfloat162_rn(y[0], y[1]), hi = __floats2bfloat162_rn(y[2], y[3]);
+              *reinterpret_cast<uint2*>(dst) =
+                  make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+            }
+          } else if (fused_add) {
             // rows_p and the strides are multiples of 4 here (checked by the launcher)
             float ssq = 0.f;
             if (idx < owned && n_out < n_limit) {
@@ -512,19 +565,19 @@ static int launch_tc(const CUtensorMap& mp, const CUtensorMap& mq, const TcParam
 // at most 8, else through `partials` (at least tiles * k_split * bn * 128 floats) and zeroed
 // `tickets` (at least `tiles`).
 // K, ldx, ldw must be multiples of 8; `status` is one int on the device.
-EK_EXPORT int ek_gemm_tc_bf16(void* out, const void* x, const void* w, int M, int N, int K, int ldx,
-                              int ldw, int ldo, int epilogue, int swap, int k_split, int cluster,
-                              float* partials, unsigned int* tickets, long long partial_floats,
-                              int n_tickets, const float* ss_in, int ss_tiles, int norm_size, float eps,
-                              float* residual, int ld_residual, const float* next_gain, float* ss_out,
-                              int* status, cudaStream_t stream) {
+static int gemm_tc_run(const ek::TcParams& extras, void* out, const void* x, const void* w, int M, int N,
+                       int K, int ldx, int ldw, int ldo, int epilogue, int swap, int k_split, int cluster,
+                       float* partials, unsigned int* tickets, long long partial_floats, int n_tickets,
+                       const float* ss_in, int ss_tiles, int norm_size, float eps, float* residual,
+                       int ld_residual, const float* next_gain, float* ss_out, int* status,
+                       cudaStream_t stream) {
   using namespace ek;
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0 || K % 8 || ldx % 8 || ldw % 8 || !status || epilogue < 0 || epilogue > 2 ||
       (epilogue == TC_EPI_SWIGLU && (N & 1)) || ((uintptr_t)x & 15) || ((uintptr_t)w & 15))
     return EK_ERR_ARG;
   const int k_blocks = (K + kTcBK - 1) / kTcBK;
-  TcParams prm{};
+  TcParams prm = extras;
   prm.out = out; prm.ldo = ldo; prm.k_blocks = k_blocks; prm.status = status;
   prm.partials = partials; prm.tickets = tickets;
   prm.swiglu_half = N / 2;
@@ -548,7 +601,7 @@ EK_EXPORT int ek_gemm_tc_bf16(void* out, const void* x, const void* w, int M, in
     prm.k_blocks_per_split = (k_blocks + k_split - 1) / k_split;
     k_split = (k_blocks + prm.k_blocks_per_split - 1) / prm.k_blocks_per_split;
     const bool clustered = cluster && k_split > 1 && k_split <= kTcMaxCluster;
-    if (k_split > 1 && !clustered && (ss_in || residual || !partials || !tickets || tiles > n_tickets ||
+    if (k_split > 1 && !clustered && (ss_in || residual || prm.qkv_positions || !partials || !tickets || tiles > n_tickets ||
                                       (long long)tiles * k_split * bn * kTcBM > partial_floats)) {
       k_split = 1;                             // (the deferred-norm forms have no scratch path)
       prm.k_blocks_per_split = k_blocks;
@@ -585,4 +638,52 @@ EK_EXPORT int ek_gemm_tc_bf16(void* out, const void* x, const void* w, int M, in
   if (epilogue == TC_EPI_BF16) return launch_tc<BN, TC_EPI_BF16, false>(mp, mq, prm, grid, stream);
   if (epilogue == TC_EPI_F32) return launch_tc<BN, TC_EPI_F32, false>(mp, mq, prm, grid, stream);
   return launch_tc<BN, TC_EPI_SWIGLU, false>(mp, mq, prm, grid, stream);
+}
+
+EK_EXPORT int ek_gemm_tc_bf16(void* out, const void* x, const void* w, int M, int N, int K, int ldx,
+                              int ldw, int ldo, int epilogue, int swap, int k_split, int cluster,
+                              float* partials, unsigned int* tickets, long long partial_floats,
+                              int n_tickets, const float* ss_in, int ss_tiles, int norm_size, float eps,
+                              float* residual, int ld_residual, const float* next_gain, float* ss_out,
+                              int* status, cudaStream_t stream) {
+  return gemm_tc_run(ek::TcParams{}, out, x, w, M, N, K, ldx, ldw, ldo, epilogue, swap, k_split, cluster,
+                     partials, tickets, partial_floats, n_tickets, ss_in, ss_tiles, norm_size, eps,
+                     residual, ld_residual, next_gain, ss_out, status, stream);
+}
+
+// The q/k/v product of an attention layer whose heads are 128 wide and fully rotated, for at most
+// 64 rows: qkv = x . w^T (optionally with the row scale of a deferred norm), then per head the
+// RMSNorm of q and k (gains may be null), the rotation by cos/sin[position] ([P, 64] each), q to
+// `out` [M, (NQ + 2 NKV) * 128] and, with write_kv, k and v into the pages at the token's place.
+// Up to 8 K splits as a cluster.
+EK_EXPORT int ek_gemm_tc_qkv_rope(void* out, const void* x, const void* w, int M, int K, int ldx, int ldw,
+                                  int ldo, int k_split, const float* ss_in, int ss_tiles, int norm_size,
+                                  float eps, const float* q_gain, const float* k_gain, float qk_eps,
+                                  const float* cos_tab, const float* sin_tab, const int* positions,
+                                  const int* token_slot, void* k_pages, void* v_pages,
+                                  const int* block_table, int table_stride, int n_q_heads,
+                                  int n_kv_heads, int write_kv, int* status, cudaStream_t stream) {
+  using namespace ek;
+  if (M <= 0) return 0;
+  if (M > 64 || n_q_heads <= 0 || n_kv_heads <= 0 || !positions || !token_slot || !cos_tab || !sin_tab ||
+      !k_pages || !v_pages || !block_table || ldo % 4 || ((uintptr_t)out & 7) ||
+      ((uintptr_t)cos_tab & 15) || ((uintptr_t)sin_tab & 15) || ((uintptr_t)q_gain & 15) ||
+      ((uintptr_t)k_gain & 15) || ((uintptr_t)k_pages & 7) || ((uintptr_t)v_pages & 7))
+    return EK_ERR_ARG;
+  TcParams extras{};
+  extras.qkv_positions = positions;
+  extras.qkv_slots = token_slot;
+  extras.q_gain = q_gain;
+  extras.k_gain = k_gain;
+  extras.cos_tab = cos_tab;
+  extras.sin_tab = sin_tab;
+  extras.cache = PagedKV{k_pages, v_pages, block_table, table_stride, n_kv_heads, kTcBM};
+  extras.n_q_heads = n_q_heads;
+  extras.write_kv = write_kv;
+  extras.qk_eps = qk_eps;
+  const int N = (n_q_heads + 2 * n_kv_heads) * kTcBM;
+  if (k_split > kTcMaxCluster) k_split = kTcMaxCluster;
+  return gemm_tc_run(extras, out, x, w, M, N, K, ldx, ldw, ldo, TC_EPI_BF16, 1, k_split, 1, nullptr,
+                     nullptr, 0, 0, ss_in, ss_tiles, norm_size, eps, nullptr, 0, nullptr, nullptr, status,
+                     stream);
 }

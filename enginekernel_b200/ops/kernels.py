@@ -488,6 +488,56 @@ def gemm_tc_bf16(out, x, w, epilogue=EPI_BF16, n_rows=None, swap=None, k_split=N
              _ptr(stream), ld_stream, _ptr(gain), _ptr(ss_out), _ptr(tc_status(x.device)), _stream())
 
 
+_gemm_tc_qkv = Function("gemm_tc_bf16", "ek_gemm_tc_qkv_rope",
+                        [_P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P, c_int, c_int, c_float,
+                         _P, _P, c_float, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, _P, _P])
+QKV_ROPE_HEAD_DIM = 128
+
+
+def gemm_tc_qkv_rope(qkv, x, w, n_rows, q_gain, k_gain, qk_eps, cos, sin, positions, token_slot, k_pages,
+                     v_pages, block_table, n_q_heads, n_kv_heads, write_kv=True, row_scale=None,
+                     k_split=None):
+    """The q/k/v product of an attention layer with heads of 128, fully rotated, for at most 64
+    rows, with :func:`qk_norm_rope_kv` done in its epilogue on the 32-bit sums: q (normalised,
+    rotated) goes to the q part of ``qkv`` [rows, (NQ + 2 NKV) * 128], k and v to the pages.
+    ``row_scale`` as in :func:`gemm_tc_bf16`."""
+    _need_cuda(qkv, x, w, cos, sin, positions, token_slot, k_pages, v_pages, block_table)
+    m, (n, k) = n_rows, w.shape
+    _need(x.dtype == w.dtype == qkv.dtype == k_pages.dtype == v_pages.dtype == torch.bfloat16,
+          "gemm_tc_qkv_rope: bfloat16 operands, result and cache")
+    _need(m <= TC_SWAP_MAX_ROWS and n == (n_q_heads + 2 * n_kv_heads) * QKV_ROPE_HEAD_DIM,
+          "gemm_tc_qkv_rope: at most 64 rows, heads of 128")
+    _need(k % 8 == 0 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and x.stride(-1) == 1
+          and w.stride(-1) == 1 and x.shape[-1] == k and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0,
+          "gemm_tc_qkv_rope: dense, 16-byte aligned operand rows")
+    _need(qkv.stride(-1) == 1 and qkv.shape[-1] == n and qkv.stride(0) % 4 == 0 and qkv.shape[0] >= m,
+          "gemm_tc_qkv_rope: qkv [rows, (NQ + 2 NKV) * 128]")
+    _need(cos.dtype == torch.float32 and sin.dtype == torch.float32 and cos.is_contiguous()
+          and sin.is_contiguous() and cos.shape[-1] == QKV_ROPE_HEAD_DIM // 2,
+          "gemm_tc_qkv_rope: 32-bit tables of 64 columns")
+    for g in (q_gain, k_gain):
+        _need(g is None or (g.is_cuda and g.dtype == torch.float32 and g.numel() == QKV_ROPE_HEAD_DIM),
+              "qk gains: 32-bit [128]")
+    _need(k_pages.is_contiguous() and v_pages.is_contiguous() and k_pages.dim() == 4
+          and k_pages.shape[1:] == (n_kv_heads, PAGE, QKV_ROPE_HEAD_DIM), "attention: pages [P, NKV, 64, 128]")
+    _need(block_table.dtype == torch.int32 and positions.dtype == torch.int32
+          and token_slot.dtype == torch.int32, "gemm_tc_qkv_rope: int32 indices")
+    ss_in, ss_tiles, size, eps = None, 0, 0, 0.0
+    if row_scale is not None:
+        ss_in, size, eps = row_scale
+        _need(ss_in.is_cuda and ss_in.dtype == torch.float32 and ss_in.is_contiguous() and ss_in.dim() == 2
+              and ss_in.shape[0] >= m, "gemm_tc_qkv_rope: row_scale needs 32-bit sums [rows, tiles]")
+        ss_tiles = ss_in.shape[1]
+    if k_split is None:
+        tiles = n // 128
+        k_split = max(1, min(2 * SM_COUNT // tiles, -(-k // 64) // 8, TC_MAX_CLUSTER))
+    _gemm_tc_qkv(_ptr(qkv), _ptr(x), _ptr(w), m, k, x.stride(0), w.stride(0), qkv.stride(0), k_split,
+                 _ptr(ss_in), ss_tiles, int(size), float(eps), _ptr(q_gain), _ptr(k_gain), float(qk_eps),
+                 _ptr(cos), _ptr(sin), _ptr(positions), _ptr(token_slot), _ptr(k_pages), _ptr(v_pages),
+                 _ptr(block_table), block_table.stride(0), n_q_heads, n_kv_heads, 1 if write_kv else 0,
+                 _ptr(tc_status(x.device)), _stream())
+
+
 # ------------------------------------------------------------------ sampling and decode state
 _sample = Function("sampling", "ek_sample",
                    [_P, _P, c_longlong, c_int, c_int, c_float, c_int, c_ulonglong, _P, _P, _P, _P, _P])

@@ -19,12 +19,13 @@ from __future__ import annotations
 import torch
 
 from ..ops import kernels
-from ..ops.linear import linear
+from ..ops.linear import linear, row_scale_of, tc_takes
 from ..registry import lookup_part, register_part
-from .base import Mixer
+from .base import DeferredNorm, Mixer
 from .spec import CacheSpec, TensorSpec
 
 SM_COUNT = 148
+FUSE_ROPE_ROWS = 64       # the q/k/v product does norm, rotation and cache write itself up to here
 
 
 @register_part("mixer", "attention")
@@ -77,8 +78,20 @@ class Attention(Mixer):
 
     def forward(self, x, ctx, entry, writes_cache=True, defer=None):
         t = ctx.n_tokens
-        qkv = linear(x, self.w_qkv, ctx, "qkv", n_rows=t)
         pos = self.position
+        if self._fuses_rope(x, ctx):
+            # few rows, heads of 128: norm, rotation and cache write ride on the product's epilogue
+            row_scale, xin = (row_scale_of(x), x.scaled) if isinstance(x, DeferredNorm) else (None, x)
+            qkv = ctx.workspace.get("qkv", (t, self.w_qkv.shape[0]), self.dtype)
+            kernels.gemm_tc_qkv_rope(
+                qkv, xin, self.w_qkv, t, self.q_gain, self.k_gain,
+                self.qk_norm_eps if self.qk_norm_eps is not None else 0.0, pos.cos, pos.sin,
+                ctx.positions, ctx.token_slot, entry.k_pages, entry.v_pages, entry.block_table,
+                self.num_heads, self.num_kv_heads, write_kv=writes_cache, row_scale=row_scale)
+            out = ctx.workspace.get("attn_out", (t, self.num_heads * self.head_dim), self.dtype)
+            self._attend(out, qkv, ctx, entry)
+            return linear(out, self.w_o, ctx, "attn_proj", n_rows=t, defer=defer)
+        qkv = linear(x, self.w_qkv, ctx, "qkv", n_rows=t)
         kernels.qk_norm_rope_kv(
             qkv, t, self.q_gain, self.k_gain,
             pos.cos if pos else _no_table(self.device), pos.sin if pos else _no_table(self.device),
@@ -88,6 +101,13 @@ class Attention(Mixer):
         out = ctx.workspace.get("attn_out", (t, self.num_heads * self.head_dim), self.dtype)
         self._attend(out, qkv, ctx, entry)
         return linear(out, self.w_o, ctx, "attn_proj", n_rows=t, defer=defer)
+
+    def _fuses_rope(self, x, ctx):
+        xin = x.scaled if isinstance(x, DeferredNorm) else x
+        pos = self.position
+        return (self.dtype == torch.bfloat16 and ctx.n_tokens <= FUSE_ROPE_ROWS
+                and self.head_dim == kernels.QKV_ROPE_HEAD_DIM and pos is not None
+                and getattr(pos, "rotary_dim", 0) == self.head_dim and tc_takes(xin, self.w_qkv))
 
     def _attend(self, out, qkv, ctx, entry):
         t = ctx.n_tokens

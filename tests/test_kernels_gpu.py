@@ -550,6 +550,76 @@ def test_gemm_tc_deferred_norm(m, n, k_):
     k.check_tc_status(DEV)
 
 
+@pytest.mark.parametrize("m,nq,nkv,hidden,gains", [(8, 32, 8, 2560, True), (1, 4, 2, 256, True),
+                                                    (37, 6, 3, 200, False), (64, 16, 8, 1024, True)])
+def test_gemm_tc_qkv_rope(m, nq, nkv, hidden, gains):
+    """The q/k/v product with head norm, rotation and cache write in its epilogue, against the
+    product followed by qk_norm_rope_kv: finished rows, pages in shuffled order, no cache write,
+    a row scale from a deferred norm."""
+    k = K()
+    d, dtype = 128, torch.bfloat16
+    eps, theta, n_slots, max_len = 1e-6, 10000.0, 5, 300
+    n = (nq + 2 * nkv) * d
+    x = rnd(m, hidden, dtype=dtype, seed=1)
+    w = rnd(n, hidden, dtype=dtype, seed=2, scale=0.05)
+    qg = 1 + 0.1 * rnd(d, seed=8) if gains else None
+    kg = 1 + 0.1 * rnd(d, seed=9) if gains else None
+    inv = 1.0 / (theta ** (torch.arange(0, d, 2, dtype=torch.float32) / d))
+    freqs = torch.outer(torch.arange(max_len, dtype=torch.float32), inv)
+    cos, sin = freqs.cos().to(DEV), freqs.sin().to(DEV)
+    g = torch.Generator().manual_seed(m)
+    slot_of = torch.randint(0, n_slots, (m,), generator=g)
+    pos_of = torch.randint(0, max_len, (m,), generator=g)
+    pos_of[torch.rand(m, generator=g) < 0.15] = -1
+    # two tokens must not share a cache place
+    seen = set()
+    for i in range(m):
+        while pos_of[i] >= 0 and (int(slot_of[i]), int(pos_of[i])) in seen:
+            pos_of[i] = (pos_of[i] + 1) % max_len
+        seen.add((int(slot_of[i]), int(pos_of[i])))
+    positions, slots = pos_of.to(torch.int32).to(DEV), slot_of.to(torch.int32).to(DEV)
+    ss = (rnd(m, 3, seed=4).abs() + 0.5) * hidden / 3
+    for write_kv, row_scale in ((True, None), (False, None), (True, (ss, hidden, 1e-5))):
+        # the two-kernel way
+        pa = Pages(n_slots, max_len, nkv, d, dtype, seed=3)
+        ref = torch.empty(m, n, dtype=dtype, device=DEV)
+        k.gemm_tc_bf16(ref, x, w, k.EPI_BF16, swap=True, row_scale=row_scale)
+        k.qk_norm_rope_kv(ref, m, qg, kg, cos, sin, d, positions, slots, pa.k, pa.v, pa.table, nq, nkv, d,
+                          eps, write_kv=write_kv)
+        # the fused way
+        pb = Pages(n_slots, max_len, nkv, d, dtype, seed=3)
+        got = torch.full((m, n), 7.0, dtype=dtype, device=DEV)
+        k.gemm_tc_qkv_rope(got, x, w, m, qg, kg, eps, cos, sin, positions, slots, pb.k, pb.v, pb.table,
+                           nq, nkv, write_kv=write_kv, row_scale=row_scale)
+        k.check_tc_status(DEV)
+        live = (pos_of >= 0).to(DEV)
+        # q: one rounding instead of two, so equal up to a bfloat16 ulp of the largest value
+        assert rel(got[live][:, :nq * d], ref[live][:, :nq * d]) <= 1e-2, (write_kv, row_scale is not None)
+        assert rel(pb.k, pa.k) <= 1e-2 and rel(pb.v, pa.v) <= 1e-2
+        assert torch.equal(pb.v, pa.v)                        # values are copied, not computed
+        if not write_kv:
+            assert pb.k.abs().sum().item() == 0 and pb.v.abs().sum().item() == 0
+    # against 64-bit arithmetic, for one live row
+    i = int(torch.nonzero(pos_of >= 0)[0])
+    full = (x[i].double() @ w.double().t()).view(nq + 2 * nkv, d).cpu()
+    c, s_ = freqs[pos_of[i]].double().cos(), freqs[pos_of[i]].double().sin()
+
+    def rot(h, gain):
+        if gain is not None:
+            h = h * torch.rsqrt(h.pow(2).mean() + eps) * gain.double().cpu()
+        lo, hi = h[: d // 2], h[d // 2:]
+        return torch.cat([lo * c - hi * s_, hi * c + lo * s_])
+    pb = Pages(n_slots, max_len, nkv, d, dtype, seed=3)
+    got = torch.empty(m, n, dtype=dtype, device=DEV)
+    k.gemm_tc_qkv_rope(got, x, w, m, qg, kg, eps, cos, sin, positions, slots, pb.k, pb.v, pb.table, nq, nkv)
+    for h in range(nq):
+        assert rel(got[i, h * d:(h + 1) * d], rot(full[h], qg)) <= TOL[dtype]
+    page = int(pb.table[slot_of[i], pos_of[i] // 64])
+    for h in range(nkv):
+        assert rel(pb.k[page, h, pos_of[i] % 64], rot(full[nq + h], kg)) <= TOL[dtype]
+        assert rel(pb.v[page, h, pos_of[i] % 64], full[nq + nkv + h]) <= TOL[dtype]
+
+
 @pytest.mark.parametrize("m,n,k_", [(128, 128, 64), (2048, 2560, 4096), (300, 1000, 1000), (65, 662, 80),
                                     (517, 6144, 2560)])
 def test_gemm_tc_direct(m, n, k_):
