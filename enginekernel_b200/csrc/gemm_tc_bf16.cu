@@ -19,7 +19,10 @@
 //     block that delivers the last partial of a tile adds them in split order.
 //   * direct (prompts): P = activations, Q = weights, BN = 128 or 256.
 // Epilogues: bfloat16, 32-bit, or SwiGLU (the tile holds gate rows/columns in its first
-// half and the matching up rows/columns in its second half).
+// half and the matching up rows/columns in its second half).  The swapped form can also carry
+// what would otherwise be small kernels between the products (see TcParams): the row scale of a
+// deferred RMSNorm, the residual add with the next norm's gain and sums of squares, and for the
+// q/k/v product the per-head norm, the rotation and the cache write.
 // The reference calls cuBLAS for these products (engine/ek_model.py:203,209,298,311) and
 // has no Blackwell path.  Every barrier wait is bounded: on a timeout the kernel records a
 // code in `status`, lets in-flight copies land, frees its TMEM and returns.
