@@ -114,7 +114,7 @@ constexpr int kWideThreads = 256;
 constexpr int kWidePasses = 4;
 
 template <int D>
-__global__ void __launch_bounds__(kWideThreads)
+__global__ void __launch_bounds__(kWideThreads, 4)
 qk_norm_rope_kv_wide_kernel(bf16* qkv, int row_stride, const float* __restrict__ q_gain,
                             const float* __restrict__ k_gain, const float* __restrict__ cos_tab,
                             const float* __restrict__ sin_tab, const int* positions,
@@ -126,18 +126,28 @@ qk_norm_rope_kv_wide_kernel(bf16* qkv, int row_stride, const float* __restrict__
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x;
-  const int pos = positions[t];
-  if (pos < 0) return;
   const int n_kv = cache.heads;
   const int n_heads = write_kv ? n_q_heads + 2 * n_kv : n_q_heads;
   const int lih = threadIdx.x % LPH;               // lane in head
   const int head0 = threadIdx.x / LPH;
+  bf16* row = qkv + (size_t)t * row_stride;
+  // the first heads are asked for before the position is known: one round trip less in the chain
+  uint4 raw[kWidePasses];
+  auto load_heads = [&](int base) {
+#pragma unroll
+    for (int p = 0; p < kWidePasses; ++p) {
+      const int head = base + p * HPP + head0;
+      if (head < n_heads) raw[p] = *reinterpret_cast<const uint4*>(row + (size_t)head * D + lih * 8);
+    }
+  };
+  load_heads(0);
+  const int pos = positions[t];
+  if (pos < 0) return;
   const bool low = lih < LPH / 2;
   // the lanes of this head within the warp: heads of one warp may take different branches
   const unsigned seg = LPH == 32 ? 0xffffffffu
                                  : ((1u << (LPH & 31)) - 1u) << ((threadIdx.x & 31) / LPH * LPH);
   const int j0 = (lih % (LPH / 2)) * 8;            // angle index of this lane's first pair
-  bf16* row = qkv + (size_t)t * row_stride;
   size_t page_base = 0;
   if (write_kv) {
     const int page = cache.block_table[(size_t)token_slot[t] * cache.table_stride + pos / EK_PAGE];
@@ -152,12 +162,7 @@ qk_norm_rope_kv_wide_kernel(bf16* qkv, int row_stride, const float* __restrict__
     sn[0] = c.x; sn[1] = c.y; sn[2] = c.z; sn[3] = c.w; sn[4] = d.x; sn[5] = d.y; sn[6] = d.z; sn[7] = d.w;
   }
   for (int base = 0; base < n_heads; base += HPP * kWidePasses) {
-    uint4 raw[kWidePasses];
-#pragma unroll
-    for (int p = 0; p < kWidePasses; ++p) {
-      const int head = base + p * HPP + head0;
-      if (head < n_heads) raw[p] = *reinterpret_cast<const uint4*>(row + (size_t)head * D + lih * 8);
-    }
+    if (base > 0) load_heads(base);
 #pragma unroll
     for (int p = 0; p < kWidePasses; ++p) {
       const int head = base + p * HPP + head0;
