@@ -178,13 +178,20 @@ class DeviceBatchRun:
     def next_tokens(self) -> List[int]:
         if self.read >= self.max_steps:
             raise RuntimeError("the batch has no more steps")
-        # keep the device ahead of the reader, never past the last step any row can need
-        while self.launched < min(self.read + 1 + LOOKAHEAD, self.max_steps):
-            self._launch()
+        # The first token is handed over before the decode queue is filled (as the reference does,
+        # engine/engine.py:625-627): nothing stands between the prompt and its first token, not
+        # even a graph capture.  After that the device is kept ahead of the reader, never past the
+        # last step any row can need.
+        if self.read > 0:
+            self._fill()
         self.events[self.read % len(self.events)].synchronize()
         toks = self.host[self.read, :self.batch].tolist()
         self.read += 1
         return toks
+
+    def _fill(self):
+        while self.launched < min(self.read + 1 + LOOKAHEAD, self.max_steps):
+            self._launch()
 
     def close(self):
         if self.closed:
