@@ -37,3 +37,17 @@ def test_family_width_ragged_batch(folder, dtype):
     steps = list(eng.generate(seqs, 5))
     if dtype == "float32":
         assert [[st[b] for st in steps] for b in range(3)] == [plain.greedy(model, s, 5) for s in seqs]
+
+
+def test_family_width_two_dozen_sequences(folder):
+    """24 sequences decode together: more rows than the deferred norms take, few enough for the
+    q/k/v product to do head norm, rotation and cache write itself (heads of 128)."""
+    from enginekernel_b200 import Engine
+    model = helpers.plain_model(folder)
+    eng = Engine(folder, "bfloat16", max_tokens=24 * 128, max_batch=24)
+    lens = [5 + (7 * i) % 40 for i in range(24)]
+    seqs = tiny_models.random_prompts(CFG, lens, seed=12)
+    got = helpers.batch_then_steps(eng, seqs, [n - 3 for n in lens])
+    for s, g in zip(seqs, got):
+        err = helpers.rel_err(g, plain.logits(model, s))
+        assert err <= helpers.TOL["bfloat16"], (len(s), err)
