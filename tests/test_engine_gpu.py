@@ -293,3 +293,22 @@ def test_long_context_decode(tmp_path, dtype):
         tail = slice(len(s) - 12, len(s))
         err = helpers.rel_err(g[tail], want[tail])
         assert err <= helpers.TOL[dtype], (dtype, len(s), err)
+
+
+@pytest.mark.parametrize("shape", [
+    dict(num_attention_heads=3, num_key_value_heads=1, head_dim=256, hidden_size=72),     # one KV head
+    dict(num_attention_heads=10, num_key_value_heads=2, head_dim=96, hidden_size=160),    # groups of 5
+    dict(num_attention_heads=2, num_key_value_heads=2, head_dim=128, hidden_size=48),     # no grouping
+    dict(num_attention_heads=40, num_key_value_heads=2, head_dim=64, hidden_size=200),    # groups of 20
+])
+def test_unusual_head_shapes(tmp_path, shape):
+    """Head sizes and groupings at the edges of what the kernels take, whole and one by one."""
+    from enginekernel_b200 import Engine
+    cfg = dict(tiny_models.TINY_C, **shape)
+    folder = helpers.make_folder(tmp_path, cfg, 6)
+    model = helpers.plain_model(folder)
+    eng = Engine(folder, "bfloat16", max_tokens=1024, max_batch=2)
+    ids = tiny_models.random_prompts(cfg, [150], seed=13)[0]
+    want = plain.logits(model, ids)
+    assert helpers.rel_err(helpers.whole(eng, ids), want) <= helpers.TOL["bfloat16"]
+    assert helpers.rel_err(helpers.tail_one_by_one(eng, ids, 20), want) <= helpers.TOL["bfloat16"]
