@@ -17,7 +17,7 @@
 //     its share of the tile's columns over all of them, in split order, through distributed
 //     shared memory.  More splits than that go through scratch in global memory, and the
 //     block that delivers the last partial of a tile adds them in split order.
-//   * direct (prompts): P = activations, Q = weights, BN = 128 or 256.
+//   * direct (prompts): P = activations, Q = weights, 128 x 256 tiles.
 // Epilogues: bfloat16, 32-bit, or SwiGLU (the tile holds gate rows/columns in its first
 // half and the matching up rows/columns in its second half).  The swapped form can also carry
 // what would otherwise be small kernels between the products (see TcParams): the row scale of a
@@ -85,7 +85,7 @@ struct TcParams {
 
 // --------------------------------------------------------------------------------- kernel
 template <int BN, int EPI, bool SWAP, int STAGES, bool CL>
-__global__ void __launch_bounds__(128, SWAP ? 2 : 1)
+__global__ void __launch_bounds__(128, (SWAP || BN > 128) ? 2 : 1)
 gemm_tc_bf16_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q,
                     const TcParams prm) {
   constexpr uint32_t kBytesP = kTcBM * kTcBK * 2;
@@ -540,8 +540,9 @@ template <int BN, int EPI, bool SWAP, bool CL = false>
 static int launch_tc(const CUtensorMap& mp, const CUtensorMap& mq, const TcParams& prm, dim3 grid,
                      cudaStream_t stream) {
   // swapped: two blocks an SM, as many stages as their shared memory holds (a stage is 16 KB of
-  // weights and BN rows of activations); direct: one block an SM with a deep ring
-  constexpr int STAGES = SWAP ? (BN <= 16 ? 6 : BN <= 32 ? 5 : 4) : (BN <= 128 ? 6 : 4);
+  // weights and BN rows of activations); direct with 256-wide tiles: two blocks an SM of two 48 KB
+  // stages each, so that one block's epilogue runs under the other's MMAs
+  constexpr int STAGES = SWAP ? (BN <= 16 ? 6 : BN <= 32 ? 5 : 4) : (BN <= 128 ? 6 : 2);
   constexpr size_t smem = 1024 + (size_t)STAGES * (kTcBM * kTcBK * 2 + BN * kTcBK * 2) +
                           (2 * STAGES + 1) * 8 + 16;
   auto kernel = gemm_tc_bf16_kernel<BN, EPI, SWAP, STAGES, CL>;
@@ -632,7 +633,7 @@ static int gemm_tc_run(const ek::TcParams& extras, void* out, const void* x, con
   prm.k_blocks_per_split = k_blocks;
   prm.rows_p = M; prm.rows_q = N;
   const bool sw = epilogue == TC_EPI_SWIGLU;
-  constexpr int BN = 128;
+  constexpr int BN = 256;
   const int tiles_q = sw ? (N / 2 + BN / 2 - 1) / (BN / 2) : (N + BN - 1) / BN;
   if (tiles_q > 65535) return EK_ERR_ARG;
   if ((rc = tensor_map(x, M, K, ldx, kTcBM, &mp))) return rc;
