@@ -59,7 +59,9 @@ def reference_decode_logits(ref_model, ids):
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) != 2:
+        sys.exit("usage: python tests/golden/make_golden.py <checkout of jeojdi1/EngineKernel>")
+    ref_root = sys.argv[1]
     os.environ["ENGINE_NO_TRITON"] = "1"
     sys.path.insert(0, os.path.join(ref_root, "engine"))
     import ek_model  # the reference's module
