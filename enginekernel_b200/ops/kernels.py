@@ -14,7 +14,7 @@ from ctypes import c_float, c_int, c_longlong, c_ulonglong, c_void_p
 
 import torch
 
-from .lib import Function, KernelError
+from .lib import Function, KernelError, count_extra_launches
 
 PAGE = 64                 # tokens per cache page; must equal EK_PAGE in csrc/common.cuh
 MAX_HEAD_DIM = 256
@@ -185,6 +185,8 @@ def attention_generic(out, q, n_tokens, positions, token_slot, k_pages, v_pages,
                            n_tokens, n_q_heads, n_kv_heads, head_dim, float(scale),
                            int(window or 0), n_splits, keys_per_split, _ptr(part_acc),
                            _ptr(part_ml), _stream())
+    if n_splits > 1:
+        count_extra_launches()               # the merge kernel
 
 
 _attn_decode_bf16 = Function("attention_decode_bf16", "ek_attention_decode_bf16",
@@ -217,6 +219,8 @@ def attention_decode_bf16(out, q, n_tokens, positions, token_slot, k_pages, v_pa
                       _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.stride(0),
                       n_tokens, n_q_heads, n_kv_heads, head_dim, float(scale), int(window or 0),
                       n_splits, keys_per_split, _ptr(part_acc), _ptr(part_ml), _stream())
+    if n_splits > 1:
+        count_extra_launches()               # the merge kernel
 
 
 _attn_decode_tma = Function("attention_decode_tma", "ek_attention_decode_tma",
@@ -620,6 +624,7 @@ def sample_wide(out_token, logits, temperature, seed, part_score, part_index, st
                  float(temperature), int(seed) & 0xFFFFFFFFFFFFFFFF, _ptr(streams), _ptr(draws),
                  _ptr(active), _ptr(dyn), _ptr(part_score), _ptr(part_index), SAMPLE_SEGMENTS,
                  _stream())
+    count_extra_launches()                   # partial kernel + final kernel
 
 
 def decode_advance(sampled, token_ids, positions, draws, remaining, out_tokens, step_index,

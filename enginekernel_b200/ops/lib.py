@@ -10,11 +10,17 @@ from . import build
 
 _libs: Dict[str, ctypes.CDLL] = {}
 _lock = threading.Lock()
-_launch_calls = 0          # launcher calls made from Python (a captured graph replays them)
+_launch_calls = 0          # kernels launched from Python (a captured graph replays them)
 
 
 def launch_calls() -> int:
     return _launch_calls
+
+
+def count_extra_launches(n: int = 1) -> None:
+    """For entry points that launch more than one kernel (a merge kernel after the partial ones)."""
+    global _launch_calls
+    _launch_calls += n
 
 
 class KernelError(RuntimeError):
