@@ -184,14 +184,17 @@ def test_qk_norm_rope_kv(dtype, nq, nkv, d, rot):
     assert torch.equal(q2[:, :nq * d], qkv[:, :nq * d])
 
 
+@pytest.mark.parametrize("per_slot", [100, 250])
 @pytest.mark.parametrize("nq,nkv,d,gains", [(5, 1, 64, True), (120, 8, 64, True), (12, 3, 128, True),
                                             (60, 4, 128, False), (3, 2, 256, True), (8, 2, 128, True)])
-def test_qk_norm_rope_kv_many_tokens(nq, nkv, d, gains):
-    """The 16-bit form that takes a whole token a block (128 tokens and more): more heads than one
-    pass holds, q and k heads sharing a warp, finished rows in between, with and without gains."""
+def test_qk_norm_rope_kv_many_tokens(nq, nkv, d, gains, per_slot):
+    """The 16-bit forms that take a whole token at a time: a block a token (300 tokens), and
+    blocks that walk the tokens with the next rows on their way into shared memory (750 tokens);
+    more heads than one pass holds, q and k heads sharing a warp, finished rows in between, with and
+    without gains."""
     k = K()
     dtype = torch.bfloat16
-    eps, theta, n_slots, per_slot = 1e-6, 10000.0, 3, 100
+    eps, theta, n_slots = 1e-6, 10000.0, 3
     t = n_slots * per_slot
     pages = Pages(n_slots, per_slot + 30, nkv, d, dtype, seed=d + nq)
     before_k, before_v = pages.k.clone(), pages.v.clone()
