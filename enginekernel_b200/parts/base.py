@@ -5,7 +5,8 @@ sizes and constants, the checkpoint names of its tensors), the engine's dtype an
 device.  It never sees the model's configuration or which model it is in.  Roles:
 
 ``norm``          ``forward(stream, ctx, add=None, rows=None, write_back=True) -> y``
-``position``      tables or constants a mixer needs to place tokens (``tables()``)
+``position``      ``prepare(max_positions)``; what a mixer needs to place tokens.  The attention part
+                  reads ``cos``, ``sin`` (32-bit, [positions, rotary_dim / 2]) and ``rotary_dim``
 ``mixer``         ``cache_spec()``, ``forward(x, ctx, entry, writes_cache) -> [T, hidden]``
 ``feed_forward``  ``forward(x, ctx) -> [T, hidden]``
 ``block``         ``forward(stream, pending, ctx, entry, writes_cache) -> pending``
@@ -134,6 +135,10 @@ class Norm(Part):
 
 
 class PositionEncoding(Part):
+    """A rotary encoding gives, after ``prepare``, ``cos`` and ``sin`` [positions, rotary_dim / 2] in
+    32-bit on the device and ``rotary_dim``: dimension j < rotary_dim / 2 of a head turns with
+    dimension j + rotary_dim / 2 by the angle whose cosine and sine stand at [position, j]; the
+    dimensions from ``rotary_dim`` on pass unchanged.  Any table of angles fits."""
     role = "position"
 
     def prepare(self, max_positions: int) -> None:

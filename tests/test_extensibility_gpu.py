@@ -3,8 +3,9 @@
 A toy mixer with fixed-size state of its own (a running mean of its inputs), a toy
 architecture whose layers differ from one another (attention in one, the toy mixer in
 another, feed-forwards of different widths), and an execution order that runs a layer twice
-and lets a run read the keys and values another run stored.  Everything is defined here,
-registered through the public registry, built from a model folder written by the
+and lets a run read the keys and values another run stored; and a second toy architecture
+with a routed feed-forward (one expert a token) and a position encoding of its own inside the
+framework's attention.  Everything is defined here, registered through the public registry, built from a model folder written by the
 random-weights mode, and stepped under the same cuts as the real model.  None of it is a
 model of anyone's.
 """
@@ -178,6 +179,187 @@ def test_toy_architecture_with_a_stateful_mixer(tmp_path, dtype):
     finally:
         registry.unregister_part("mixer", "running_mean")
         registry.unregister_architecture("ToyMixedForCausalLM")
+
+
+# -- a feed-forward with routing and another position encoding ---------------------------------
+def define_routed_toy():
+    from enginekernel_b200 import registry
+    from enginekernel_b200.config.base import ModelConfig, key
+    from enginekernel_b200.parts.base import FeedForward, PositionEncoding
+    from enginekernel_b200.parts.spec import LayerSpec, ModelSpec, PartSpec, RunSpec, TensorSpec
+
+    class StretchedRope(PositionEncoding):
+        """Rotation by (position / stretch) x theta^(-2j/rotary_dim) of the first ``rotary_dim``
+        dimensions of a head.  The attention part reads ``cos``, ``sin`` and ``rotary_dim``."""
+
+        def __init__(self, spec, dtype, device):
+            super().__init__(spec, dtype, device)
+            self.rotary_dim = int(self.param("rotary_dim"))
+            self.cos = self.sin = None
+
+        def prepare(self, max_positions):
+            rot = self.rotary_dim
+            inv = 1.0 / (float(self.param("theta")) ** (torch.arange(0, rot, 2, dtype=torch.float32) / rot))
+            angles = torch.outer(torch.arange(max_positions, dtype=torch.float32) / float(self.param("stretch")), inv)
+            self.cos, self.sin = angles.cos().to(self.device), angles.sin().to(self.device)
+
+    class RoutedFeedForward(FeedForward):
+        """Each token goes to the one expert its router scores highest; the expert's output is
+        weighted by the router's softmax probability.  Router and softmax in 32-bit."""
+
+        @classmethod
+        def tensors(cls, spec):
+            h, w, e = spec.params["hidden_size"], spec.params["width"], spec.params["experts"]
+            out = [TensorSpec(spec.weights["router"], (e, h))]
+            for i in range(e):
+                out += [TensorSpec(spec.weights["in"].format(i), (w, h)),
+                        TensorSpec(spec.weights["out"].format(i), (h, w))]
+            return out
+
+        def load(self, tensors):
+            e = self.param("experts")
+            self.router = tensors[self.spec.weights["router"]].float()
+            self.w_in = [tensors[self.spec.weights["in"].format(i)].float() for i in range(e)]
+            self.w_out = [tensors[self.spec.weights["out"].format(i)].float() for i in range(e)]
+
+        def forward(self, x, ctx):
+            x = x[:ctx.n_tokens].float()
+            prob = torch.softmax(x @ self.router.t(), dim=-1)
+            top, choice = prob.max(dim=-1)
+            y = torch.zeros_like(x)
+            for i in range(len(self.w_in)):
+                mine = (choice == i).float()[:, None]       # no host decision: the same work every step
+                y += mine * (torch.relu(x @ self.w_in[i].t()) @ self.w_out[i].t())
+            return (top[:, None] * y).to(self.dtype)
+
+    @dataclasses.dataclass(frozen=True)
+    class RoutedConfig(ModelConfig):
+        architecture = "ToyRoutedForCausalLM"
+        hidden_size: int = key("hidden_size")
+        vocab_size: int = key("vocab_size")
+        heads: int = key("heads")
+        kv_heads: int = key("kv_heads")
+        head_dim: int = key("head_dim")
+        width: int = key("ff_width")
+        experts: int = key("experts")
+        eps: float = key("eps")
+        theta: float = key("theta")
+        stretch: float = key("stretch")
+        rotary_dim: int = key("rotary_dim")
+        max_positions: int = key("max_positions")
+
+    def build(cfg):
+        h = cfg.hidden_size
+
+        def norms(p):
+            return {n: PartSpec("rms_norm", {"size": h, "eps": cfg.eps}, {"gain": f"{p}.{n}.gain"})
+                    for n in ("pre_mixer", "pre_feed_forward")}
+
+        def attn(p, position):
+            return PartSpec("attention", {
+                "hidden_size": h, "num_heads": cfg.heads, "num_kv_heads": cfg.kv_heads,
+                "head_dim": cfg.head_dim, "scale": cfg.head_dim ** -0.5, "qk_norm_eps": None,
+                "window": None, "position": position},
+                {"q": f"{p}.q", "k": f"{p}.k", "v": f"{p}.v", "o": f"{p}.o"})
+
+        plain_rope = PartSpec("rope_neox", {"head_dim": cfg.head_dim, "theta": cfg.theta,
+                                            "rotary_dim": cfg.head_dim})
+        stretched = PartSpec("stretched_rope", {"theta": cfg.theta, "rotary_dim": cfg.rotary_dim,
+                                                "stretch": cfg.stretch})
+        layers = [
+            LayerSpec(PartSpec("pre_norm"), attn("l0", plain_rope),
+                      PartSpec("gated_mlp", {"hidden_size": h, "intermediate_size": cfg.width},
+                               {"gate": "l0.ff.gate", "up": "l0.ff.up", "down": "l0.ff.down"}), norms("l0")),
+            LayerSpec(PartSpec("pre_norm"), attn("l1", stretched),
+                      PartSpec("routed", {"hidden_size": h, "width": cfg.width, "experts": cfg.experts},
+                               {"router": "l1.ff.router", "in": "l1.ff.{}.in", "out": "l1.ff.{}.out"}),
+                      norms("l1")),
+        ]
+        return ModelSpec(
+            hidden_size=h, vocab_size=cfg.vocab_size, max_positions=cfg.max_positions,
+            embedding=TensorSpec("embed", (cfg.vocab_size, h), "embedding"), layers=layers,
+            schedule=[RunSpec(0, 0), RunSpec(1, 1)],
+            final_norm=PartSpec("rms_norm", {"size": h, "eps": cfg.eps}, {"gain": "final.gain"}),
+            lm_head=TensorSpec("head", (cfg.vocab_size, h)))
+
+    registry.register_part("position", "stretched_rope", StretchedRope, replace=True)
+    registry.register_part("feed_forward", "routed", RoutedFeedForward, replace=True)
+    registry.register_architecture("ToyRoutedForCausalLM", RoutedConfig, build, replace=True)
+    return RoutedConfig
+
+
+ROUTED_RAW = {"architectures": ["ToyRoutedForCausalLM"], "hidden_size": 48, "vocab_size": 83, "heads": 6,
+              "kv_heads": 2, "head_dim": 32, "ff_width": 40, "experts": 3, "eps": 1e-6, "theta": 500.0,
+              "stretch": 2.5, "rotary_dim": 16, "max_positions": 256}
+
+
+def routed_plain_logits(folder, ids):
+    """The routed toy model on one whole sequence in plain 32-bit torch -> (logits, sure): the
+    routed feed-forward is the last thing before the head, so a token whose two best experts are
+    almost tied (``sure`` False) may differ in its own logits only."""
+    c = ROUTED_RAW
+    w = plain.read_weights(folder, torch.float32)
+    s, nh, nkv, d, eps, rot = len(ids), c["heads"], c["kv_heads"], c["head_dim"], c["eps"], c["rotary_dim"]
+    r = w["embed"][torch.tensor(ids)]
+
+    def rotate(x, cos, sin):                       # x [S, heads, D]; the first `rot` dimensions turn
+        n = cos.shape[-1]
+        a, b, rest = x[..., :n // 2], x[..., n // 2:n], x[..., n:]
+        c1, s1 = cos[:, None, :n // 2], sin[:, None, :n // 2]
+        return torch.cat((a * c1 - b * s1, b * c1 + a * s1, rest), dim=-1)
+
+    def angles(n, stretch):
+        inv = 1.0 / (c["theta"] ** (torch.arange(0, n, 2, dtype=torch.float32) / n))
+        f = torch.outer(torch.arange(s, dtype=torch.float32) / stretch, inv)
+        f = torch.cat((f, f), dim=-1)
+        return f.cos(), f.sin()
+
+    sure = None
+    for p, (cos, sin) in (("l0", angles(d, 1.0)), ("l1", angles(rot, c["stretch"]))):
+        a = plain.rms_norm(r, w[f"{p}.pre_mixer.gain"], eps)
+        q = rotate((a @ w[f"{p}.q"].t()).view(s, nh, d), cos, sin)
+        k = rotate((a @ w[f"{p}.k"].t()).view(s, nkv, d), cos, sin)
+        v = (a @ w[f"{p}.v"].t()).view(s, nkv, d)
+        r = r + plain.causal_gqa_attention(q, k, v, d ** -0.5) @ w[f"{p}.o"].t()
+        m = plain.rms_norm(r, w[f"{p}.pre_feed_forward.gain"], eps)
+        if p == "l0":
+            g, u = m @ w["l0.ff.gate"].t(), m @ w["l0.ff.up"].t()
+            r = r + (torch.nn.functional.silu(g) * u) @ w["l0.ff.down"].t()
+        else:
+            scores = m @ w["l1.ff.router"].t()
+            two = scores.topk(2, dim=-1).values
+            sure = (two[:, 0] - two[:, 1]) > 0.05 * scores.abs().max()
+            best = torch.softmax(scores, dim=-1).topk(2, dim=-1)
+            y = torch.stack([torch.relu(m[t] @ w[f"l1.ff.{int(e)}.in"].t()) @ w[f"l1.ff.{int(e)}.out"].t()
+                             for t, e in enumerate(best.indices[:, 0])])
+            r = r + best.values[:, :1] * y
+    assert len(set(best.indices[:, 0].tolist())) > 1 or s < 8      # the router does choose
+    return plain.rms_norm(r, w["final.gain"], eps) @ w["head"].t(), sure
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_routed_feed_forward_and_another_position_encoding(tmp_path, dtype):
+    from enginekernel_b200 import Engine, registry
+    from enginekernel_b200.weights import write_random_model
+    RoutedConfig = define_routed_toy()
+    try:
+        folder = write_random_model(str(tmp_path / "routed"), RoutedConfig.from_dict(ROUTED_RAW), seed=9)
+        eng = Engine(folder, dtype, max_tokens=1024, max_batch=4)
+        g = torch.Generator().manual_seed(1)
+        seqs = [torch.randint(0, 83, (n,), generator=g).tolist() for n in (70, 5, 33)]
+        wants = [routed_plain_logits(folder, s) for s in seqs]
+        assert sum(int(sure.sum()) for _, sure in wants) > 0.8 * sum(len(s) for s in seqs)
+        tol = helpers.TOL[dtype]
+        for s, (w, sure) in zip(seqs, wants):
+            assert helpers.rel_err(helpers.whole(eng, s)[sure], w[sure]) <= tol
+            assert helpers.rel_err(helpers.tail_one_by_one(eng, s, 32)[sure], w[sure]) <= tol
+        got = helpers.batch_then_steps(eng, seqs, [40, 5, 2])
+        for gl, (w, sure) in zip(got, wants):
+            assert helpers.rel_err(gl[sure], w[sure]) <= tol
+    finally:
+        registry.unregister_part("position", "stretched_rope")
+        registry.unregister_part("feed_forward", "routed")
+        registry.unregister_architecture("ToyRoutedForCausalLM")
 
 
 def test_unknown_kinds_are_named():
