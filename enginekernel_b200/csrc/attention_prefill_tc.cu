@@ -18,7 +18,11 @@
 // it by more than 2^8, which keeps every probability finite in bfloat16 and skips the rescale
 // of almost every page.  O is divided by the sum once, at the end.
 // Warp 4 (one thread) is the TMA producer, warps 5 and 6 (one thread each) issue the S and the
-// P.V MMAs.  Shared memory
+// P.V MMAs.  Q comes by TMA as well: the rows (token, head of the group) are a box of a tensor map
+// that sees the query rows as [tokens][heads][head size].  A block's fixed costs count here (half
+// the time of a 2,048-token prompt went to them when Q was fetched with plain loads and all
+// setup stood behind the wait for the kernel ahead), so everything that does not read that
+// kernel's results - tile search, barriers, the TMEM allocation - is done before the wait.  Shared memory
 // holds Q, three stages of K (the scores of page t+1 need their K two softmax steps ahead of
 // time, or the softmax warps wait for it) and two of V - 112 KB at head size 128 - and TMEM 256
 // columns (S, S, O): two blocks an SM.  Every wait is bounded and reports through `status`.
@@ -34,14 +38,15 @@ constexpr int kFaThreads = 224;              // 4 softmax warps, a producer warp
 constexpr int kFaKStages = 3;                // K pages in flight: two pages of lookahead for the scores
 constexpr int kFaVStages = 2;
 // mbarriers: K full / empty per K stage, V full / empty per V stage, then per S buffer (2):
-// scores complete, P written, P.V done
+// scores complete, P written, P.V done; and Q landed
 constexpr int kBarKFull = 0, kBarKEmpty = kBarKFull + kFaKStages, kBarVFull = kBarKEmpty + kFaKStages,
               kBarVEmpty = kBarVFull + kFaVStages, kBarSFull = kBarVEmpty + kFaVStages,
-              kBarPFull = kBarSFull + 2, kBarPvDone = kBarPFull + 2, kFaBars = kBarPvDone + 2;
+              kBarPFull = kBarSFull + 2, kBarPvDone = kBarPFull + 2, kBarQFull = kBarPvDone + 2,
+              kFaBars = kBarQFull + 1;
 
 template <int D>
 __global__ void __launch_bounds__(kFaThreads, 2)
-attention_prefill_tc_kernel(bf16* __restrict__ out, const bf16* q, int q_row_stride,
+attention_prefill_tc_kernel(bf16* __restrict__ out, const __grid_constant__ CUtensorMap map_q,
                             const int* positions, const int* token_slot, const int* cu_seqlens,
                             int n_seqs, const __grid_constant__ CUtensorMap map_k,
                             const __grid_constant__ CUtensorMap map_v, const int* block_table,
@@ -67,10 +72,14 @@ attention_prefill_tc_kernel(bf16* __restrict__ out, const bf16* q, int q_row_str
 
   pdl_launch_dependents();
   if (tid == 128) {
+    tma_prefetch_map(&map_q);
     tma_prefetch_map(&map_k);
     tma_prefetch_map(&map_v);
   }
-  pdl_wait();
+  // Sequence bounds, positions, slots and block tables were uploaded before the step's first
+  // kernel, so they are read without waiting for the kernel ahead.
+  const uint32_t bar0 = smem_u32(bars);
+  auto bar = [&](int i) { return bar0 + 8u * i; };
   if (tid == 0) {
     int idx = blockIdx.y, found = -1, first = 0, count = 0;
     for (int b = 0; b < n_seqs; ++b) {
@@ -86,22 +95,31 @@ attention_prefill_tc_kernel(bf16* __restrict__ out, const bf16* q, int q_row_str
       idx -= tiles;
     }
     tile_info[0] = first; tile_info[1] = count; tile_info[2] = found;
+    for (int i = 0; i < kFaBars; ++i) mbar_init(bar(i), (i == kBarPFull || i == kBarPFull + 1) ? 4 : 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
+  if (warp == 4) tmem_alloc(smem_u32(tmem_slot), kTmemCols);
+  tc_fence_before();
   __syncthreads();
-  if ((smem_u32(smem) & 1023u) != 0) {           // never seen; the swizzled tiles would be wrong
-    if (tid == 0) atomicCAS(status, 0, 19);
-    return;
-  }
-  if (tile_info[2] < 0) return;
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
   const int t_first = tile_info[0], n_tok = tile_info[1];
-  const int pos0 = positions[t_first];
   const int n_rows = n_tok * group;
-  if (pos0 < 0) {                                  // rows of a finished sequence: zeros
-    for (int i = tid; i < n_rows * D; i += kFaThreads) {
-      const int r = i / D, d = i % D;
-      out[((size_t)(t_first + r / group) * n_q_heads + kv_head * group + r % group) * D + d] =
-          __float2bfloat16_rn(0.f);
+  const bool misplaced = (smem_u32(smem) & 1023u) != 0;   // never seen; the swizzled tiles would be wrong
+  const int pos0 = (tile_info[2] < 0 || misplaced) ? -1 : positions[t_first];
+  if (pos0 < 0) {                                  // no tile, or rows of a finished sequence: zeros
+    if (misplaced && tid == 0) atomicCAS(status, 0, 19);
+    if (tile_info[2] >= 0 && !misplaced) {
+      pdl_wait();                                  // the rows may still be read by a kernel ahead
+      for (int i = tid; i < n_rows * D; i += kFaThreads) {
+        const int r = i / D, d = i % D;
+        out[((size_t)(t_first + r / group) * n_q_heads + kv_head * group + r % group) * D + d] =
+            __float2bfloat16_rn(0.f);
+      }
     }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 4) tmem_dealloc(tmem_base, kTmemCols);
     return;
   }
   const int* table = block_table + (size_t)token_slot[t_first] * table_stride;
@@ -109,33 +127,17 @@ attention_prefill_tc_kernel(bf16* __restrict__ out, const bf16* q, int q_row_str
   const int lo_tile = window > 0 ? max(0, pos0 - window + 1) : 0;
   const int kt_lo = lo_tile / kFaKeys, kt_hi = hi_tile / kFaKeys;
   const int n_iter = kt_hi - kt_lo + 1;
-
-  const uint32_t bar0 = smem_u32(bars);
-  auto bar = [&](int i) { return bar0 + 8u * i; };
-  if (tid == 0) {
-    for (int i = 0; i < kFaBars; ++i) mbar_init(bar(i), (i == kBarPFull || i == kBarPFull + 1) ? 4 : 1);
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-  }
-  if (warp == 4) tmem_alloc(smem_u32(tmem_slot), kTmemCols);
-
-  // Q -> shared memory in the K-major 128-byte-swizzle layout (rows beyond the real ones: 0)
-  for (int i = tid; i < kFaRows * (D / 8); i += kFaThreads) {
-    const int r = i / (D / 8), c = i % (D / 8);            // 16-byte piece c of row r
-    uint4 v = make_uint4(0, 0, 0, 0);
-    if (r < n_rows)
-      v = *reinterpret_cast<const uint4*>(q + (size_t)(t_first + r / group) * q_row_stride +
-                                          (size_t)(kv_head * group + r % group) * D + c * 8);
-    *reinterpret_cast<uint4*>(q_s + (c / 8) * 2 * kSub + r * 128 + (((c & 7) ^ (r & 7)) << 4)) = v;
-  }
-  fence_proxy_async_smem();
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = *tmem_slot;
+  pdl_wait();                                      // Q and the newest keys and values: the kernel ahead
 
   bool ok = true;
   if (tid == 128) {
     // ------------------------------------------------------------------- TMA producer
+    // Rows of Q past this tile's tokens are the next sequence's or zeros (past the last token);
+    // they make rows of S and O that nobody stores.
+    mbar_expect_tx(bar(kBarQFull), DB * 2 * kSub);
+#pragma unroll
+    for (int j = 0; j < DB; ++j)
+      tma_load_3d(smem_u32(q_s + j * 2 * kSub), &map_q, 64 * j, kv_head * group, t_first, bar(kBarQFull));
     for (int it = 0; it < n_iter; ++it) {
       const int ks = it % kFaKStages, vs = it % kFaVStages;
       const uint32_t k_phase = (it / kFaKStages) & 1, v_phase = (it / kFaVStages) & 1;
@@ -159,7 +161,8 @@ attention_prefill_tc_kernel(bf16* __restrict__ out, const bf16* q, int q_row_str
     // thread issuing both kinds of MMA spent 2,000 cycles a page, more than the softmax needs.
     constexpr uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kFaKeys >> 3) << 17) |
                                  ((uint32_t)(kFaRows >> 4) << 24);
-    for (int it = 0; it < n_iter; ++it) {
+    ok = mbar_wait(bar(kBarQFull), 0, status, 20);
+    for (int it = 0; it < n_iter && ok; ++it) {
       const int s = it & 1;
       const int ks = it % kFaKStages;
       ok = mbar_wait(bar(kBarKFull + ks), (it / kFaKStages) & 1, status, 21);
@@ -338,8 +341,9 @@ static int launch_fa(bf16* out, const bf16* q, int q_row_stride, const int* posi
                      float scale, int window, int* status, cudaStream_t stream) {
   const int group = n_q_heads / n_kv_heads;
   const int tok_per_tile = kFaRows / group;
-  CUtensorMap mk, mv;
+  CUtensorMap mq, mk, mv;
   int rc;
+  if ((rc = tensor_map_heads(q, n_tokens, n_q_heads, D, q_row_stride, group, tok_per_tile, &mq))) return rc;
   if ((rc = tensor_map(k_pages, page_rows, D, D, kFaKeys, &mk))) return rc;
   if ((rc = tensor_map(v_pages, page_rows, D, D, kFaKeys, &mv))) return rc;
   constexpr int DB = D / 64;
@@ -359,7 +363,7 @@ static int launch_fa(bf16* out, const bf16* q, int q_row_stride, const int* posi
   const int tiles = (n_tokens + tok_per_tile - 1) / tok_per_tile + n_seqs;   // upper bound
   if (tiles > 65535) return EK_ERR_ARG;
   dim3 grid(n_kv_heads, tiles);
-  return (int)launch_pdl(kernel, grid, dim3(kFaThreads), smem, stream, out, q, q_row_stride, positions,
+  return (int)launch_pdl(kernel, grid, dim3(kFaThreads), smem, stream, out, mq, positions,
                          token_slot, cu_seqlens, n_seqs, mk, mv, block_table, table_stride, n_kv_heads,
                          n_q_heads, scale * 1.4426950408889634f, window, tok_per_tile, status);
 }

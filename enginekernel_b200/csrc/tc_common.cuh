@@ -50,6 +50,13 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
       " [%0], [%1, {%2, %3}], [%4];"
       ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar) : "memory");
 }
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2,
+                                            uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%2, %3, %4}], [%5];"
+      ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(bar) : "memory");
+}
 // L2 policy for data that is read once (a weight stream): first to be evicted.
 __device__ __forceinline__ uint64_t l2_policy_evict_first() {
   uint64_t p;
@@ -271,5 +278,47 @@ inline int tensor_map(const void* ptr, long long rows, long long k, long long ld
   return 0;
 }
 
+// Tensor map of bfloat16 rows seen as [tokens][heads][head_dim] with `ld` elements between tokens;
+// boxes of 64 dimensions x box_heads heads x box_tokens tokens, 128-byte swizzle, zeros outside.
+// In shared memory a box is a K-major tile whose row (token, head) is token * box_heads + head.
+inline int tensor_map_heads(const void* ptr, long long tokens, long long heads, long long head_dim,
+                            long long ld, int box_heads, int box_tokens, CUtensorMap* out) {
+  struct Key {
+    const void* ptr; long long tokens, heads, head_dim, ld; int box_heads, box_tokens;
+    bool operator==(const Key& o) const {
+      return ptr == o.ptr && tokens == o.tokens && heads == o.heads && head_dim == o.head_dim &&
+             ld == o.ld && box_heads == o.box_heads && box_tokens == o.box_tokens;
+    }
+  };
+  struct KeyHash {
+    size_t operator()(const Key& m) const {
+      size_t h = (size_t)m.ptr;
+      for (long long v : {m.tokens, m.heads, m.head_dim, m.ld, (long long)m.box_heads, (long long)m.box_tokens})
+        h = h * 1000003u ^ (size_t)v;
+      return h;
+    }
+  };
+  static std::mutex mu;
+  static std::unordered_map<Key, CUtensorMap, KeyHash> cache;
+  const Key key{ptr, tokens, heads, head_dim, ld, box_heads, box_tokens};
+  std::lock_guard<std::mutex> lock(mu);
+  auto it = cache.find(key);
+  if (it != cache.end()) { *out = it->second; return 0; }
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return (int)cudaErrorNotSupported;
+  const cuuint64_t dims[3] = {(cuuint64_t)head_dim, (cuuint64_t)heads, (cuuint64_t)tokens};
+  const cuuint64_t strides[2] = {(cuuint64_t)head_dim * 2, (cuuint64_t)ld * 2};
+  const cuuint32_t box[3] = {(cuuint32_t)kTcBK, (cuuint32_t)box_heads, (cuuint32_t)box_tokens};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  CUtensorMap m;
+  const CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides,
+                        box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return EK_ERR_ARG;
+  if (cache.size() > 8192) cache.clear();
+  cache.emplace(key, m);
+  *out = m;
+  return 0;
+}
 
 }  // namespace ek
