@@ -90,7 +90,11 @@ gemm_tc_bf16_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
                     const TcParams prm) {
   constexpr uint32_t kBytesP = kTcBM * kTcBK * 2;
   constexpr uint32_t kBytesQ = BN * kTcBK * 2;
-  constexpr uint32_t kTmemCols = BN < 32 ? 32 : BN;
+  // The swapped form has two MMA-issuing threads with an accumulator each (stages in turn); the
+  // second accumulator stands BN columns after the first.
+  constexpr bool TWO = SWAP;
+  static_assert(!TWO || STAGES % 2 == 0, "two issuing threads need an even number of stages");
+  constexpr uint32_t kTmemCols = TWO ? (2 * BN < 32 ? 32 : 2 * BN) : (BN < 32 ? 32 : BN);
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   // 1024-byte alignment is needed by the 128-byte swizzle
   unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -121,7 +125,7 @@ gemm_tc_bf16_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
       mbar_init(full0 + 8 * s, 1);
       mbar_init(empty0 + 8 * s, 1);
     }
-    mbar_init(accum_bar, 1);
+    mbar_init(accum_bar, TWO ? 2 : 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 0) tmem_alloc(smem_u32(tmem_slot), kTmemCols);
@@ -186,10 +190,17 @@ gemm_tc_bf16_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
       load_p(it);
       load_q(it);
     }
-  } else if (tid == 32) {
-    // ---------------------------------------------------------------- MMA issuer
+  } else if (tid == 32 || (TWO && tid == 64)) {
+    // ---------------------------------------------------------------- MMA issuer(s)
+    // A stage costs its issuing thread about 600 cycles (the barrier read 220, four MMAs 65 each,
+    // the commit 130) whether or not the tile was there already, and with one thread that chain,
+    // not the memory, set the pace of a block with many K blocks.  In the swapped form two
+    // threads of two warps take the stages in turn, each into its own accumulator (the order of
+    // the sum stays fixed); the epilogue adds the two.
     constexpr uint32_t idesc = tc_idesc(BN);
-    for (int it = 0; it < n_iter && ok; ++it) {
+    const int mine = tid == 32 ? 0 : 1, step = TWO ? 2 : 1;
+    const uint32_t acc = tmem_base + (uint32_t)(mine * BN);
+    for (int it = mine; it < n_iter && ok; it += step) {
       const int s = it % STAGES;
       const uint32_t phase = (it / STAGES) & 1;
       ok = mbar_wait(full0 + 8 * s, phase, prm.status, 2);
@@ -199,10 +210,10 @@ gemm_tc_bf16_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
       const uint64_t db = smem_desc_k_sw128(smem_u32(q_tiles + s * kBytesQ));
 #pragma unroll
       for (int k = 0; k < kTcBK / 16; ++k)       // 32 bytes further along K inside the swizzle row
-        tc_mma(tmem_base, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, (it | k) ? 1u : 0u);
+        tc_mma(acc, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, (it >= step || k) ? 1u : 0u);
       tc_commit(empty0 + 8 * s);               // the stage is free once these MMAs have read it
     }
-    tc_commit(accum_bar);                      // all MMAs done: the accumulator is complete
+    tc_commit(accum_bar);                      // this thread's MMAs done: its accumulator is complete
   }
 
   // -------------------------------------------------------------------- epilogue (all warps)
@@ -228,6 +239,49 @@ gemm_tc_bf16_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
     }
     if (h == 0 && m < prm.rows_q && m < 64) rstd_s[m] = rsqrtf(ss * prm.ss_inv_size + prm.eps);
   }
+  // The staged epilogue (swapped form, below): a thread takes 4 neighbouring weight rows of one
+  // sequence; a warp covers the tile's rows for one sequence (two with SwiGLU, whose outputs are
+  // the 64 gate rows), the block 4 (8) sequences a pass, P passes a batch.  What a batch needs from
+  // global memory - the stream and the next norm's gain, or the token's position, angles and cache
+  // page - is asked for here for the first batch, while the MMAs still run: behind the cluster
+  // barrier these loads (two and three dependent rounds) were the longest part of the epilogue.
+  constexpr int R = EPI == TC_EPI_SWIGLU ? 64 : kTcBM;     // output rows of the tile
+  constexpr int MPW = 32 / (R / 4);                         // sequences a warp and pass
+  constexpr int P = CL ? 2 : 4;                             // passes a batch
+  const int step = CL ? n_split : 1, first = CL ? split : 0;
+  const int owned = prm.rows_q > first ? (prm.rows_q - first + step - 1) / step : 0;
+  const int sub = lane / (R / 4), r0 = 4 * (lane % (R / 4));
+  const bool fused_add = EPI == TC_EPI_BF16 && prm.stream != nullptr;
+  const bool qkv_form = EPI == TC_EPI_BF16 && prm.qkv_positions != nullptr;
+  const bool head_is_q = tile_p < prm.n_q_heads, head_is_k = !head_is_q && tile_p < prm.n_q_heads + prm.cache.heads;
+  struct Asked { float4 st, gn, cs, sn; int pos, page; };
+  Asked pre[P];
+  auto ask = [&](int base) {
+#pragma unroll
+    for (int ps = 0; ps < P; ++ps) {
+      const int idx = base + (ps * 4 + warp) * MPW + sub;
+      const int m = first + idx * step;
+      pre[ps].pos = -1;
+      pre[ps].page = 0;
+      if (fused_add && idx < owned && tile_p * kTcBM + r0 < prm.rows_p) {
+        const int n_out = tile_p * kTcBM + r0;
+        pre[ps].st = __ldcg(reinterpret_cast<const float4*>(prm.stream + (size_t)m * prm.ld_stream + n_out));
+        pre[ps].gn = *reinterpret_cast<const float4*>(prm.next_gain + n_out);
+      }
+      if (qkv_form && idx < owned) {
+        const int pos = prm.qkv_positions[m];
+        pre[ps].pos = pos;
+        if (pos >= 0 && (head_is_q || head_is_k)) {
+          // dimension d pairs with d + 64: 16 lanes further on, same place in the lane
+          pre[ps].cs = *reinterpret_cast<const float4*>(prm.cos_tab + (size_t)pos * 64 + (r0 & 63));
+          pre[ps].sn = *reinterpret_cast<const float4*>(prm.sin_tab + (size_t)pos * 64 + (r0 & 63));
+        }
+        if (pos >= 0 && !head_is_q && prm.write_kv)
+          pre[ps].page = prm.cache.block_table[(size_t)prm.qkv_slots[m] * prm.cache.table_stride + pos / EK_PAGE];
+      }
+    }
+  };
+  if (SWAP && (CL || n_split == 1)) ask(0);
   bool acc_ok = n_iter > 0 ? mbar_wait(accum_bar, 0, prm.status, 3) : true;
   tc_fence_after();
   // a failure anywhere in the block is everybody's failure
@@ -236,6 +290,15 @@ gemm_tc_bf16_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
   const int row = warp * 32 + lane;            // row of the tile = TMEM lane
   const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
   const int tile_linear = SWAP ? tile_p : (tile_q * gridDim.x + tile_p);
+  auto acc_ld16 = [&](uint32_t col, float* v) {     // 16 columns of the sum, this thread's row
+    tmem_ld16(lane_addr + col, v);
+    if (TWO && n_iter > 1) {                   // (with one K block the second accumulator was never written)
+      float w[16];
+      tmem_ld16(lane_addr + BN + col, w);
+#pragma unroll
+      for (int i = 0; i < 16; ++i) v[i] += w[i];
+    }
+  };
 
   if (SWAP && (CL || n_split == 1)) {
     // The tile goes to shared memory as [sequence][weight row] (the operand tiles are dead), and
@@ -250,7 +313,7 @@ gemm_tc_bf16_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
       for (int c0 = 0; c0 < BN && c0 < prm.rows_q; c0 += 16) {
         float v[16];
         if (n_iter > 0) {
-          tmem_ld16(lane_addr + c0, v);
+          acc_ld16(c0, v);
         } else {
 #pragma unroll
           for (int i = 0; i < 16; ++i) v[i] = 0.f;
@@ -261,16 +324,8 @@ gemm_tc_bf16_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
     }
     if (CL) cluster_sync(); else __syncthreads();
     if (!failed) {
-      // A thread takes 4 neighbouring weight rows (one 16-byte load a block of the cluster) of one
-      // sequence; a warp covers the tile's rows for one sequence (two with SwiGLU, whose outputs
-      // are the 64 gate rows), the block 4 (8) sequences a pass.  All loads of two passes are
-      // issued before the first sum.
-      constexpr int R = EPI == TC_EPI_SWIGLU ? 64 : kTcBM;     // output rows of the tile
-      constexpr int MPW = 32 / (R / 4);                         // sequences a warp and pass
-      constexpr int P = CL ? 2 : 4;                             // passes a batch
-      const int step = CL ? n_split : 1, first = CL ? split : 0;
-      const int owned = prm.rows_q > first ? (prm.rows_q - first + step - 1) / step : 0;
-      const int sub = lane / (R / 4), r0 = 4 * (lane % (R / 4));
+      // One 16-byte load a block of the cluster and thread; all loads of a batch are issued before
+      // the first sum.
       const bool wide_ok = (prm.ldo & 3) == 0 && ((uintptr_t)prm.out & 15) == 0;
       auto fetch4 = [&](const float* p, int sp) {
         return CL ? ld_cluster_f32x4(p, (unsigned)sp) : *reinterpret_cast<const float4*>(p);
@@ -278,17 +333,11 @@ gemm_tc_bf16_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
 #pragma unroll 1
       for (int base = 0; base < owned; base += P * 4 * MPW) {
         float4 part[P][NS], part_up[P][NS];
-        float4 st_old[P], gn[P];                 // the stream and the next norm's gain (residual form)
-        const bool fused_add = EPI == TC_EPI_BF16 && prm.stream != nullptr;
+        if (base > 0) ask(base);                 // (the first batch was asked for before the barrier)
 #pragma unroll
         for (int ps = 0; ps < P; ++ps) {
           const int idx = base + (ps * 4 + warp) * MPW + sub;
           const int m = first + idx * step;
-          if (fused_add && idx < owned && tile_p * kTcBM + r0 < prm.rows_p) {
-            const int n_out = tile_p * kTcBM + r0;
-            st_old[ps] = __ldcg(reinterpret_cast<const float4*>(prm.stream + (size_t)m * prm.ld_stream + n_out));
-            gn[ps] = *reinterpret_cast<const float4*>(prm.next_gain + n_out);
-          }
 #pragma unroll
           for (int sp = 0; sp < NS; ++sp) {
             const bool live = idx < owned && sp < n_split;
@@ -329,11 +378,11 @@ gemm_tc_bf16_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
             n_out = tile_p * kTcBM + r0;
             n_limit = prm.rows_p;
           }
-          if (EPI == TC_EPI_BF16 && prm.qkv_positions != nullptr) {
+          if (qkv_form) {
             // head = tile; everything below is uniform over the warp except the lane's 4 dimensions
             const int head = tile_p, n_kv = prm.cache.heads;
-            const int pos = idx < owned ? prm.qkv_positions[m] : -1;
-            const bool is_q = head < prm.n_q_heads, is_k = !is_q && head < prm.n_q_heads + n_kv;
+            const int pos = pre[ps].pos;
+            const bool is_q = head_is_q, is_k = head_is_k;
             if (pos >= 0 && (is_q || prm.write_kv) && head < prm.n_q_heads + 2 * n_kv) {
               float y[4] = {acc.x, acc.y, acc.z, acc.w};
               if (is_q || is_k) {
@@ -345,9 +394,7 @@ gemm_tc_bf16_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
                   y[0] = y[0] * rstd * g4.x; y[1] = y[1] * rstd * g4.y;
                   y[2] = y[2] * rstd * g4.z; y[3] = y[3] * rstd * g4.w;
                 }
-                // dimension d pairs with d + 64: 16 lanes further on, same place in the lane
-                const float4 cs = *reinterpret_cast<const float4*>(prm.cos_tab + (size_t)pos * 64 + (r0 & 63));
-                const float4 sn = *reinterpret_cast<const float4*>(prm.sin_tab + (size_t)pos * 64 + (r0 & 63));
+                const float4 cs = pre[ps].cs, sn = pre[ps].sn;
                 const float c[4] = {cs.x, cs.y, cs.z, cs.w}, sv[4] = {sn.x, sn.y, sn.z, sn.w};
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
@@ -359,8 +406,7 @@ gemm_tc_bf16_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
               if (is_q) {
                 dst = (bf16*)prm.out + (size_t)m * prm.ldo + n_out;
               } else {
-                const int page = prm.cache.block_table[(size_t)prm.qkv_slots[m] * prm.cache.table_stride +
-                                                       pos / EK_PAGE];
+                const int page = pre[ps].page;
                 const int kv_head = is_k ? head - prm.n_q_heads : head - prm.n_q_heads - n_kv;
                 dst = (bf16*)(is_k ? prm.cache.k : prm.cache.v) + page_offset(prm.cache, page, kv_head, pos) + r0;
               }
@@ -373,12 +419,12 @@ gemm_tc_bf16_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
             float ssq = 0.f;
             if (idx < owned && n_out < n_limit) {
               float* sp = prm.stream + (size_t)m * prm.ld_stream + n_out;
-              float4 st = st_old[ps];
+              float4 st = pre[ps].st;
               st.x += acc.x; st.y += acc.y; st.z += acc.z; st.w += acc.w;
               *reinterpret_cast<float4*>(sp) = st;
               ssq = st.x * st.x + st.y * st.y + st.z * st.z + st.w * st.w;
-              __nv_bfloat162 lo = __floats2bfloat162_rn(st.x * gn[ps].x, st.y * gn[ps].y);
-              __nv_bfloat162 hi = __floats2bfloat162_rn(st.z * gn[ps].z, st.w * gn[ps].w);
+              __nv_bfloat162 lo = __floats2bfloat162_rn(st.x * pre[ps].gn.x, st.y * pre[ps].gn.y);
+              __nv_bfloat162 hi = __floats2bfloat162_rn(st.z * pre[ps].gn.z, st.w * pre[ps].gn.w);
               *reinterpret_cast<uint2*>((bf16*)prm.out + (size_t)m * prm.ldo + n_out) =
                   make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
             }
@@ -418,7 +464,7 @@ gemm_tc_bf16_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
       for (int c0 = 0; c0 < BN; c0 += 16) {
         float v[16];
         if (n_iter > 0) {
-          tmem_ld16(lane_addr + c0, v);
+          acc_ld16(c0, v);
         } else {
 #pragma unroll
           for (int i = 0; i < 16; ++i) v[i] = 0.f;
@@ -445,7 +491,7 @@ gemm_tc_bf16_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
         float v[16], u[16];
         auto fetch = [&](int col, float dst[16]) {
           if (n_split == 1) {
-            tmem_ld16(lane_addr + col, dst);
+            acc_ld16(col, dst);
           } else {
 #pragma unroll
             for (int i = 0; i < 16; ++i) dst[i] = 0.f;
@@ -536,13 +582,20 @@ gemm_tc_bf16_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
   if (warp == 0) tmem_dealloc(tmem_base, kTmemCols);
 }
 
+// Stages of the swapped form's operand ring: what two blocks an SM can hold, and an even number.
+// Its two MMA-issuing threads take the stages in turn, and a thread has to see every filling of
+// a stage it waits for: an mbarrier's phase is known by its parity alone, so a thread that saw
+// only every other filling would take "the filling before is not there yet" for "mine is
+// complete" (with 5 stages that happened, rarely, and broke the barrier protocol).
+constexpr int swap_stages(int bn) { return bn <= 16 ? 6 : 4; }
+
 template <int BN, int EPI, bool SWAP, bool CL = false>
 static int launch_tc(const CUtensorMap& mp, const CUtensorMap& mq, const TcParams& prm, dim3 grid,
                      cudaStream_t stream) {
-  // swapped: two blocks an SM, as many stages as their shared memory holds (a stage is 16 KB of
-  // weights and BN rows of activations); direct with 256-wide tiles: two blocks an SM of two 48 KB
+  // swapped: two blocks an SM, stages as swap_stages says (a stage is 16 KB of weights and BN rows
+  // of activations); direct with 256-wide tiles: two blocks an SM of two 48 KB
   // stages each, so that one block's epilogue runs under the other's MMAs
-  constexpr int STAGES = SWAP ? (BN <= 16 ? 6 : BN <= 32 ? 5 : 4) : (BN <= 128 ? 6 : 2);
+  constexpr int STAGES = SWAP ? swap_stages(BN) : (BN <= 128 ? 6 : 2);
   constexpr size_t smem = 1024 + (size_t)STAGES * (kTcBM * kTcBK * 2 + BN * kTcBK * 2) +
                           (2 * STAGES + 1) * 8 + 16;
   auto kernel = gemm_tc_bf16_kernel<BN, EPI, SWAP, STAGES, CL>;

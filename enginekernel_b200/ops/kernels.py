@@ -437,6 +437,14 @@ def check_tc_status(device):
 TC_MAX_CLUSTER = 8          # blocks of a thread-block cluster (the portable limit)
 
 
+def swap_k_split(n_out, k, epilogue):
+    """Blocks that share a tile's K in the swapped form: two blocks fit an SM - fill those 296
+    places, keep at least 8 K blocks a block, stay within one cluster."""
+    tiles = -(-n_out // (64 if epilogue == EPI_SWIGLU else 128))
+    k_blocks = -(-k // 64)
+    return max(1, min(2 * SM_COUNT // tiles, k_blocks // 8, TC_MAX_CLUSTER))
+
+
 def gemm_tc_bf16(out, x, w, epilogue=EPI_BF16, n_rows=None, swap=None, k_split=None, cluster=True,
                  row_scale=None, residual=None):
     """out = x . w^T (or the SwiGLU of it) on tcgen05 tensor cores with TMA-staged operands.
@@ -470,13 +478,7 @@ def gemm_tc_bf16(out, x, w, epilogue=EPI_BF16, n_rows=None, swap=None, k_split=N
     _need(not swap or m <= TC_SWAP_MAX_ROWS, "gemm_tc_bf16: the swapped form takes at most 64 rows")
     partials, tickets = gemv_scratch(x.device)
     if k_split is None:
-        k_split = 1
-        if swap:
-            # two blocks fit an SM: fill those 296 places, keep at least 8 K blocks a block, stay
-            # within one cluster
-            tiles = -(-n_out // (64 if epilogue == EPI_SWIGLU else 128))
-            k_blocks = -(-k // 64)
-            k_split = max(1, min(2 * SM_COUNT // tiles, k_blocks // 8, TC_MAX_CLUSTER))
+        k_split = swap_k_split(n_out, k, epilogue) if swap else 1
     if row_scale is not None or residual is not None:
         cluster, k_split = True, min(k_split, TC_MAX_CLUSTER)     # these forms have no scratch path
     ss_in, ss_tiles, size, eps = None, 0, 0, 0.0
@@ -546,8 +548,7 @@ def gemm_tc_qkv_rope(qkv, x, w, n_rows, q_gain, k_gain, qk_eps, cos, sin, positi
               and ss_in.shape[0] >= m, "gemm_tc_qkv_rope: row_scale needs 32-bit sums [rows, tiles]")
         ss_tiles = ss_in.shape[1]
     if k_split is None:
-        tiles = n // 128
-        k_split = max(1, min(2 * SM_COUNT // tiles, -(-k // 64) // 8, TC_MAX_CLUSTER))
+        k_split = swap_k_split(n, k, EPI_BF16)
     _gemm_tc_qkv(_ptr(qkv), _ptr(x), _ptr(w), m, k, x.stride(0), w.stride(0), qkv.stride(0), k_split,
                  _ptr(ss_in), ss_tiles, int(size), float(eps), _ptr(q_gain), _ptr(k_gain), float(qk_eps),
                  _ptr(cos), _ptr(sin), _ptr(positions), _ptr(token_slot), _ptr(k_pages), _ptr(v_pages),

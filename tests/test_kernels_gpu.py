@@ -477,7 +477,8 @@ def test_gemv_bf16_epilogues(m, n, k_):
 
 
 @pytest.mark.parametrize("m,n,k_", [(17, 256, 128), (64, 2560, 4096), (33, 1000, 1000), (1, 128, 64),
-                                    (48, 331 * 2, 80), (64, 6144, 2560)])
+                                    (48, 331 * 2, 80), (64, 6144, 2560), (24, 1280, 2560),
+                                    (24, 20012, 2560)])
 def test_gemm_tc_swapped(m, n, k_):
     """tcgen05 + TMA product with the weights on the 128-row side (decode with many sequences)."""
     k = K()
@@ -554,7 +555,8 @@ def test_gemm_tc_deferred_norm(m, n, k_):
 
 
 @pytest.mark.parametrize("m,nq,nkv,hidden,gains", [(8, 32, 8, 2560, True), (1, 4, 2, 256, True),
-                                                    (37, 6, 3, 200, False), (64, 16, 8, 1024, True)])
+                                                    (37, 6, 3, 200, False), (64, 16, 8, 1024, True),
+                                                    (24, 8, 2, 2560, True)])
 def test_gemm_tc_qkv_rope(m, nq, nkv, hidden, gains):
     """The q/k/v product with head norm, rotation and cache write in its epilogue, against the
     product followed by qk_norm_rope_kv: finished rows, pages in shuffled order, no cache write,
