@@ -15,11 +15,15 @@
 //     before P.V - the same arithmetic as the register-streaming kernel in
 //     attention_decode_bf16.cu, which remains for the other head sizes.
 //   * the warps merge in shared memory; the splits of one (token, KV head) are a thread-block
-//     cluster, leave their partial results in their own shared memory and merge them, in split
-//     order, through distributed shared memory: no partials in global memory, no second kernel.
+//     cluster.  The (head, dimension) pairs are dealt to its blocks in equal runs; a block sends
+//     its partial result for a pair, with its maximum and sum, into the shared memory of the
+//     block that owns the pair (st.shared::cluster, into a buffer beside the ring, since the
+//     owner may still be reading pages), and after one cluster barrier every block merges what
+//     it was sent, in split order, and stores its run: no partials in global memory, no second
+//     kernel, and no block has to outlive another's reads.
 // The reference's counterpart is its Triton split-K flash-decoding kernel and combine kernel
 // (engine/ek_kernels.py:534-615, 988-1019).  Every barrier wait is bounded and reports through
-// `status`; every block of a cluster reaches both cluster barriers whatever happened to it.
+// `status`; every block of a cluster reaches the cluster barrier whatever happened to it.
 #include "tc_common.cuh"
 
 namespace ek {
@@ -28,6 +32,11 @@ constexpr int kDtWarps = 4;                  // consumer warps
 constexpr int kDtThreads = (kDtWarps + 1) * 32;
 constexpr int kDtPortableSplits = 8;         // blocks of a cluster: the portable limit
 constexpr int kDtMaxSplits = 16;             // and the limit with the attribute for larger ones
+// floats a block can be sent by its cluster: every (head, dimension) pair once (dealt in runs of
+// ceil(pairs / splits), so up to one more a split), and (max, sum) of 16 heads from 16 splits
+template <int D>
+constexpr int kDtRecvO = 16 * D + kDtMaxSplits;
+constexpr int kDtRecvMl = kDtMaxSplits * 16 * 2;
 
 __device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2,
                                         uint32_t& r3) {
@@ -68,13 +77,17 @@ attention_decode_tma_kernel(bf16* __restrict__ out, const bf16* q, int q_row_str
   unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint64_t* bars = (uint64_t*)(smem + STAGES * kStage);        // full[STAGES], empty[STAGES]
   // after the last page the ring is dead and holds, from its start: the warps' accumulators
-  // [4][16][D], their (max, sum) [4][16][2], the block's result [16][D] and its (max, sum) [16][2]
+  // [4][16][OS] and their (max, sum) [4][16][2].
+  // A row of the accumulators is OS = D + 8 floats long, so that the rows a warp stores at once
+  // (one per group of four lanes) lie on different banks.
+  constexpr int OS = D + 8;
   float* o_s = (float*)smem;
-  float* ml_s = o_s + kDtWarps * 16 * D;
-  float* bp_o = ml_s + kDtWarps * 16 * 2;
-  float* bp_ml = bp_o + 16 * D;
-  static_assert((size_t)(kDtWarps * 16 * (D + 2) + 16 * (D + 2)) * 4 <= (size_t)STAGES * kStage,
+  float* ml_s = o_s + kDtWarps * 16 * OS;
+  static_assert((size_t)(kDtWarps * 16 * (OS + 2)) * 4 <= (size_t)STAGES * kStage,
                 "merge buffers must fit the ring");
+  // what the other blocks of the cluster send: [split][run] results, [split][head][2] (max, sum)
+  float* recv_o = (float*)(bars + 2 * STAGES);
+  float* recv_ml = recv_o + kDtRecvO<D>;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, tq = lane & 3;
   const int split = blockIdx.x, n_splits = gridDim.x;
@@ -242,25 +255,35 @@ attention_decode_tma_kernel(bf16* __restrict__ out, const bf16* q, int q_row_str
       l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
       l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
     }
-    // acc[n][e]: row g (e < 2) or g + 8, dimension 8n + 2tq + (e & 1)
+    // acc[n][e]: row g (e < 2) or g + 8, dimension 8n + 2tq + (e & 1); only the group's rows
+    // are real (the others pad the MMA's 16) and only those are stored and merged
+    if (g < group) {
 #pragma unroll
-    for (int n = 0; n < D / 8; ++n) {
-      *reinterpret_cast<float2*>(o_s + ((size_t)warp * 16 + g) * D + 8 * n + 2 * tq) =
-          make_float2(acc[n][0], acc[n][1]);
-      *reinterpret_cast<float2*>(o_s + ((size_t)warp * 16 + g + 8) * D + 8 * n + 2 * tq) =
-          make_float2(acc[n][2], acc[n][3]);
+      for (int n = 0; n < D / 8; ++n)
+        *reinterpret_cast<float2*>(o_s + ((size_t)warp * 16 + g) * OS + 8 * n + 2 * tq) =
+            make_float2(acc[n][0], acc[n][1]);
+      if (tq == 0) {
+        ml_s[(warp * 16 + g) * 2] = m_run[0];
+        ml_s[(warp * 16 + g) * 2 + 1] = l_run[0];
+      }
     }
-    if (tq == 0) {
-      ml_s[(warp * 16 + g) * 2] = m_run[0];
-      ml_s[(warp * 16 + g) * 2 + 1] = l_run[0];
-      ml_s[(warp * 16 + g + 8) * 2] = m_run[1];
-      ml_s[(warp * 16 + g + 8) * 2 + 1] = l_run[1];
+    if (g + 8 < group) {
+#pragma unroll
+      for (int n = 0; n < D / 8; ++n)
+        *reinterpret_cast<float2*>(o_s + ((size_t)warp * 16 + g + 8) * OS + 8 * n + 2 * tq) =
+            make_float2(acc[n][2], acc[n][3]);
+      if (tq == 0) {
+        ml_s[(warp * 16 + g + 8) * 2] = m_run[1];
+        ml_s[(warp * 16 + g + 8) * 2 + 1] = l_run[1];
+      }
     }
   }
   __syncthreads();
+  const int pairs = group * D;
+  const int run = (pairs + n_splits - 1) / n_splits;            // pairs a block of the cluster owns
   if (!failed) {
     // in warp order; a thread takes (row, dimension) pairs
-    for (int idx = tid; idx < group * D; idx += kDtThreads) {
+    for (int idx = tid; idx < pairs; idx += kDtThreads) {
       const int r = idx / D, d = idx % D;
       float m = -INFINITY;
 #pragma unroll
@@ -272,16 +295,19 @@ attention_decode_tma_kernel(bf16* __restrict__ out, const bf16* q, int q_row_str
         if (lw > 0.f) {
           const float f = exp2f(ml_s[(w * 16 + r) * 2] - m);
           l += lw * f;
-          o += o_s[((size_t)w * 16 + r) * D + d] * f;
+          o += o_s[((size_t)w * 16 + r) * OS + d] * f;
         }
       }
       if (n_splits == 1) {
         out[((size_t)t * n_q_heads + head0 + r) * D + d] = __float2bfloat16_rn(l > 0.f ? o / l : 0.f);
       } else {
-        bp_o[r * D + d] = o;
-        if (d == 0) {
-          bp_ml[2 * r] = m;
-          bp_ml[2 * r + 1] = l;
+        const int owner = idx / run;
+        st_cluster_f32(&recv_o[split * run + (idx - owner * run)], (unsigned)owner, o);
+        if (d == 0) {                            // every block needs this head's maximum and sum
+          for (int sp = 0; sp < n_splits; ++sp) {
+            st_cluster_f32(&recv_ml[(split * 16 + r) * 2], (unsigned)sp, m);
+            st_cluster_f32(&recv_ml[(split * 16 + r) * 2 + 1], (unsigned)sp, l);
+          }
         }
       }
     }
@@ -291,35 +317,25 @@ attention_decode_tma_kernel(bf16* __restrict__ out, const bf16* q, int q_row_str
   if (n_splits == 1) return;
 
   // ------------------------------------------------------------ the splits, merged in order
-  cluster_sync();
+  cluster_sync();                                // (every block gets here, whatever happened to it)
   if (!failed) {
-    // the (row, dimension) pairs are dealt to the blocks of the cluster, a thread each
-    for (int idx = split * kDtThreads + tid; idx < group * D; idx += n_splits * kDtThreads) {
+    for (int slot = tid; slot < run && split * run + slot < pairs; slot += kDtThreads) {
+      const int idx = split * run + slot;
       const int r = idx / D;
-      float ms[kDtMaxSplits], ls[kDtMaxSplits], os[kDtMaxSplits];
-#pragma unroll
-      for (int sp = 0; sp < kDtMaxSplits; ++sp) {
-        const bool live = sp < n_splits;
-        ms[sp] = live ? ld_cluster_f32(&bp_ml[2 * r], (unsigned)sp) : -INFINITY;
-        ls[sp] = live ? ld_cluster_f32(&bp_ml[2 * r + 1], (unsigned)sp) : 0.f;
-        os[sp] = live ? ld_cluster_f32(&bp_o[idx], (unsigned)sp) : 0.f;
-      }
       float m = -INFINITY;
-#pragma unroll
-      for (int sp = 0; sp < kDtMaxSplits; ++sp) m = fmaxf(m, ms[sp]);
+      for (int sp = 0; sp < n_splits; ++sp) m = fmaxf(m, recv_ml[(sp * 16 + r) * 2]);
       float l = 0.f, o = 0.f;
-#pragma unroll
-      for (int sp = 0; sp < kDtMaxSplits; ++sp) {
-        if (ls[sp] > 0.f) {
-          const float f = exp2f(ms[sp] - m);
-          l += ls[sp] * f;
-          o += os[sp] * f;
+      for (int sp = 0; sp < n_splits; ++sp) {
+        const float ls = recv_ml[(sp * 16 + r) * 2 + 1];
+        if (ls > 0.f) {
+          const float f = exp2f(recv_ml[(sp * 16 + r) * 2] - m);
+          l += ls * f;
+          o += recv_o[sp * run + slot] * f;
         }
       }
       out[((size_t)t * n_q_heads + head0) * D + idx] = __float2bfloat16_rn(l > 0.f ? o / l : 0.f);
     }
   }
-  cluster_sync();                                // nobody leaves while its result may be read
 }
 
 // DEEP: a ring twice as deep (192 KB, one block an SM) for launches that leave SMs empty anyway, so
@@ -332,7 +348,8 @@ static int launch_dt(bf16* out, const bf16* q, int q_row_stride, const int* posi
                      cudaStream_t stream) {
   constexpr int STAGES = (D == 128 ? 3 : 6) * (DEEP ? 2 : 1);
   constexpr int DB = D / 64;
-  constexpr size_t smem = 1024 + (size_t)STAGES * 2 * DB * EK_PAGE * 128 + 2 * STAGES * 8;
+  constexpr size_t smem = 1024 + (size_t)STAGES * 2 * DB * EK_PAGE * 128 + 2 * STAGES * 8 +
+                          (size_t)(kDtRecvO<D> + kDtRecvMl) * 4;
   CUtensorMap mk, mv;
   int rc;
   if (!QUERY) {

@@ -202,6 +202,13 @@ inline cudaError_t launch_pdl_cluster_x(void (*kernel)(KArgs...), dim3 grid, dim
 __device__ __forceinline__ void cluster_sync() {
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
+// A 32-bit float to the same shared-memory offset in block `rank` of this cluster (seen there
+// after the next cluster barrier).
+__device__ __forceinline__ void st_cluster_f32(float* own, unsigned rank, float v) {
+  unsigned a = (unsigned)__cvta_generic_to_shared(own), r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(rank));
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(r), "f"(v) : "memory");
+}
 // Four floats (16-byte aligned) at the same shared-memory offset in block `rank` of this cluster.
 __device__ __forceinline__ float4 ld_cluster_f32x4(const float* own, unsigned rank) {
   unsigned a = (unsigned)__cvta_generic_to_shared(own), r;
