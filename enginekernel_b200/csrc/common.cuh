@@ -209,6 +209,13 @@ __device__ __forceinline__ void st_cluster_f32(float* own, unsigned rank, float 
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(rank));
   asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(r), "f"(v) : "memory");
 }
+// Four floats (16-byte aligned) to the same shared-memory offset in block `rank` of this cluster.
+__device__ __forceinline__ void st_cluster_f32x4(float* own, unsigned rank, float4 v) {
+  unsigned a = (unsigned)__cvta_generic_to_shared(own), r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(rank));
+  asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};"
+               ::"r"(r), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+}
 // Four floats (16-byte aligned) at the same shared-memory offset in block `rank` of this cluster.
 __device__ __forceinline__ float4 ld_cluster_f32x4(const float* own, unsigned rank) {
   unsigned a = (unsigned)__cvta_generic_to_shared(own), r;

@@ -33,6 +33,7 @@ namespace ek {
 enum { TC_EPI_BF16 = 0, TC_EPI_F32 = 1, TC_EPI_SWIGLU = 2 };
 
 constexpr int kTcBM = 128;                    // rows of P per tile (TMEM lanes)
+constexpr int kTcPushRows = 8;               // sequences whose partial sums are sent, not fetched
 constexpr int kTcMaxCluster = 8;              // blocks of a cluster (the portable limit)
 
 // Instruction descriptor: bfloat16 x bfloat16 -> float, both operands K-major, M = 128.
@@ -95,15 +96,19 @@ gemm_tc_bf16_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
   constexpr bool TWO = SWAP;
   static_assert(!TWO || STAGES % 2 == 0, "two issuing threads need an even number of stages");
   constexpr uint32_t kTmemCols = TWO ? (2 * BN < 32 ? 32 : 2 * BN) : (BN < 32 ? 32 : BN);
-  extern __shared__ __align__(1024) unsigned char smem_raw[];
-  // 1024-byte alignment is needed by the 128-byte swizzle
-  unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  // No static shared memory in this kernel, so the dynamic part starts at the block's first shared
+  // byte, which is 1024-byte aligned as the 128-byte swizzle needs (checked below): two blocks of
+  // the narrowest swapped form fill an SM's shared memory to the last kilobyte.
+  extern __shared__ __align__(1024) unsigned char smem[];
   unsigned char* p_tiles = smem;
   unsigned char* q_tiles = smem + STAGES * kBytesP;
   uint64_t* bars = (uint64_t*)(q_tiles + STAGES * kBytesQ);   // full[STAGES], empty[STAGES], accum
   uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES + 1);
-  __shared__ int is_last;
-  __shared__ float rstd_s[64];                 // 1/rms of each sequence (a norm deferred to here)
+  int& is_last = *(int*)(tmem_slot + 1);
+  float* rstd_s = (float*)(tmem_slot + 2);     // [64] 1/rms of each sequence (a norm deferred to here)
+  // Clustered narrowest form with at most 8 sequences: what the other blocks of the cluster send,
+  // [split][sequence of mine][weight row] (kTcRecvFloats floats, 16-byte aligned)
+  float* recv = rstd_s + 64;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int tile_p = blockIdx.x;               // 128-row tile of P
@@ -134,7 +139,8 @@ gemm_tc_bf16_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  bool ok = true;
+  bool ok = (smem_u32(smem) & 1023u) == 0;       // never seen otherwise; the swizzled tiles would be wrong
+  if (!ok && tid == 0) atomicCAS(prm.status, 0, 9);
   if (tid == 0) {
     // ---------------------------------------------------------------- TMA producer
     int p_row0, p_row1 = 0;
@@ -172,7 +178,7 @@ gemm_tc_bf16_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
     };
     // The weight operand does not depend on the kernel before this one: the first ring of
     // weight tiles is requested before waiting for that kernel, the activations after.
-    const int first = min(n_iter, STAGES);
+    const int first = ok ? min(n_iter, STAGES) : 0;
     for (int it = 0; it < first; ++it) {
       mbar_expect_tx(full0 + 8 * (it % STAGES), kBytesP + kBytesQ);
       if (SWAP) load_p(it); else load_q(it);
@@ -181,7 +187,7 @@ gemm_tc_bf16_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
     for (int it = 0; it < first; ++it) {
       if (SWAP) load_q(it); else load_p(it);
     }
-    for (int it = first; it < n_iter; ++it) {
+    for (int it = first; it < n_iter && ok; ++it) {
       const int s = it % STAGES;
       const uint32_t phase = (it / STAGES) & 1;
       ok = mbar_wait(empty0 + 8 * s, phase ^ 1, prm.status, 1);
@@ -305,9 +311,15 @@ gemm_tc_bf16_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
     // from there each output is put together: the sum over the blocks of the cluster in split
     // order, SwiGLU of a gate row and its up row 64 further on, one rounding, one store.  A
     // block takes the sequences split, split + n_split, ...  Every block of a cluster passes
-    // both barriers whatever happened to it, so that none waits for one that gave up.
+    // the barriers whatever happened to it, so that none waits for one that gave up.
+    // With at most kTcPushRows sequences (narrowest clustered form) a block does not wait to be
+    // read: it sends each sequence's partial sums (16 bytes a store) into the shared memory of the
+    // block that owns the sequence (a buffer beside the ring - the owner may still be
+    // multiplying), and after ONE cluster barrier every block has all it needs at home.
     float* red = (float*)smem;
     constexpr int NS = CL ? kTcMaxCluster : 1;
+    const int slots = (prm.rows_q + n_split - 1) / n_split;    // sequences a block owns at most
+    const bool push = CL && BN == 16 && n_split * slots <= kTcPushRows;
     if (!failed) {
 #pragma unroll 1
       for (int c0 = 0; c0 < BN && c0 < prm.rows_q; c0 += 16) {
@@ -322,12 +334,24 @@ gemm_tc_bf16_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
         for (int i = 0; i < 16; ++i) red[(c0 + i) * kTcBM + row] = v[i];
       }
     }
+    if (push) {
+      __syncthreads();
+      if (!failed) {
+        for (int f = tid; f < prm.rows_q * (kTcBM / 4); f += 128) {
+          const int m = f / (kTcBM / 4), c = 4 * (f % (kTcBM / 4));
+          st_cluster_f32x4(&recv[(split * slots + m / n_split) * kTcBM + c], (unsigned)(m % n_split),
+                           *reinterpret_cast<const float4*>(&red[m * kTcBM + c]));
+        }
+      }
+    }
     if (CL) cluster_sync(); else __syncthreads();
     if (!failed) {
       // One 16-byte load a block of the cluster and thread; all loads of a batch are issued before
       // the first sum.
       const bool wide_ok = (prm.ldo & 3) == 0 && ((uintptr_t)prm.out & 15) == 0;
-      auto fetch4 = [&](const float* p, int sp) {
+      auto fetch4 = [&](int m, int idx, int col, int sp) {   // 4 weight rows from `col` of split sp's tile
+        if (push) return *reinterpret_cast<const float4*>(&recv[(sp * slots + idx) * kTcBM + col]);
+        const float* p = &red[m * kTcBM + col];
         return CL ? ld_cluster_f32x4(p, (unsigned)sp) : *reinterpret_cast<const float4*>(p);
       };
 #pragma unroll 1
@@ -341,9 +365,9 @@ gemm_tc_bf16_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
 #pragma unroll
           for (int sp = 0; sp < NS; ++sp) {
             const bool live = idx < owned && sp < n_split;
-            part[ps][sp] = live ? fetch4(&red[m * kTcBM + r0], sp) : make_float4(0.f, 0.f, 0.f, 0.f);
+            part[ps][sp] = live ? fetch4(m, idx, r0, sp) : make_float4(0.f, 0.f, 0.f, 0.f);
             if (EPI == TC_EPI_SWIGLU)
-              part_up[ps][sp] = live ? fetch4(&red[m * kTcBM + r0 + 64], sp) : make_float4(0.f, 0.f, 0.f, 0.f);
+              part_up[ps][sp] = live ? fetch4(m, idx, r0 + 64, sp) : make_float4(0.f, 0.f, 0.f, 0.f);
           }
         }
 #pragma unroll
@@ -455,7 +479,7 @@ gemm_tc_bf16_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
     } else {
       for (int i = 0; i < 2000; ++i) __nanosleep(1000);
     }
-    if (CL) cluster_sync();                    // nobody leaves while its partial may be read
+    if (CL && !push) cluster_sync();           // nobody leaves while its partial may be read
   } else if (!failed) {
     if (n_split > 1) {
       // partial tile -> scratch [tile][split][BN][128] (coalesced over rows)
@@ -596,8 +620,11 @@ static int launch_tc(const CUtensorMap& mp, const CUtensorMap& mq, const TcParam
   // of activations); direct with 256-wide tiles: two blocks an SM of two 48 KB
   // stages each, so that one block's epilogue runs under the other's MMAs
   constexpr int STAGES = SWAP ? swap_stages(BN) : (BN <= 128 ? 6 : 2);
-  constexpr size_t smem = 1024 + (size_t)STAGES * (kTcBM * kTcBK * 2 + BN * kTcBK * 2) +
-                          (2 * STAGES + 1) * 8 + 16;
+  // ring, barriers, TMEM slot + flag, 64 row scales, and the receive buffer of the clustered
+  // narrowest form; 2 x (this + 1 KB the system keeps) fits an SM's 228 KB
+  constexpr size_t smem = (size_t)STAGES * (kTcBM * kTcBK * 2 + BN * kTcBK * 2) + (2 * STAGES + 1) * 8 + 8 +
+                          64 * 4 + ((CL && BN == 16) ? kTcPushRows * kTcBM * 4 : 0);
+  static_assert(!SWAP || 2 * (smem + 1024) <= 228 * 1024, "two blocks an SM");
   auto kernel = gemm_tc_bf16_kernel<BN, EPI, SWAP, STAGES, CL>;
   static bool configured[kMaxDevices] = {};     // the attribute is per device and sticks
   int device = 0;
