@@ -7,16 +7,19 @@
 //   warp 0, one thread : TMA producer - fills a ring of STAGES (P tile, Q tile) pairs
 //   warp 1, one thread : issues 4 tcgen05.mma (K = 16 each) per stage, commits to the
 //                        stage's "empty" barrier, and finally to the accumulator barrier
+//                        (swapped form: one thread of warp 2 as well; they take the stages in
+//                        turn, each with an accumulator of its own)
 //   all 4 warps        : epilogue - each warp reads its 32 TMEM lanes (rows of the tile)
 // Two uses:
-//   * swapped (decode, 17..64 sequences): P = the weight matrix, Q = the activations, so
+//   * swapped (decode, 1..64 sequences): P = the weight matrix, Q = the activations, so
 //     the 128-row side of the MMA is filled with weight rows and the batch is the narrow
 //     N side; the tile is out^T and is stored transposed.  The work is bound by streaming
 //     the weights, so K is also split over blocks (grid.y).  Up to 8 blocks of a tile form
 //     a thread-block cluster: each leaves its partial tile in its own shared memory and sums
 //     its share of the tile's columns over all of them, in split order, through distributed
-//     shared memory.  More splits than that go through scratch in global memory, and the
-//     block that delivers the last partial of a tile adds them in split order.
+//     shared memory (with at most 8 sequences each block sends its partial sums to the
+//     owning block instead).  More splits than that go through scratch in global memory, and
+//     the block that delivers the last partial of a tile adds them in split order.
 //   * direct (prompts): P = activations, Q = weights, 128 x 256 tiles.
 // Epilogues: bfloat16, 32-bit, or SwiGLU (the tile holds gate rows/columns in its first
 // half and the matching up rows/columns in its second half).  The swapped form can also carry
