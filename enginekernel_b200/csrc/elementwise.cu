@@ -79,6 +79,57 @@ __global__ void rmsnorm_kernel(T* __restrict__ y, float* resid, const T* add,
   }
 }
 
+// The same for rows of at most 4,096 values in steps of 4: 128 threads a row, the row held in
+// registers (NV loads of 16 bytes a thread at most, all issued before the first use), no row in
+// shared memory - so that an SM keeps more rows in flight, which is what a kernel that only moves
+// memory needs.  Same arithmetic; the sum of squares is taken in another order.
+constexpr int kNormRegThreads = 128, kNormRegVecs = 8;
+template <typename T, int NV>
+__global__ void __launch_bounds__(kNormRegThreads, NV <= 6 ? 8 : 5)
+rmsnorm_reg_kernel(T* __restrict__ y, float* resid, const T* add, const float* __restrict__ gain,
+                   const int* rows, float eps, int hidden, int write_back) {
+  __shared__ float scratch[33];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int out_row = blockIdx.x;
+  const int src_row = rows ? rows[out_row] : out_row;
+  float* r = resid + (size_t)src_row * hidden;
+  const T* a = add ? add + (size_t)src_row * hidden : nullptr;
+  T* out = y + (size_t)out_row * hidden;
+  float4 v[NV], w[NV];
+#pragma unroll
+  for (int j = 0; j < NV; ++j) {
+    const int i = (threadIdx.x + j * kNormRegThreads) * 4;
+    v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+    w[j] = v[j];
+    if (i < hidden) {
+      v[j] = *reinterpret_cast<const float4*>(r + i);
+      if (a) w[j] = Vec4<T>::load(a + i);
+    }
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < NV; ++j) {
+    const int i = (threadIdx.x + j * kNormRegThreads) * 4;
+    if (a) {
+      v[j].x += w[j].x; v[j].y += w[j].y; v[j].z += w[j].z; v[j].w += w[j].w;
+      if (write_back && i < hidden) *reinterpret_cast<float4*>(r + i) = v[j];
+    }
+    ss += v[j].x * v[j].x + v[j].y * v[j].y + v[j].z * v[j].z + v[j].w * v[j].w;
+  }
+  const float total = block_sum(ss, scratch);
+  const float rstd = rsqrtf(total / (float)hidden + eps);
+#pragma unroll
+  for (int j = 0; j < NV; ++j) {
+    const int i = (threadIdx.x + j * kNormRegThreads) * 4;
+    if (i < hidden) {
+      const float4 g = *reinterpret_cast<const float4*>(gain + i);
+      Vec4<T>::store(out + i, make_float4(v[j].x * rstd * g.x, v[j].y * rstd * g.y, v[j].z * rstd * g.z,
+                                          v[j].w * rstd * g.w));
+    }
+  }
+}
+
 // stream += add, without a norm (the last feed-forward output when no norm follows)
 template <typename T>
 __global__ void add_residual_kernel(float* __restrict__ resid, const T* __restrict__ add, size_t n) {
@@ -143,6 +194,15 @@ static int launch_rmsnorm(void* y, float* resid, const void* add, const float* g
   if (hidden <= 0 || (size_t)hidden * 4 > 200 * 1024) return EK_ERR_ARG;
   const size_t smem = (size_t)hidden * sizeof(float);
   const bool vec = hidden % 4 == 0 && ((uintptr_t)y % 8) == 0 && ((uintptr_t)add % 8) == 0;
+  if (vec && hidden <= kNormRegThreads * kNormRegVecs * 4 && ((uintptr_t)resid % 16) == 0 &&
+      ((uintptr_t)gain % 16) == 0)
+  {
+    const int nv = (hidden / 4 + kNormRegThreads - 1) / kNormRegThreads;
+    auto reg_kernel = nv <= 2 ? rmsnorm_reg_kernel<T, 2> : nv <= 4 ? rmsnorm_reg_kernel<T, 4>
+                    : nv <= 6 ? rmsnorm_reg_kernel<T, 6> : rmsnorm_reg_kernel<T, 8>;
+    return (int)launch_pdl(reg_kernel, dim3(n_rows), dim3(kNormRegThreads), 0, stream, (T*)y, resid,
+                           (const T*)add, gain, rows, eps, hidden, write_back);
+  }
   auto kernel = vec ? rmsnorm_kernel<T, true> : rmsnorm_kernel<T, false>;
   if (smem > 40 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
