@@ -16,6 +16,7 @@ returns only the last position's hidden state.
 
 from __future__ import annotations
 
+import array
 import dataclasses
 from typing import List, Optional, Sequence
 
@@ -35,6 +36,22 @@ class StepEntry:
     slot: int
     tokens: Sequence[int]
     want: Sequence[int] = ()
+
+    def token_tensor(self) -> torch.Tensor:
+        """The tokens as an int64 tensor on the host, converted once (a prompt has thousands)."""
+        t = self.__dict__.get("_token_tensor")
+        if t is None:
+            toks = self.tokens
+            if isinstance(toks, torch.Tensor):
+                t = toks.to(torch.int64).cpu()
+            else:
+                try:                               # four times as fast as torch's own way from a list
+                    t = torch.frombuffer(array.array("q", toks), dtype=torch.int64).clone() if len(toks) \
+                        else torch.empty(0, dtype=torch.int64)
+                except (TypeError, OverflowError):
+                    t = torch.as_tensor([int(x) for x in toks], dtype=torch.int64)
+            self.__dict__["_token_tensor"] = t
+        return t
 
 
 class PlanBuffers:
@@ -111,9 +128,10 @@ class ModelRunner:
             length = self.cache.length(e.slot)                       # raises if not open
             if len(e.tokens) == 0:
                 raise StepError(f"slot {e.slot} brings no tokens")
-            for tok in e.tokens:
-                if not 0 <= int(tok) < vocab:
-                    raise StepError(f"token id {tok} is outside the vocabulary of {vocab}")
+            ids = e.token_tensor()
+            low, high = int(ids.min()), int(ids.max())
+            if low < 0 or high >= vocab:
+                raise StepError(f"token id {low if low < 0 else high} is outside the vocabulary of {vocab}")
             for w in e.want:
                 if not 0 <= int(w) < len(e.tokens):
                     raise StepError(f"wanted place {w} is outside the {len(e.tokens)} tokens "
@@ -182,7 +200,7 @@ class ModelRunner:
         for b, e in enumerate(entries):
             n = len(e.tokens)
             past = self.cache.length(e.slot)
-            ids[t:t + n] = torch.as_tensor(list(e.tokens), dtype=torch.int32)
+            ids[t:t + n] = e.token_tensor()
             pos[t:t + n] = torch.arange(past, past + n, dtype=torch.int32)
             slot[t:t + n] = e.slot
             h_pos += range(past, past + n)
