@@ -128,7 +128,10 @@ class ModelRunner:
             length = self.cache.length(e.slot)                       # raises if not open
             if len(e.tokens) == 0:
                 raise StepError(f"slot {e.slot} brings no tokens")
-            ids = e.token_tensor()
+            try:
+                ids = e.token_tensor()
+            except (ValueError, TypeError, OverflowError) as err:
+                raise StepError(f"slot {e.slot}: token ids must be integers ({err})") from None
             low, high = int(ids.min()), int(ids.max())
             if low < 0 or high >= vocab:
                 raise StepError(f"token id {low if low < 0 else high} is outside the vocabulary of {vocab}")
