@@ -26,6 +26,7 @@ from .spec import CacheSpec, TensorSpec
 
 SM_COUNT = 148
 FUSE_ROPE_ROWS = 64       # the q/k/v product does norm, rotation and cache write itself up to here
+WIDE_CLUSTER_PAGES = 64     # clusters of more than 8 key splits only from this many pages of context
 
 
 @register_part("mixer", "attention")
@@ -131,7 +132,7 @@ class Attention(Mixer):
             blocks = t * self.num_kv_heads
             pages = -(-visible // kernels.PAGE)
             # (more than 8 blocks a token only pay with many pages each: long contexts, few sequences)
-            limit = kernels.decode_tma_max_splits(self.head_dim, self.device) if pages >= 64 else \
+            limit = kernels.decode_tma_max_splits(self.head_dim, self.device) if pages >= WIDE_CLUSTER_PAGES else \
                 kernels.DECODE_TMA_PORTABLE_SPLITS
             splits = max(1, min(2 * SM_COUNT // blocks, pages, limit))
             splits = 1 << (splits.bit_length() - 1)      # clusters of 3, 5, 6, 7 pack the GPCs badly
