@@ -51,3 +51,15 @@ def test_family_width_two_dozen_sequences(folder):
     for s, g in zip(seqs, got):
         err = helpers.rel_err(g, plain.logits(model, s))
         assert err <= helpers.TOL["bfloat16"], (len(s), err)
+
+
+@pytest.mark.parametrize("batch", [3, 24])
+def test_family_width_generation_repeats_bit_for_bit(folder, batch):
+    """The same prompts twice: the same tokens at every step (sums over K splits, clusters and
+    two accumulators are taken in a fixed order; a barrier that let a thread run ahead would show)."""
+    from enginekernel_b200 import Engine
+    eng = Engine(folder, "bfloat16", max_tokens=batch * 256, max_batch=batch)
+    seqs = tiny_models.random_prompts(CFG, [20 + (11 * i) % 50 for i in range(batch)], seed=5)
+    runs = [[list(t) for t in eng.generate(seqs, 96)] for _ in range(2)]
+    assert runs[0] == runs[1]
+    eng.runner.check_kernels()
