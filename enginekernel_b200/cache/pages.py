@@ -132,24 +132,34 @@ class SlotBook:
 
     def reserve(self, slot: int, new_length: int) -> None:
         """Pages for the sequence to grow to ``new_length`` tokens, in every group."""
-        self._check_held(slot)
-        if new_length > self.max_len:
-            raise CacheError(f"a sequence of {new_length} tokens exceeds the limit of "
-                             f"{self.max_len} positions")
-        # all-or-nothing over the groups: check first, then take
+        self.reserve_all([(slot, new_length)])
+
+    def reserve_all(self, wanted) -> None:
+        """Pages for several sequences at once, ``wanted`` = (slot, new length) pairs: either every
+        sequence gets its pages in every group, or none gets any and CacheError says why."""
+        wanted = list(wanted)
+        for slot, new_length in wanted:
+            self._check_held(slot)
+            if new_length > self.max_len:
+                raise CacheError(f"a sequence of {new_length} tokens exceeds the limit of "
+                                 f"{self.max_len} positions")
+        # all-or-nothing over the sequences and the groups: count first, then take
         for g in self.groups:
-            row = g.table[slot]
-            last = (new_length + PAGE - 1) // PAGE
-            if last > g.max_pages_per_slot:
-                raise CacheError(f"a sequence of {new_length} tokens exceeds the cache's limit of "
-                                 f"{g.max_pages_per_slot * PAGE} tokens per sequence")
-            start = g._trim_mark.get(slot, 0)
-            missing = sum(1 for lp in range(start, last) if row[lp] < 0)
+            missing = 0
+            for slot, new_length in wanted:
+                row = g.table[slot]
+                last = (new_length + PAGE - 1) // PAGE
+                if last > g.max_pages_per_slot:
+                    raise CacheError(f"a sequence of {new_length} tokens exceeds the cache's limit of "
+                                     f"{g.max_pages_per_slot * PAGE} tokens per sequence")
+                start = g._trim_mark.get(slot, 0)
+                missing += sum(1 for lp in range(start, last) if row[lp] < 0)
             if missing > g.pool.available():
                 raise CacheError(f"the cache is full: {missing} more pages of {PAGE} tokens are "
                                  f"needed, {g.pool.available()} of {g.pool.n} are free")
         for g in self.groups:
-            g.cover(slot, new_length)
+            for slot, new_length in wanted:
+                g.cover(slot, new_length)
 
     def advance(self, slot: int, n: int) -> None:
         self._check_held(slot)

@@ -134,6 +134,10 @@ class SequenceCache:
     def reserve(self, slot: int, new_length: int) -> None:
         self.book.reserve(slot, new_length)
 
+    def reserve_all(self, wanted) -> None:
+        """(slot, new length) pairs: all of them get their pages, or none does."""
+        self.book.reserve_all(wanted)
+
     def advance(self, slot: int, n: int) -> None:
         self.book.advance(slot, n)
 

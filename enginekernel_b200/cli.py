@@ -35,12 +35,14 @@ def _parse_prompts(args, vocab):
 
 def cmd_generate(args) -> int:
     from .engine.engine import Engine
+    from .registry import config_from_folder, model_spec_for
     t0 = time.perf_counter()
-    probe = 64 * ((args.in_len + args.out_len) // 64 + 2) * max(args.batch, 1)
-    engine = Engine(args.model, args.dtype, max_tokens=max(args.max_tokens or 0, probe),
-                    max_batch=args.max_batch or max(args.batch, 1))
+    prompts = _parse_prompts(args, model_spec_for(config_from_folder(args.model)).vocab_size)
+    # the cache holds every prompt with its output, each counted in whole pages of 64 tokens
+    need = sum(64 * ((len(p) + args.out_len) // 64 + 1) for p in prompts)
+    engine = Engine(args.model, args.dtype, max_tokens=max(args.max_tokens or 0, need),
+                    max_batch=args.max_batch or max(len(prompts), 1))
     print(f"engine load: {time.perf_counter() - t0:.1f}s", file=sys.stderr)
-    prompts = _parse_prompts(args, engine.model.spec.vocab_size)
     kw = dict(temperature=args.temperature, top_k=args.top_k, seed=args.seed,
               stop_token_ids=[int(s) for s in args.stop_ids.split(",") if s.strip()])
     times, ttfts, out = [], [], None

@@ -100,7 +100,10 @@ attention_decode_tma_kernel(bf16* __restrict__ out, const bf16* q, int q_row_str
     tma_prefetch_map(&map_k);
     tma_prefetch_map(&map_v);
   }
-  // positions, slots and block tables were written before this step's kernels were launched
+  // Read before the wait: positions, slots and block tables must have been written by work that
+  // a plain (not programmatic) launch separates from this kernel.  A step's first kernel, the
+  // embedding lookup, is such a launch, so the state advance of the step before is complete and
+  // visible here, in a captured graph and in eager decoding alike.
   const int pos = positions[t];
   int lo = 0, hi = -1, pg_first = 0, pg_last = -1;
   if (pos >= 0) {
@@ -435,7 +438,7 @@ EK_EXPORT int ek_attention_decode_tma(void* out, const void* q, int q_row_stride
     return EK_ERR_ARG;
   const long long page_rows = (long long)n_pages * n_kv_heads * EK_PAGE;
   // one block an SM at most, and a cluster of the portable size (a deep ring is one block an SM)
-  const bool deep = (long long)n_tokens * n_kv_heads * n_splits <= 148 && n_splits <= kDtPortableSplits;
+  const bool deep = (long long)n_tokens * n_kv_heads * n_splits <= sm_count() && n_splits <= kDtPortableSplits;
 #define EK_DT(D_, DEEP_)                                                                          \
   return launch_dt<D_, DEEP_>((bf16*)out, (const bf16*)q, q_row_stride, positions, token_slot,     \
                               k_pages, v_pages, page_rows, block_table, table_stride, n_tokens,   \

@@ -138,6 +138,19 @@ inline void prefer_carveout(const void* fn, int percent_shared) {
     cudaFuncSetAttribute(fn, cudaFuncAttributePreferredSharedMemoryCarveout, percent_shared);
 }
 
+// Streaming multiprocessors of the current device (asked once per device; 0 if it cannot be asked).
+inline int sm_count() {
+  static int cached[64] = {};
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return 0;
+  if (cached[device] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) return 0;
+    cached[device] = n;
+  }
+  return cached[device];
+}
+
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
                               cudaStream_t stream, Args... args) {

@@ -239,8 +239,13 @@ using namespace ek;
   EK_EXPORT int ek_embed_##SUFFIX(float* resid, const void* table, const int* ids, int n_tokens, \
                                   int hidden, int vocab, cudaStream_t stream) {                 \
     if (n_tokens <= 0) return 0;                                                                \
-    return (int)ek::launch_pdl(embed_kernel<T>, dim3(n_tokens), dim3(256), 0, stream, resid,    \
-                               (const T*)table, ids, hidden, vocab);                            \
+    /* A plain launch, on purpose: the first kernel of a step starts only when everything   */ \
+    /* before it on the stream has finished and is visible.  The kernels behind it may then */ \
+    /* read per-step state (positions, slots) before their own griddepcontrol.wait even     */ \
+    /* when the step before was not a graph launch of its own (eager decode).               */ \
+    embed_kernel<T><<<dim3(n_tokens), dim3(256), 0, stream>>>(resid, (const T*)table, ids,     \
+                                                               hidden, vocab);                  \
+    EK_RETURN_LAUNCH_STATUS();                                                                  \
   }                                                                                             \
   EK_EXPORT int ek_rmsnorm_##SUFFIX(void* y, float* resid, const void* add, const float* gain,  \
                                     const int* rows, float eps, int n_rows, int hidden,         \

@@ -90,6 +90,17 @@ class DecodeState:
                                self.remaining, self.out_tokens, self.step_index, self.stop_ids,
                                self.n_stop, self.batch)
 
+    _ADVANCED = ("token_ids", "positions", "draws", "remaining", "sampled", "step_index")
+
+    def snapshot(self):
+        """Copies of the arrays a step advances (for measurements that replay steps and then put
+        the batch back where it was)."""
+        return {name: getattr(self, name).clone() for name in self._ADVANCED}
+
+    def restore(self, saved) -> None:
+        for name, value in saved.items():
+            getattr(self, name).copy_(value)
+
     def _body(self):
         model, cache = self.runner.model, self.runner.cache
         logits = model.forward(self.ctx, cache, self.rows, self.batch)

@@ -103,6 +103,7 @@ class Engine:
 
     def step(self, entries: Sequence) -> torch.Tensor:
         """``entries``: (slot, tokens, want) triples or :class:`StepEntry`.  Returns 32-bit
-        logits [wanted places, vocab] on the device."""
+        logits [wanted places, vocab] on the device, the caller's own (a later step does not
+        overwrite them)."""
         es = [e if isinstance(e, StepEntry) else StepEntry(*e) for e in entries]
-        return self.runner.step(es)
+        return self.runner.step(es).clone()

@@ -107,19 +107,16 @@ class DecoderModel:
             specs[run.cache] = cs if cs is not None else specs[run.cache]
         return specs
 
-    def weight_bytes_read_per_step(self) -> int:
-        """Bytes of weights a decode step reads once each (embedding rows excluded)."""
+    def weight_bytes_read_per_step(self, n_tokens: int = 1) -> int:
+        """Bytes of weights a step of ``n_tokens`` tokens reads, each once: what every scheduled
+        run's parts say they read (a layer that runs twice reads twice), the final norm and the
+        LM head.  Embedding rows are left out (a few rows of the table)."""
         total = self.lm_head.numel() * self.lm_head.element_size()
-        seen = set()
+        total += self.final_norm.bytes_read_per_step(n_tokens)
         for run in self.spec.schedule:
-            if run.layer in seen:
-                continue
-            seen.add(run.layer)
             b = self.blocks[run.layer]
-            for part in (b.mixer, b.feed_forward):
-                for v in vars(part).values():
-                    if isinstance(v, torch.Tensor) and v.dim() == 2:
-                        total += v.numel() * v.element_size()
+            for part in (b.mixer, b.feed_forward, *b.norms.values()):
+                total += part.bytes_read_per_step(n_tokens)
         return total
 
     # -- one step -----------------------------------------------------------------

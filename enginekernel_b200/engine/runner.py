@@ -95,7 +95,7 @@ class ModelRunner:
         self._uploaded = None          # event: the last step's host->device copies are done
         if model.dtype == torch.bfloat16:
             from ..ops import kernels
-            kernels.gemv_scratch(self.device)      # exist before any graph capture
+            kernels.split_scratch(self.device)      # exist before any graph capture
             kernels.tc_status(self.device)
         model.prepare(min(cache.max_len, model.spec.max_positions))
 
@@ -146,14 +146,15 @@ class ModelRunner:
     @torch.inference_mode()
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
         """Run one step; returns 32-bit logits [wanted places, vocab] on the device, in
-        the order of the entries and of each entry's ``want``."""
+        the order of the entries and of each entry's ``want``.  The result is a view of the
+        runner's workspace: it is valid until the next step (``Engine.step`` hands out a copy)."""
         entries = list(entries)
         self.check(entries)
         if not entries:
             return torch.empty((0, self.model.spec.vocab_size), dtype=torch.float32,
                                device=self.device)
-        for e in entries:                                          # all-or-nothing on pages
-            self.cache.reserve(e.slot, self.cache.length(e.slot) + len(e.tokens))
+        # all-or-nothing on pages: a step that cannot run leaves the cache as it was
+        self.cache.reserve_all((e.slot, self.cache.length(e.slot) + len(e.tokens)) for e in entries)
         total = sum(len(e.tokens) for e in entries)
         if total <= self.max_step_tokens:
             return self._run(entries)

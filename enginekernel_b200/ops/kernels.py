@@ -14,11 +14,11 @@ from ctypes import c_float, c_int, c_longlong, c_ulonglong, c_void_p
 
 import torch
 
+from . import lib
 from .lib import Function, KernelError, count_extra_launches
 
 PAGE = 64                 # tokens per cache page; must equal EK_PAGE in csrc/common.cuh
 MAX_HEAD_DIM = 256
-GEMV_MAX_ROWS = 64
 
 _SUFFIX = {torch.float32: "f32", torch.bfloat16: "bf16"}
 _P = c_void_p
@@ -64,6 +64,25 @@ def _need(cond, msg):
         raise KernelError(msg)
 
 
+def _attention_cost(q, n_tokens, positions, n_q_heads, n_kv_heads, head_dim, window, new_keys_only):
+    """While a launch record is active: what an attention launch has to read and compute.  Reads
+    the positions back (a synchronisation, which is why it is done only then).  Keys and values:
+    for single tokens every visible key of every token; for prompts (``new_keys_only``) each
+    token's own key and value once, as the work is bound by its flops anyway."""
+    if not lib.recording():
+        return
+    pos = positions[:n_tokens].to(torch.int64)
+    visible = torch.clamp(pos + 1, min=0)
+    if window:
+        visible = torch.clamp(visible, max=int(window))
+    keys = int(visible.sum().item())
+    live = int((pos >= 0).sum().item())
+    size = q.element_size()
+    kv_tokens = live if new_keys_only else keys
+    lib.annotate(bytes=size * (2 * kv_tokens * n_kv_heads * head_dim + 2 * live * n_q_heads * head_dim),
+                 flops=4 * keys * n_q_heads * head_dim)
+
+
 def _per_dtype(module, name, argtypes):
     return {dt: Function(module, f"{name}_{sfx}", argtypes) for dt, sfx in _SUFFIX.items()}
 
@@ -83,6 +102,8 @@ def embed(resid, table, ids, n_tokens):
     _need(table.is_contiguous() and resid.is_contiguous(), "embed: contiguous tensors")
     vocab, hidden = table.shape
     _need(resid.shape[-1] == hidden and resid.shape[0] >= n_tokens, "embed: resid shape")
+    if lib.recording():
+        lib.annotate(bytes=n_tokens * hidden * (table.element_size() + 4))
     _embed[table.dtype](_ptr(resid), _ptr(table), _ptr(ids), n_tokens, hidden, vocab, _stream())
 
 
@@ -99,6 +120,9 @@ def rmsnorm(y, resid, gain, eps, add=None, rows=None, n_rows=None, write_back=Tr
     if n_rows is None:
         n_rows = rows.numel() if rows is not None else resid.shape[0]
     _need(y.shape[0] >= n_rows, "rmsnorm: y has too few rows")
+    if lib.recording():
+        per_value = 4 + y.element_size() + ((y.element_size() + (4 if write_back else 0)) if add is not None else 0)
+        lib.annotate(bytes=n_rows * hidden * per_value)
     _rmsnorm[y.dtype](_ptr(y), _ptr(resid), _ptr(add), _ptr(gain), _ptr(rows), float(eps),
                       n_rows, hidden, 1 if write_back else 0, _stream())
 
@@ -118,6 +142,8 @@ def silu_mul(out, gu, n_rows=None):
           "silu_mul: out must be [rows, I] for gu [rows, 2I]")
     _need(out.is_contiguous() and gu.is_contiguous(), "silu_mul: contiguous tensors")
     rows = n_rows if n_rows is not None else gu.shape[0]
+    if lib.recording():
+        lib.annotate(bytes=3 * rows * inter * gu.element_size())
     for r0 in range(0, rows, 65535):
         r1 = min(rows, r0 + 65535)
         _silu_mul[gu.dtype](_ptr(out[r0:]), _ptr(gu[r0:]), r1 - r0, inter, _stream())
@@ -150,6 +176,8 @@ def qk_norm_rope_kv(qkv, n_tokens, q_gain, k_gain, cos, sin, rot_dim, positions,
           and token_slot.dtype == torch.int32, "qk_norm_rope_kv: int32 indices")
     for g in (q_gain, k_gain):
         _need(g is None or (g.dtype == torch.float32 and g.numel() == head_dim), "qk gains: 32-bit [D]")
+    if lib.recording():
+        lib.annotate(bytes=n_tokens * head_dim * qkv.element_size() * (2 * n_q_heads + 3 * n_kv_heads))
     _rope_kv[qkv.dtype](_ptr(qkv), qkv.stride(0), _ptr(q_gain), _ptr(k_gain), _ptr(cos), _ptr(sin),
                         rot_dim, _ptr(positions), _ptr(token_slot), _ptr(k_pages), _ptr(v_pages),
                         _ptr(block_table), block_table.stride(0), n_tokens, n_q_heads, n_kv_heads,
@@ -180,6 +208,7 @@ def attention_generic(out, q, n_tokens, positions, token_slot, k_pages, v_pages,
         _need(part_acc is not None and part_ml is not None
               and part_acc.numel() >= n_tokens * n_q_heads * n_splits * head_dim
               and part_ml.numel() >= n_tokens * n_q_heads * n_splits * 2, "attention: split buffers")
+    _attention_cost(q, n_tokens, positions, n_q_heads, n_kv_heads, head_dim, window, False)
     _attn_generic[q.dtype](_ptr(out), _ptr(q), q.stride(0), _ptr(positions), _ptr(token_slot),
                            _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.stride(0),
                            n_tokens, n_q_heads, n_kv_heads, head_dim, float(scale),
@@ -215,6 +244,7 @@ def attention_decode_bf16(out, q, n_tokens, positions, token_slot, k_pages, v_pa
         _need(part_acc is not None and part_ml is not None
               and part_acc.numel() >= n_tokens * n_q_heads * n_splits * head_dim
               and part_ml.numel() >= n_tokens * n_q_heads * n_splits * 2, "attention: split buffers")
+    _attention_cost(q, n_tokens, positions, n_q_heads, n_kv_heads, head_dim, window, False)
     _attn_decode_bf16(_ptr(out), _ptr(q), q.stride(0), _ptr(positions), _ptr(token_slot),
                       _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.stride(0),
                       n_tokens, n_q_heads, n_kv_heads, head_dim, float(scale), int(window or 0),
@@ -252,7 +282,12 @@ def attention_decode_tma(out, q, n_tokens, positions, token_slot, k_pages, v_pag
     """One new token per sequence (bfloat16, head size 64 or 128, at most 16 heads a group): the
     cache pages come by TMA, started before the kernel ahead has finished; ``n_splits`` (1 to 8)
     blocks (16 where :func:`decode_tma_max_splits` says so) share a token's pages and merge inside
-    a thread-block cluster."""
+    a thread-block cluster.
+
+    Precondition: ``positions``, ``token_slot`` and ``block_table`` are read before the kernel
+    waits for the one ahead of it, so whatever wrote them (an upload, the state advance of the
+    step before) must be separated from this launch by a launch that is not programmatic:
+    :func:`embed`, the first kernel of every step, is one."""
     _need_cuda(out, q, positions, token_slot, k_pages, v_pages, block_table)
     _need(attention_decode_tma_supported(q.dtype, head_dim, n_q_heads, n_kv_heads),
           "attention_decode_tma: bfloat16, head size 64 or 128, at most 16 query heads a KV head")
@@ -265,6 +300,7 @@ def attention_decode_tma(out, q, n_tokens, positions, token_slot, k_pages, v_pag
     _need(1 <= n_splits <= decode_tma_max_splits(head_dim, q.device),
           f"attention_decode_tma: 1 to {decode_tma_max_splits(head_dim, q.device)} splits on this device")
     _need(n_tokens <= 65535, "attention_decode_tma: at most 65535 tokens a call")
+    _attention_cost(q, n_tokens, positions, n_q_heads, n_kv_heads, head_dim, window, False)
     _attn_decode_tma(_ptr(out), _ptr(q), q.stride(0), _ptr(positions), _ptr(token_slot),
                      _ptr(k_pages), _ptr(v_pages), k_pages.shape[0], _ptr(block_table),
                      block_table.stride(0), n_tokens, n_q_heads, n_kv_heads, head_dim, float(scale),
@@ -294,6 +330,7 @@ def attention_prefill_bf16(out, q, n_tokens, positions, token_slot, cu_seqlens, 
     _need(out.is_contiguous() and out.shape[-1] == n_q_heads * head_dim, "attention: out [T, NQ*D]")
     _need(q.stride(-1) == 1 and q.stride(0) % 8 == 0, "attention: dense, 16-byte aligned q rows")
     _need(cu_seqlens.dtype == torch.int32 and cu_seqlens.numel() >= n_seqs + 1, "attention: cu_seqlens")
+    _attention_cost(q, n_tokens, positions, n_q_heads, n_kv_heads, head_dim, window, True)
     _attn_prefill_bf16(_ptr(out), _ptr(q), q.stride(0), _ptr(positions), _ptr(token_slot),
                        _ptr(cu_seqlens), n_seqs, n_tokens, _ptr(k_pages), _ptr(v_pages),
                        _ptr(block_table), block_table.stride(0), n_q_heads, n_kv_heads, head_dim,
@@ -324,6 +361,7 @@ def attention_prefill_tc(out, q, n_tokens, positions, token_slot, cu_seqlens, n_
     _need(k_pages.is_contiguous() and v_pages.is_contiguous() and k_pages.dim() == 4
           and k_pages.shape[1:] == (n_kv_heads, PAGE, head_dim), "attention: pages [P, NKV, 64, D]")
     _need(cu_seqlens.dtype == torch.int32 and cu_seqlens.numel() >= n_seqs + 1, "attention: cu_seqlens")
+    _attention_cost(q, n_tokens, positions, n_q_heads, n_kv_heads, head_dim, window, True)
     _attn_prefill_tc(_ptr(out), _ptr(q), q.stride(0), _ptr(positions), _ptr(token_slot),
                      _ptr(cu_seqlens), n_seqs, n_tokens, _ptr(k_pages), _ptr(v_pages),
                      k_pages.shape[0], _ptr(block_table), block_table.stride(0), n_q_heads,
@@ -334,10 +372,6 @@ def attention_prefill_tc(out, q, n_tokens, positions, token_slot, cu_seqlens, n_
 # ------------------------------------------------------------------ matrix products
 _gemm_f32 = Function("gemm_f32", "ek_gemm_nt_f32",
                      [_P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P])
-_gemv_bf16 = Function("gemv_bf16", "ek_gemv_bf16",
-                      [_P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                       _P, _P, c_longlong, c_int, _P])
-
 EPI_BF16, EPI_F32, EPI_SWIGLU = 0, 1, 2
 
 
@@ -349,66 +383,40 @@ def gemm_f32(out, x, w, n_rows=None):
     m = n_rows if n_rows is not None else x.shape[0]
     n, k = w.shape
     _need(x.shape[-1] == k and out.shape[-1] == n and out.shape[0] >= m, "gemm_f32: shapes disagree")
+    if lib.recording():
+        lib.annotate(bytes=4 * (n * k + m * k + m * n), flops=2 * m * n * k)
     _gemm_f32(_ptr(out), _ptr(x), _ptr(w), m, n, k, x.stride(0), w.stride(0), out.stride(0), _stream())
 
 
-SM_COUNT = 148
-_GEMV_PARTIAL_FLOATS = 4 * 1024 * 1024      # 16 MiB of split partials per device
-_GEMV_TICKETS = 16384
-_gemv_scratch = {}
+B200_SM_COUNT = 148        # used only where no device can be asked (launch plans worked out on a CPU box)
+_sm_counts = {}
 
 
-def gemv_scratch(device):
-    """Per-device scratch of the split-K path: partial tiles and zeroed tickets.  Created on
-    first use; create it before capturing a graph (``ModelRunner`` does)."""
+def sm_count(device=None) -> int:
+    """Streaming multiprocessors of ``device`` (the current one if None), asked once."""
+    if not torch.cuda.is_available():
+        return B200_SM_COUNT
+    index = torch.cuda.current_device() if device is None or torch.device(device).index is None \
+        else torch.device(device).index
+    if index not in _sm_counts:
+        _sm_counts[index] = int(torch.cuda.get_device_properties(index).multi_processor_count)
+    return _sm_counts[index]
+
+
+_SPLIT_PARTIAL_FLOATS = 4 * 1024 * 1024      # 16 MiB of split partials per device
+_SPLIT_TICKETS = 16384
+_split_scratch = {}
+
+
+def split_scratch(device):
+    """Per-device scratch of products whose K is split over more blocks than a cluster holds:
+    partial tiles and zeroed tickets.  Created on first use; create it before capturing a graph
+    (``ModelRunner`` does)."""
     key = str(torch.device(device))
-    if key not in _gemv_scratch:
-        _gemv_scratch[key] = (torch.empty(_GEMV_PARTIAL_FLOATS, dtype=torch.float32, device=device),
-                              torch.zeros(_GEMV_TICKETS, dtype=torch.int32, device=device))
-    return _gemv_scratch[key]
-
-
-GEMV_BLOCKS_PER_SM = 4
-
-
-def _gemv_plan(n_tiles, k, m):
-    """(warps a block, blocks): a grid that is resident at once (four blocks an SM), each
-    block with at least one full batch of loads for every warp."""
-    chunks = max(1, -(-k // 32))
-    unroll = 4 if m <= 16 else (2 if m <= 32 else 1)
-    warps = max(1, min(8, chunks // unroll))
-    total = n_tiles * chunks
-    blocks = max(1, min(GEMV_BLOCKS_PER_SM * SM_COUNT, total // (warps * unroll)))
-    return warps, blocks
-
-
-def gemv_bf16(out, x, w, epilogue=EPI_BF16, n_rows=None, warps=None, blocks=None):
-    """out = x . w^T for at most 64 rows of x, bfloat16 in, 32-bit accumulation.
-
-    ``epilogue``: EPI_BF16 -> out bfloat16 [M, N]; EPI_F32 -> out float32 [M, N];
-    EPI_SWIGLU -> w holds I gate rows then I up rows, out bfloat16 [M, I] = silu(g) * u.
-    """
-    _need_cuda(out, x, w)
-    m = n_rows if n_rows is not None else x.shape[0]
-    n, k = w.shape
-    _need(x.dtype == w.dtype == torch.bfloat16, "gemv_bf16: bfloat16 operands")
-    _need(m <= GEMV_MAX_ROWS, f"gemv_bf16: at most {GEMV_MAX_ROWS} rows")
-    _need(k % 8 == 0, f"gemv_bf16: inner size {k} must be a multiple of 8")
-    _need(x.stride(-1) == 1 and w.stride(-1) == 1 and out.stride(-1) == 1 and x.shape[-1] == k,
-          "gemv_bf16: dense rows of matching inner size")
-    n_out = n // 2 if epilogue == EPI_SWIGLU else n
-    _need(out.shape[-1] == n_out and out.shape[0] >= m, "gemv_bf16: out shape")
-    _need(out.dtype == (torch.float32 if epilogue == EPI_F32 else torch.bfloat16), "gemv_bf16: out dtype")
-    if epilogue == EPI_SWIGLU:
-        _need(n % 2 == 0, "gemv_bf16: SwiGLU needs gate and up rows")
-    tiles = -(-n_out // (8 if epilogue == EPI_SWIGLU else 16))
-    plan_warps, plan_blocks = _gemv_plan(tiles, k, m)
-    warps = warps or plan_warps
-    blocks = blocks or plan_blocks
-    partials, tickets = gemv_scratch(x.device)
-    _gemv_bf16(_ptr(out), _ptr(x), _ptr(w), m, n, k, x.stride(0), w.stride(0), out.stride(0),
-               epilogue, warps, blocks, _ptr(partials), _ptr(tickets), _GEMV_PARTIAL_FLOATS,
-               _GEMV_TICKETS, _stream())
+    if key not in _split_scratch:
+        _split_scratch[key] = (torch.empty(_SPLIT_PARTIAL_FLOATS, dtype=torch.float32, device=device),
+                               torch.zeros(_SPLIT_TICKETS, dtype=torch.int32, device=device))
+    return _split_scratch[key]
 
 
 _gemm_tc = Function("gemm_tc_bf16", "ek_gemm_tc_bf16",
@@ -443,7 +451,7 @@ def swap_k_split(n_out, k, epilogue):
     (clusters of 3, 5, 6 or 7 blocks do not pack the GPCs evenly: 5 -> 4 was worth 0.6-1 % of a step)."""
     tiles = -(-n_out // (64 if epilogue == EPI_SWIGLU else 128))
     k_blocks = -(-k // 64)
-    split = max(1, min(2 * SM_COUNT // tiles, k_blocks // 8, TC_MAX_CLUSTER))
+    split = max(1, min(2 * sm_count() // tiles, k_blocks // 8, TC_MAX_CLUSTER))
     return 1 << (split.bit_length() - 1)
 
 
@@ -478,7 +486,7 @@ def gemm_tc_bf16(out, x, w, epilogue=EPI_BF16, n_rows=None, swap=None, k_split=N
     if swap is None:
         swap = m <= TC_SWAP_MAX_ROWS
     _need(not swap or m <= TC_SWAP_MAX_ROWS, "gemm_tc_bf16: the swapped form takes at most 64 rows")
-    partials, tickets = gemv_scratch(x.device)
+    partials, tickets = split_scratch(x.device)
     if k_split is None:
         k_split = swap_k_split(n_out, k, epilogue) if swap else 1
     if row_scale is not None or residual is not None:
@@ -503,9 +511,12 @@ def gemm_tc_bf16(out, x, w, epilogue=EPI_BF16, n_rows=None, swap=None, k_split=N
         _need(ss_out.dtype == torch.float32 and ss_out.is_contiguous() and ss_out.shape[0] >= m
               and ss_out.shape[1] == -(-n // 128), "gemm_tc_bf16: ss_out [rows, ceil(N/128)] in 32-bit")
         ld_stream = stream.stride(0)
+    if lib.recording():
+        moved = 2 * (n * k + m * k) + m * n_out * out.element_size() + (8 * m * n if residual is not None else 0)
+        lib.annotate(bytes=moved, flops=2 * m * n * k)
     _gemm_tc(_ptr(out), _ptr(x), _ptr(w), m, n, k, x.stride(0), w.stride(0), out.stride(0),
              epilogue, 1 if swap else 0, k_split, 1 if cluster else 0, _ptr(partials), _ptr(tickets),
-             _GEMV_PARTIAL_FLOATS, _GEMV_TICKETS, _ptr(ss_in), ss_tiles, int(size), float(eps),
+             _SPLIT_PARTIAL_FLOATS, _SPLIT_TICKETS, _ptr(ss_in), ss_tiles, int(size), float(eps),
              _ptr(stream), ld_stream, _ptr(gain), _ptr(ss_out), _ptr(tc_status(x.device)), _stream())
 
 
@@ -551,6 +562,8 @@ def gemm_tc_qkv_rope(qkv, x, w, n_rows, q_gain, k_gain, qk_eps, cos, sin, positi
         ss_tiles = ss_in.shape[1]
     if k_split is None:
         k_split = swap_k_split(n, k, EPI_BF16)
+    if lib.recording():
+        lib.annotate(bytes=2 * (n * k + m * k + m * n), flops=2 * m * n * k)
     _gemm_tc_qkv(_ptr(qkv), _ptr(x), _ptr(w), m, k, x.stride(0), w.stride(0), qkv.stride(0), k_split,
                  _ptr(ss_in), ss_tiles, int(size), float(eps), _ptr(q_gain), _ptr(k_gain), float(qk_eps),
                  _ptr(cos), _ptr(sin), _ptr(positions), _ptr(token_slot), _ptr(k_pages), _ptr(v_pages),
@@ -587,6 +600,8 @@ def sample(out_token, logits, temperature, top_k, seed, streams=None, draws=None
     _need(logits.dtype == torch.float32 and logits.stride(-1) == 1, "sample: dense 32-bit logits")
     _need(out_token.dtype == torch.int32, "sample: int32 out")
     rows = n_rows if n_rows is not None else logits.shape[0]
+    if lib.recording():
+        lib.annotate(bytes=4 * rows * logits.shape[-1])
     _sample(_ptr(out_token), _ptr(logits), logits.stride(0), rows, logits.shape[-1],
             float(temperature), int(top_k), int(seed) & 0xFFFFFFFFFFFFFFFF, _ptr(streams),
             _ptr(draws), _ptr(active), _ptr(dyn), _stream())
@@ -608,6 +623,8 @@ def sample_cluster(out_token, logits, temperature, top_k, seed, streams=None, dr
     _need(logits.dtype == torch.float32 and logits.stride(-1) == 1, "sample: dense 32-bit logits")
     _need(out_token.dtype == torch.int32, "sample: int32 out")
     rows = n_rows if n_rows is not None else logits.shape[0]
+    if lib.recording():
+        lib.annotate(bytes=4 * rows * logits.shape[-1])
     _sample_cluster(_ptr(out_token), _ptr(logits), logits.stride(0), rows, logits.shape[-1],
                     float(temperature), int(top_k), int(seed) & 0xFFFFFFFFFFFFFFFF, _ptr(streams),
                     _ptr(draws), _ptr(active), _ptr(dyn), _stream())
@@ -623,6 +640,8 @@ def sample_wide(out_token, logits, temperature, seed, part_score, part_index, st
     _need(part_score.dtype == torch.float32 and part_index.dtype == torch.int32
           and part_score.numel() >= rows * SAMPLE_SEGMENTS
           and part_index.numel() >= rows * SAMPLE_SEGMENTS, "sample_wide: partial buffers")
+    if lib.recording():
+        lib.annotate(bytes=4 * rows * logits.shape[-1])
     _sample_wide(_ptr(out_token), _ptr(logits), logits.stride(0), rows, logits.shape[-1],
                  float(temperature), int(seed) & 0xFFFFFFFFFFFFFFFF, _ptr(streams), _ptr(draws),
                  _ptr(active), _ptr(dyn), _ptr(part_score), _ptr(part_index), SAMPLE_SEGMENTS,

@@ -11,6 +11,8 @@ from . import build
 _libs: Dict[str, ctypes.CDLL] = {}
 _lock = threading.Lock()
 _launch_calls = 0          # kernels launched from Python (a captured graph replays them)
+_recorder = None           # the list of the active LaunchRecord
+_pending_cost = None       # what the launcher said about the launch that comes next
 
 
 def launch_calls() -> int:
@@ -21,6 +23,78 @@ def count_extra_launches(n: int = 1) -> None:
     """For entry points that launch more than one kernel (a merge kernel after the partial ones)."""
     global _launch_calls
     _launch_calls += n
+
+
+class LaunchRecord:
+    """Collects every launch made while it is active, so that the same launches (same pointers,
+    same sizes) can be issued again, alone or grouped by entry point, for timing.
+
+    An entry is ``(name, issue, cost)``: ``issue(stream)`` launches it again on the raw stream
+    handle ``stream`` and ``cost`` is what the launcher said the launch has to move and compute,
+    ``{"bytes": ..., "flops": ...}`` (see :func:`annotate`; empty if it said nothing).  The
+    tensors behind the recorded pointers must outlive the record."""
+
+    def __init__(self):
+        self.launches = []
+
+    def __enter__(self):
+        global _recorder
+        if _recorder is not None:
+            raise RuntimeError("a launch record is already active")
+        _recorder = self.launches
+        return self
+
+    def __exit__(self, *exc):
+        global _recorder, _pending_cost
+        _recorder = None
+        _pending_cost = None
+        return False
+
+    def names(self):
+        """Entry points in the order of their first launch."""
+        seen = []
+        for name, _, _ in self.launches:
+            if name not in seen:
+                seen.append(name)
+        return seen
+
+    def cost(self, name: str = None):
+        """Summed bytes and flops of the recorded launches (of ``name`` only, if given)."""
+        total = {"bytes": 0, "flops": 0, "launches": 0}
+        for n, _, c in self.launches:
+            if name is None or n == name:
+                total["bytes"] += c.get("bytes", 0)
+                total["flops"] += c.get("flops", 0)
+                total["launches"] += 1
+        return total
+
+    def issue(self, stream: int, name: str = None) -> int:
+        """Launch again, on ``stream`` (a raw handle), every recorded launch (of entry point
+        ``name`` only, if given); returns how many."""
+        n = 0
+        for launch_name, again, _ in self.launches:
+            if name is None or launch_name == name:
+                again(stream)
+                n += 1
+        return n
+
+
+def recording() -> bool:
+    return _recorder is not None
+
+
+def annotate(bytes: int = 0, flops: int = 0) -> None:
+    """Called by a launcher just before its launch while a record is active: the bytes the
+    launch has to read and write and the floating-point operations it has to do."""
+    global _pending_cost
+    _pending_cost = {"bytes": int(bytes), "flops": int(flops)}
+
+
+def record_library_call(name: str, again, bytes: int = 0, flops: int = 0) -> None:
+    """Put a library call (a cuBLAS product through torch) into the active record; ``again()``
+    repeats it on torch's current stream."""
+    if _recorder is not None:
+        _recorder.append((name, lambda stream: again(), {"bytes": int(bytes), "flops": int(flops)}))
 
 
 class KernelError(RuntimeError):
@@ -89,4 +163,8 @@ class Function:
         if not self.check_status:
             return fn(*args)
         _launch_calls += 1
+        if _recorder is not None:
+            global _pending_cost
+            head, cost, _pending_cost = args[:-1], _pending_cost or {}, None
+            _recorder.append((self.name, lambda stream: check(fn(*head, stream), self.name), cost))
         check(fn(*args), self.name)

@@ -11,7 +11,7 @@ from __future__ import annotations
 
 import torch
 
-from . import kernels
+from . import kernels, lib
 
 SMALL_ROWS = kernels.TC_SWAP_MAX_ROWS
 
@@ -74,9 +74,9 @@ def linear(x, w, ctx, name: str, n_rows=None, out_dtype=None, defer=None):
         # rows that TMA cannot address (inner size or stride not a multiple of 8 values): the
         # library product, rounded once from its 32-bit accumulator
         if want_f32:
-            torch.matmul(x[:m].float(), w.float().t(), out=out)
+            _library_product(x[:m].float(), w.float(), out)
         else:
-            torch.matmul(x[:m], w.t(), out=out)
+            _library_product(x[:m], w, out)
         return out
     if m <= SMALL_ROWS:
         kernels.gemm_tc_bf16(out, x, w, epi, n_rows=m, swap=True, row_scale=row_scale)
@@ -84,5 +84,17 @@ def linear(x, w, ctx, name: str, n_rows=None, out_dtype=None, defer=None):
         # 32-bit logits for many rows: 128 x 128 tiles with the accumulator stored as it is
         kernels.gemm_tc_bf16(out, x, w, epi, n_rows=m, swap=False)
     else:
-        torch.matmul(x[:m], w.t(), out=out)
+        _library_product(x[:m], w, out)
     return out
+
+
+def _library_product(x, w, out):
+    """out = x . w^T by the library (cuBLAS through torch), as the reference does for prompts
+    (engine/ek_model.py:298, 311, 203-209)."""
+    torch.matmul(x, w.t(), out=out)
+    if lib.recording():
+        m, k = x.shape
+        n = w.shape[0]
+        lib.record_library_call("library_matmul", lambda: torch.matmul(x, w.t(), out=out),
+                                bytes=x.element_size() * (m * k + n * k) + out.element_size() * m * n,
+                                flops=2 * m * n * k)

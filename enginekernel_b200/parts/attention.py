@@ -24,7 +24,6 @@ from ..registry import lookup_part, register_part
 from .base import DeferredNorm, Mixer
 from .spec import CacheSpec, TensorSpec
 
-SM_COUNT = 148
 FUSE_ROPE_ROWS = 64       # the q/k/v product does norm, rotation and cache write itself up to here
 WIDE_CLUSTER_PAGES = 64     # clusters of more than 8 key splits only from this many pages of context
 
@@ -72,6 +71,10 @@ class Attention(Mixer):
         if self.qk_norm_eps is not None:
             self.q_gain = tensors[w["q_norm"]].to(torch.float32).contiguous()
             self.k_gain = tensors[w["k_norm"]].to(torch.float32).contiguous()
+
+    def bytes_read_per_step(self, n_tokens):
+        return sum(t.numel() * t.element_size() for t in (self.w_qkv, self.w_o, self.q_gain, self.k_gain)
+                   if t is not None)
 
     # ------------------------------------------------------------------
     takes_deferred_norm = True
@@ -134,7 +137,7 @@ class Attention(Mixer):
             # (more than 8 blocks a token only pay with many pages each: long contexts, few sequences)
             limit = kernels.decode_tma_max_splits(self.head_dim, self.device) if pages >= WIDE_CLUSTER_PAGES else \
                 kernels.DECODE_TMA_PORTABLE_SPLITS
-            splits = max(1, min(2 * SM_COUNT // blocks, pages, limit))
+            splits = max(1, min(2 * kernels.sm_count(self.device) // blocks, pages, limit))
             splits = 1 << (splits.bit_length() - 1)      # clusters of 3, 5, 6, 7 pack the GPCs badly
             kernels.attention_decode_tma(
                 out, qkv, t, ctx.positions, ctx.token_slot, entry.k_pages, entry.v_pages,
@@ -146,7 +149,7 @@ class Attention(Mixer):
             # the keys so that the blocks just fill the machine once, or about twice when one
             # filling cannot be approached; never finer than two pages a split.
             blocks = t * self.num_kv_heads * -(-(self.num_heads // self.num_kv_heads) // 16)
-            resident = 3 * SM_COUNT
+            resident = 3 * kernels.sm_count(self.device)
             splits = resident // blocks
             if blocks * splits < 0.7 * resident:
                 splits = int(1.8 * resident / blocks + 0.5)
@@ -155,8 +158,8 @@ class Attention(Mixer):
         else:
             blocks = t * self.num_heads
             splits = 1
-            if blocks < 2 * SM_COUNT and ctx.max_context > 512:
-                splits = max(1, min(-(-visible // 256), -(-4 * SM_COUNT // blocks), 64))
+            if blocks < 2 * kernels.sm_count(self.device) and ctx.max_context > 512:
+                splits = max(1, min(-(-visible // 256), -(-4 * kernels.sm_count(self.device) // blocks), 64))
             unit = 128
         per_split, acc, ml = 0, None, None
         if splits > 1 and not fast_decode:      # the decode kernel cuts each token's own range

@@ -76,8 +76,14 @@ class StepContext:
     dtype: torch.dtype
     device: torch.device
     workspace: Workspace
-    #: host copies for parts written in plain torch (tests, toy parts); None inside a
-    #: captured decode step, where the host does not know the values
+    #: Host copies of positions, token_slot and cu_seqlens, for parts written in plain torch (tests,
+    #: toy parts).  They exist only in steps that the host lays out (``ModelRunner.step``: prompts,
+    #: chunks, single tokens through ``Engine.step``).  Inside the decode step of ``generate`` -
+    #: captured once in a CUDA graph and replayed - they are None: positions advance on the device
+    #: and the host does not know them.  There a part may use only the device tensors above
+    #: (``n_tokens``, ``n_seqs``, ``is_decode``, ``max_new``, ``max_context`` and the workspace are
+    #: fixed for a captured step), must skip rows whose position is negative, and must not
+    #: allocate or synchronise.
     host_positions: Optional[List[int]] = None
     host_token_slot: Optional[List[int]] = None
     host_cu_seqlens: Optional[List[int]] = None
@@ -113,6 +119,13 @@ class Part:
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
         """Take the tensors named in ``spec.weights`` (already on the device, in their
         stored precision) and keep them in the form the kernels want."""
+
+    def bytes_read_per_step(self, n_tokens: int) -> int:
+        """Bytes of this part's weights that a step of ``n_tokens`` tokens has to read, each
+        once (what a bandwidth roofline divides by time).  The default counts every tensor the
+        part holds; a part that touches only some of its weights (routed experts) says how many."""
+        return sum(v.numel() * v.element_size() for v in vars(self).values()
+                   if isinstance(v, torch.Tensor))
 
     def param(self, name: str):
         try:

@@ -41,6 +41,9 @@ class GatedMLP(FeedForward):
             .to(self.dtype).contiguous()
         self.w_down = tensors[w["down"]].to(self.dtype).contiguous()
 
+    def bytes_read_per_step(self, n_tokens):
+        return sum(t.numel() * t.element_size() for t in (self.w_gate_up, self.w_down))
+
     takes_deferred_norm = True
     defers_norm = True
 

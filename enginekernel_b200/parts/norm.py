@@ -29,6 +29,9 @@ class RMSNorm(Norm):
     def load(self, tensors):
         self.gain = tensors[self.spec.weights["gain"]].to(torch.float32).contiguous()
 
+    def bytes_read_per_step(self, n_tokens):
+        return self.gain.numel() * self.gain.element_size()
+
     def deferrable(self):
         return self.gain, self.eps
 

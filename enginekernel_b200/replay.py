@@ -54,7 +54,7 @@ def main(argv=None) -> int:
             if rid not in slots:
                 slots[rid] = engine.open_sequence()
             entries.append(StepEntry(slots[rid], e["tokens"], e.get("want", [])))
-        logits = engine.step(entries)
+        logits = engine.runner.step(entries)          # a view, written to the file before the next step
         if logits.shape[0] > 0:
             arr = logits.detach().to("cpu", torch.float32).contiguous().numpy().astype("<f4", copy=False)
             path = os.path.join(args.out, f"{step['step']}.f32")

@@ -43,14 +43,16 @@ def random_tensors(expected: Mapping[str, TensorSpec], seed: int, dtype=torch.bf
     return out
 
 
-def write_random_model(folder: str, config, seed: int, dtype=torch.bfloat16) -> str:
-    """Write ``config.json`` and ``model.safetensors`` for ``config`` under ``folder``."""
+def write_random_model(folder: str, config, seed: int, dtype=torch.bfloat16, device="cpu") -> str:
+    """Write ``config.json`` and ``model.safetensors`` for ``config`` under ``folder``.  Drawn on
+    ``device`` (a GPU is much faster for gigabytes of weights, but gives other values than the CPU)."""
     from safetensors.torch import save_file
     from ..engine.model import expected_tensors
     from ..registry import model_spec_for
     os.makedirs(folder, exist_ok=True)
     spec = model_spec_for(config)
-    tensors = random_tensors(expected_tensors(spec), seed, dtype=dtype)
+    tensors = random_tensors(expected_tensors(spec), seed, dtype=dtype, device=device)
+    tensors = {k: v.cpu() for k, v in tensors.items()}
     raw = config.to_dict()
     raw["torch_dtype"] = {torch.bfloat16: "bfloat16", torch.float32: "float32"}.get(dtype, str(dtype))
     with open(os.path.join(folder, "config.json"), "w") as f:

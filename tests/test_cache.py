@@ -157,3 +157,28 @@ def test_random_churn_never_loses_or_doubles_a_page():
     for s in list(live):
         c.close(s)
     assert all(g.pool.available() == g.pool.n for g in groups)
+
+
+def test_a_step_of_several_sequences_gets_all_its_pages_or_none():
+    """Three sequences ask together for more pages than are left: none of them keeps a page, and
+    what was free before is free after (a step that cannot run must not shrink the cache)."""
+    c = make_cache()                                    # 10 pages
+    a, b, d = c.open(), c.open(), c.open()
+    c.reserve(a, 2 * PAGE)
+    c.advance(a, 2 * PAGE)
+    before = c.free_tokens()
+    assert before == 8 * PAGE
+    with pytest.raises(CacheError, match="cache is full"):
+        c.reserve_all([(a, 5 * PAGE), (b, 3 * PAGE), (d, 3 * PAGE + 1)])      # 3 + 3 + 4 = 10 > 8
+    assert c.free_tokens() == before
+    for g in c.groups:
+        if g.page_group is not None:
+            assert g.page_group.pages_of(b) == [] and g.page_group.pages_of(d) == []
+            assert len(g.page_group.pages_of(a)) == 2
+    c.reserve_all([(a, 5 * PAGE), (b, 3 * PAGE), (d, 2 * PAGE)])              # 3 + 3 + 2 = 8
+    assert c.free_tokens() == 0
+    with pytest.raises(CacheError, match="not open"):
+        c.reserve_all([(a, 5 * PAGE), (3, 1)])
+    for s in (a, b, d):
+        c.close(s)
+    assert c.free_tokens() == 10 * PAGE

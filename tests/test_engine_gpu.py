@@ -10,14 +10,19 @@ from tests.plain import tiny_models
 pytestmark = pytest.mark.gpu
 
 CONFIGS = {"A": (tiny_models.TINY_A, 0), "B": (tiny_models.TINY_B, 1), "C": (tiny_models.TINY_C, 2),
-           "D": (tiny_models.TINY_D, 3), "E": (tiny_models.TINY_E, 4)}
+           "D": (tiny_models.TINY_D, 3), "E": (tiny_models.TINY_E, 4),
+           # A with matrices fifteen times as large: with the usual N(0, 0.02) and a tied head, greedy
+           # decoding of A only repeats the prompt's last token, which no test of generation can use
+           "A_sharp": (tiny_models.TINY_A, 5)}
+WEIGHT_OPTIONS = {"A_sharp": dict(linear_std=0.3)}
 
 
 @pytest.fixture(scope="module")
 def folders(tmp_path_factory):
     out = {}
     for tag, (cfg, seed) in CONFIGS.items():
-        out[tag] = helpers.make_folder(tmp_path_factory.mktemp("tiny_" + tag), cfg, seed)
+        out[tag] = helpers.make_folder(tmp_path_factory.mktemp("tiny_" + tag), cfg, seed,
+                                       **WEIGHT_OPTIONS.get(tag, {}))
     return out
 
 
@@ -125,27 +130,35 @@ def test_padding_and_batch_mates_change_nothing(engines):
         assert helpers.rel_err(t, a) <= 1e-6
 
 
+def check_tokens_against_plain(model, prompt, tokens, dtype):
+    """32-bit: the plain arg-max at every position.  bfloat16 may pick another token where two
+    logits are within rounding: every emitted token must be within twice the logits' bound of the
+    plain arg-max at its position (teacher-forced on the emitted tokens)."""
+    if dtype == "float32":
+        assert tokens == plain.greedy(model, prompt, len(tokens))
+        return
+    lg = plain.logits(model, list(prompt) + list(tokens[:-1]))[len(prompt) - 1:]
+    scale = lg.abs().max().item()
+    for step, (row, tok) in enumerate(zip(lg, tokens)):
+        gap = row.max().item() - row[tok].item()
+        assert gap <= 2 * helpers.TOL[dtype] * scale, (step, tok, gap, scale)
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_greedy_generation_through_the_entry_point(engines, plains, folders, dtype):
-    for tag in ("A", "B"):
+    for tag in ("A_sharp", "B", "D"):
         cfg = CONFIGS[tag][0]
         eng = engines(tag, dtype)
-        lens = (5, 9, 13) if tag == "A" else (1, 7, 16, 31)
+        lens = (5, 9, 13) if tag == "A_sharp" else (1, 7, 16, 31)
         prompts = tiny_models.random_prompts(cfg, lens, seed=60)
-        steps = list(eng.generate(prompts, 8))
-        assert len(steps) == 8 and all(len(s) == len(prompts) for s in steps)
+        steps = list(eng.generate(prompts, 12))
+        assert len(steps) == 12 and all(len(s) == len(prompts) for s in steps)
         got = [[s[b] for s in steps] for b in range(len(prompts))]
-        assert got == eng.generate_all(prompts, 8)
-        if dtype == "float32":
-            assert got == [plain.greedy(plains[tag], p, 8) for p in prompts]
-        else:
-            # bfloat16 may pick another token where two logits are within rounding: every
-            # emitted token must be within the bound of the plain arg-max at its position
-            for p, g in zip(prompts, got):
-                lg = plain.logits(plains[tag], p + g[:-1])[len(p) - 1:]
-                scale = lg.abs().max().item()
-                for row, tok in zip(lg, g):
-                    assert row.max().item() - row[tok].item() <= 2 * helpers.TOL[dtype] * scale
+        assert got == eng.generate_all(prompts, 12)
+        for p, g in zip(prompts, got):
+            check_tokens_against_plain(plains[tag], p, g, dtype)
+        # the outputs are not one repeated token: an engine stuck after its first step would show
+        assert max(len(set(plain.greedy(plains[tag], p, 12))) for p in prompts) >= 6
 
 
 def test_sampling_through_the_entry_point(engines, plains):
@@ -157,15 +170,21 @@ def test_sampling_through_the_entry_point(engines, plains):
     got = eng.generate_all(prompts, 12, temperature=0.8, top_k=0, seed=1234)
     again = eng.generate_all(prompts, 12, temperature=0.8, top_k=0, seed=1234)
     assert got == again
-    alone = eng.generate_all([prompts[2]], 12, temperature=0.8, seed=1234)
-    for b, p in enumerate(prompts):
-        ids = list(p)
-        for step, tok in enumerate(got[b]):
+
+    def plain_draws(prompt, stream, n, temperature, top_k, seed):
+        ids, out = list(prompt), []
+        for step in range(n):
             row = plain.logits(plains[tag], ids)[-1]
-            assert tok == plain.sample_token(row, 0.8, 0, 1234, b, step), (b, step)
-            ids.append(tok)
-    # draws depend on the request's index, not on batch mates: request 2 alone is stream 0
-    assert alone[0] != got[2] or True
+            out.append(plain.sample_token(row, temperature, top_k, seed, stream, step))
+            ids.append(out[-1])
+        return out
+    for b, p in enumerate(prompts):
+        assert got[b] == plain_draws(p, b, 12, 0.8, 0, 1234), b
+    # draws depend on the request's index in its call, not on batch mates: request 2 alone is
+    # stream 0 of its call and draws what the plain rule draws for stream 0
+    alone = eng.generate_all([prompts[2]], 12, temperature=0.8, seed=1234)
+    assert alone[0] == plain_draws(prompts[2], 0, 12, 0.8, 0, 1234)
+    assert alone[0] != got[2], "streams 0 and 2 should not draw alike over 12 tokens"
     topk = eng.generate_all(prompts, 6, temperature=1.5, top_k=3, seed=7)
     for b, p in enumerate(prompts):
         ids = list(p)
@@ -177,19 +196,24 @@ def test_sampling_through_the_entry_point(engines, plains):
 
 
 def test_stop_tokens_and_early_end(engines, plains):
-    tag = "A"
+    """A stop token that first appears inside the captured decode steps ends its sequence there,
+    while its batch mates go on exactly as they would alone; a budget of 2 ends another one."""
+    tag = "A_sharp"
     cfg = CONFIGS[tag][0]
     eng = engines(tag, "float32")
     prompts = tiny_models.random_prompts(cfg, (5, 9, 13), seed=60)
-    free = plain.greedy(plains[tag], prompts[1], 8)
-    stop = free[3]
-    first = free.index(stop)
-    out = eng.generate_all(prompts, [8, 8, 2], stop_token_ids=[stop])
-    assert out[1] == free[:first + 1]
-    assert len(out[2]) <= 2
-    steps = list(eng.generate(prompts, 8, stop_token_ids=[stop]))
-    col = [s[1] for s in steps]
-    assert col[:first + 1] == free[:first + 1] and all(t == -1 for t in col[first + 1:])
+    free = [plain.greedy(plains[tag], p, 10) for p in prompts]
+    # a token of request 1 that first appears at step 2 or later and that requests 0 and 2 never emit
+    stop, first = next((tok, i) for i, tok in enumerate(free[1])
+                       if i >= 2 and free[1].index(tok) == i and tok not in free[0] and tok not in free[2])
+    out = eng.generate_all(prompts, [10, 10, 2], stop_token_ids=[stop])
+    assert out[0] == free[0]                           # untouched by its mates' ends
+    assert out[1] == free[1][:first + 1]               # the stop token is kept as the last one
+    assert out[2] == free[2][:2]                       # its budget
+    steps = list(eng.generate(prompts, 10, stop_token_ids=[stop]))
+    cols = [[s[b] for s in steps] for b in range(3)]
+    assert cols[0] == free[0] and cols[2] == free[2]
+    assert cols[1][:first + 1] == free[1][:first + 1] and all(t == -1 for t in cols[1][first + 1:])
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

@@ -34,9 +34,51 @@ def test_family_width_ragged_batch(folder, dtype):
     for s, g in zip(seqs, got):
         err = helpers.rel_err(g, plain.logits(model, s))
         assert err <= helpers.TOL[dtype], (dtype, len(s), err)
-    steps = list(eng.generate(seqs, 5))
+
+
+def tokens_follow_plain(model, prompt, tokens, dtype):
+    """32-bit: the plain arg-max.  bfloat16: every emitted token within twice the logits' bound
+    of the plain arg-max at its position, teacher-forced on the emitted tokens."""
     if dtype == "float32":
-        assert [[st[b] for st in steps] for b in range(3)] == [plain.greedy(model, s, 5) for s in seqs]
+        assert tokens == plain.greedy(model, prompt, len(tokens))
+        return
+    lg = plain.logits(model, list(prompt) + list(tokens[:-1]))[len(prompt) - 1:]
+    scale = lg.abs().max().item()
+    for step, (row, tok) in enumerate(zip(lg, tokens)):
+        gap = row.max().item() - row[tok].item()
+        assert gap <= 2 * helpers.TOL[dtype] * scale, (step, tok, gap, scale)
+
+
+@pytest.mark.parametrize("dtype,batch", [("float32", 3), ("bfloat16", 3), ("bfloat16", 24)])
+def test_family_width_generation_follows_plain(folder, dtype, batch):
+    """Generation through the captured decode step at heads of 128: the q/k/v product that
+    normalises, rotates and writes the cache itself, the norms carried by the products (3
+    sequences) or the norm kernel (24), the TMA-fed decode attention, positions advanced on the
+    device - every token against the plain implementation."""
+    from enginekernel_b200 import Engine
+    model = helpers.plain_model(folder)
+    eng = Engine(folder, dtype, max_tokens=batch * 192, max_batch=batch)
+    seqs = tiny_models.random_prompts(CFG, [9 + (13 * i) % 80 for i in range(batch)], seed=21)
+    got = eng.generate_all(seqs, 24)
+    for p, g in zip(seqs, got):
+        assert len(g) == 24
+        tokens_follow_plain(model, p, g, dtype)
+    eng.runner.check_kernels()
+
+
+@pytest.mark.parametrize("batch", [3, 24])
+def test_family_width_eager_decode_equals_the_captured_step(folder, batch):
+    """Without the graph each decode step is launched kernel by kernel, and the state advance of
+    one step is still in flight when the next step's kernels are queued behind it: the tokens must
+    be the captured step's, bit for bit, over many steps."""
+    from enginekernel_b200 import Engine
+    seqs = tiny_models.random_prompts(CFG, [20 + (11 * i) % 50 for i in range(batch)], seed=5)
+    runs = []
+    for use_graph in (True, False):
+        eng = Engine(folder, "bfloat16", max_tokens=batch * 256, max_batch=batch, use_graph=use_graph)
+        runs.append(eng.generate_all(seqs, 64))
+        eng.runner.check_kernels()
+    assert runs[0] == runs[1]
 
 
 def test_family_width_two_dozen_sequences(folder):
@@ -63,3 +105,37 @@ def test_family_width_generation_repeats_bit_for_bit(folder, batch):
     runs = [[list(t) for t in eng.generate(seqs, 96)] for _ in range(2)]
     assert runs[0] == runs[1]
     eng.runner.check_kernels()
+
+
+# The smallest model of the family at its full depth and vocabulary (28 layers, 151,936 tokens),
+# 32-bit logits of a batch of 4 against the plain implementation, then the same in bfloat16.
+SMALL_FAMILY = {
+    "architectures": ["Qwen3ForCausalLM"],
+    "num_hidden_layers": 28, "hidden_size": 1024, "num_attention_heads": 16,
+    "num_key_value_heads": 8, "head_dim": 128, "intermediate_size": 3072,
+    "vocab_size": 151936, "rope_theta": 1000000.0, "rms_norm_eps": 1e-6,
+    "max_position_embeddings": 8192, "tie_word_embeddings": True,
+}
+
+
+@pytest.fixture(scope="module")
+def small_family(tmp_path_factory):
+    folder = helpers.make_folder(tmp_path_factory.mktemp("small_family"), SMALL_FAMILY, 4)
+    model = helpers.plain_model(folder)
+    seqs = tiny_models.random_prompts(SMALL_FAMILY, [70, 9, 33, 130], seed=3)
+    want = [plain.logits(model, s)[-12:] for s in seqs]
+    del model
+    return folder, seqs, want
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_whole_small_family_model_at_full_depth_batch_of_4(small_family, dtype):
+    from enginekernel_b200 import Engine
+    folder, seqs, want = small_family
+    eng = Engine(folder, dtype, max_tokens=4 * 192, max_batch=4)
+    got = helpers.batch_then_steps(eng, seqs, [len(s) - 6 for s in seqs])
+    for s, g, w in zip(seqs, got, want):
+        err = helpers.rel_err(g[-12:] if len(s) >= 12 else g, w[-len(s):])
+        assert err <= helpers.TOL[dtype], (dtype, len(s), err)
+    del eng
+    torch.cuda.empty_cache()

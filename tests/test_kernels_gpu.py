@@ -441,41 +441,6 @@ def test_gemm_f32_is_true_32_bit(m, n, k_):
         assert torch.equal(one[0], out[m - 1])
 
 
-@pytest.mark.parametrize("m", [1, 3, 8, 9, 33, 64])
-@pytest.mark.parametrize("n,k_", [(331, 80), (2560, 4096), (48, 8), (1000, 1000)])
-def test_gemv_bf16_epilogues(m, n, k_):
-    k = K()
-    x = rnd(m, k_, dtype=torch.bfloat16, seed=1)
-    w = rnd(n, k_, dtype=torch.bfloat16, seed=2, scale=0.05)
-    want = x.double() @ w.double().t()
-    out32 = torch.empty(m, n, device=DEV)
-    k.gemv_bf16(out32, x, w, k.EPI_F32)
-    assert rel(out32, want) <= 1e-5
-    out16 = torch.empty(m, n, dtype=torch.bfloat16, device=DEV)
-    k.gemv_bf16(out16, x, w, k.EPI_BF16)
-    assert rel(out16, want) <= 4e-3                       # one rounding to bfloat16
-    if n % 2 == 0:
-        inter = n // 2
-        act = torch.empty(m, inter, dtype=torch.bfloat16, device=DEV)
-        k.gemv_bf16(act, x, w, k.EPI_SWIGLU)
-        g, u = want[:, :inter], want[:, inter:]
-        assert rel(act, g / (1 + torch.exp(-g)) * u) <= 4e-3
-    for warps, blocks in ((1, 1), (4, 3), (8, 7), (32, 2), (2, 64), (8, 592), (3, 37)):
-        o = torch.empty(m, n, device=DEV)
-        k.gemv_bf16(o, x, w, k.EPI_F32, warps=warps, blocks=blocks)
-        assert rel(o, want) <= 1e-5
-        again = torch.empty(m, n, device=DEV)
-        k.gemv_bf16(again, x, w, k.EPI_F32, warps=warps, blocks=blocks)
-        assert torch.equal(o, again)                       # fixed summation order: bit-stable
-        if n % 2 == 0:
-            act2 = torch.empty(m, n // 2, dtype=torch.bfloat16, device=DEV)
-            k.gemv_bf16(act2, x, w, k.EPI_SWIGLU, warps=warps, blocks=blocks)
-            g, u = want[:, :n // 2], want[:, n // 2:]
-            assert rel(act2, g / (1 + torch.exp(-g)) * u) <= 4e-3
-    _, tickets = k.gemv_scratch(DEV)
-    assert int(tickets.abs().sum()) == 0                   # every launch leaves the tickets zero
-
-
 @pytest.mark.parametrize("m,n,k_", [(17, 256, 128), (64, 2560, 4096), (33, 1000, 1000), (1, 128, 64),
                                     (48, 331 * 2, 80), (64, 6144, 2560), (24, 1280, 2560),
                                     (24, 20012, 2560)])
@@ -506,7 +471,7 @@ def test_gemm_tc_swapped(m, n, k_):
     k.gemm_tc_bf16(b32, x, w, k.EPI_F32, swap=True, k_split=3, cluster=False)
     assert torch.equal(a32, b32)
     k.check_tc_status(DEV)
-    _, tickets = k.gemv_scratch(DEV)
+    _, tickets = k.split_scratch(DEV)
     assert int(tickets.abs().sum()) == 0
 
 
@@ -648,13 +613,13 @@ def test_gemm_tc_direct(m, n, k_):
     k.check_tc_status(DEV)
 
 
-def test_gemv_refuses_what_it_cannot_do():
+def test_launchers_refuse_what_they_cannot_do():
     k = K()
     from enginekernel_b200.ops.lib import KernelError
     x = rnd(2, 12, dtype=torch.bfloat16)
     w = rnd(16, 12, dtype=torch.bfloat16)
-    with pytest.raises(KernelError):
-        k.gemv_bf16(torch.empty(2, 16, dtype=torch.bfloat16, device=DEV), x, w)
+    with pytest.raises(KernelError):                      # inner size 12 is no multiple of 8
+        k.gemm_tc_bf16(torch.empty(2, 16, dtype=torch.bfloat16, device=DEV), x, w)
     with pytest.raises(KernelError):
         k.check_head_dim(24)
     with pytest.raises(KernelError):

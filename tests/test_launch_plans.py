@@ -16,7 +16,7 @@ def test_k_split_of_the_swapped_form(n_out, k, epi):
     k_blocks = -(-k // 64)
     assert 1 <= split <= kernels.TC_MAX_CLUSTER
     assert split & (split - 1) == 0                        # clusters of 3, 5, 6, 7 blocks run slowly
-    assert split == 1 or tiles * split <= 2 * kernels.SM_COUNT      # one filling of the machine
+    assert split == 1 or tiles * split <= 2 * kernels.sm_count()      # one filling of the machine
     assert split == 1 or k_blocks // split >= 8            # a block keeps a ring's worth of K
 
 
