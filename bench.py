@@ -177,6 +177,12 @@ def make_prompts(shape: str, batch: int, vocab: int, seed: int = 0):
     return [torch.randint(0, vocab, (n,), generator=g).tolist() for n in lengths]
 
 
+def e2e_new_tokens(steps, context, prompts):
+    """New tokens of an end-to-end call, the same for both arms: the timed step count, but no
+    fewer than 128 (the longest of the reference's own workloads, bench/bench.py:18-22)."""
+    return max(2, min(max(steps, 128), context - max(len(p) for p in prompts)))
+
+
 def timed_generate(engine, prompts, n_new):
     """One whole ``generate`` call on the host's clock: (seconds, seconds to the first token)."""
     import torch
@@ -234,7 +240,6 @@ def run_reference(args) -> int:
     cfg = Qwen3Config.from_dict(raw)
     batch = args.batch or work["batch"]
     steps = args.steps or work["steps"]
-    n_new = max(steps, 2)
     folder = tempfile.mkdtemp(prefix="ek_ref_model_")
     try:
         write_random_model(folder, cfg, seed=0, device="cuda")
@@ -243,6 +248,7 @@ def run_reference(args) -> int:
         import engine as reference_engine               # the reference's engine/engine.py, unmodified
         eng = reference_engine.Engine(folder)
         prompts = make_prompts(args.shape, batch, cfg.vocab_size)
+        n_new = e2e_new_tokens(steps, work["context"], prompts)
         list(eng.generate(prompts, n_new))                # its graphs for this shape are captured here
         for _ in range(max(0, min(args.warmup, 3) - 1)):
             list(eng.generate(prompts, n_new))
@@ -425,7 +431,7 @@ def main(argv=None) -> int:
 
     # ---- end to end through Engine.generate --------------------------------------------
     host_prompts = make_prompts(args.shape, batch, V)
-    n_new = max(2, min(max(steps, 128), context - max(len(p) for p in host_prompts)))
+    n_new = e2e_new_tokens(steps, context, host_prompts)
     e2e = end_to_end(engine, host_prompts, n_new, batch)
 
     prompt_desc = work["prompt"]

@@ -144,6 +144,7 @@ gemm_tc_bf16_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
 
   bool ok = (smem_u32(smem) & 1023u) == 0;       // never seen otherwise; the swizzled tiles would be wrong
   if (!ok && tid == 0) atomicCAS(prm.status, 0, 9);
+  int fillings = 0;                              // stage fillings this thread has asked TMA for
   if (tid == 0) {
     // ---------------------------------------------------------------- TMA producer
     int p_row0, p_row1 = 0;
@@ -190,6 +191,7 @@ gemm_tc_bf16_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
     for (int it = 0; it < first; ++it) {
       if (SWAP) load_q(it); else load_p(it);
     }
+    fillings = first;
     for (int it = first; it < n_iter && ok; ++it) {
       const int s = it % STAGES;
       const uint32_t phase = (it / STAGES) & 1;
@@ -198,6 +200,7 @@ gemm_tc_bf16_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
       mbar_expect_tx(full0 + 8 * s, kBytesP + kBytesQ);
       load_p(it);
       load_q(it);
+      fillings = it + 1;
     }
   } else if (tid == 32 || (TWO && tid == 64)) {
     // ---------------------------------------------------------------- MMA issuer(s)
@@ -604,9 +607,32 @@ gemm_tc_bf16_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
     for (int i = 0; i < 2000; ++i) __nanosleep(1000);
   }
 
+  // No copy of this block may still be on its way when the block exits: a bulk copy that lands in
+  // the shared memory of a block that is gone, and completes a barrier there, is a fault (an
+  // "unspecified launch failure"), not a wrong number.  Normally every filling has been waited for
+  // by the thread that multiplied it.  The producer makes sure of it all the same - an issuing
+  // thread that mistook a barrier's phase once ran through its stages without waiting, and the
+  // block left with copies in flight.  The last filling of each stage is complete by now, so
+  // each of these waits is a single look at its barrier.
+  if (tid == 0) {
+    for (int it = fillings > STAGES ? fillings - STAGES : 0; it < fillings; ++it)
+      if (!mbar_wait(full0 + 8 * (it % STAGES), (it / STAGES) & 1, prm.status, 4)) break;
+  }
   tc_fence_before();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tmem_base, kTmemCols);
+}
+
+// A bounded wait that must run out: one thread waits for a barrier that nothing completes, for
+// `limit` rounds, records `code` in `status` and returns.  For the host-side test of the path from
+// a timed-out wait to the error the caller sees; the kernel ends by itself after `limit` rounds.
+__global__ void wait_that_runs_out_kernel(int* status, int code, unsigned limit) {
+  __shared__ uint64_t bar;
+  if (threadIdx.x == 0) {
+    mbar_init(smem_u32(&bar), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    mbar_wait_limit(smem_u32(&bar), 0, status, code, limit);
+  }
 }
 
 // Stages of the swapped form's operand ring: what two blocks an SM can hold, and an even number.
@@ -773,4 +799,12 @@ EK_EXPORT int ek_gemm_tc_qkv_rope(void* out, const void* x, const void* w, int M
   return gemm_tc_run(extras, out, x, w, M, N, K, ldx, ldw, ldo, TC_EPI_BF16, 1, k_split, 1, nullptr,
                      nullptr, 0, 0, ss_in, ss_tiles, norm_size, eps, nullptr, 0, nullptr, nullptr, status,
                      stream);
+}
+
+// Launches one thread that waits `limit` rounds (at most 1,000,000, a fraction of a second) for a
+// barrier that never completes and then records `code` in `status`.  Nothing else is touched.
+EK_EXPORT int ek_tc_wait_that_runs_out(int* status, int code, unsigned limit, cudaStream_t stream) {
+  if (!status || code <= 0 || limit == 0 || limit > 1000000u) return EK_ERR_ARG;
+  ek::wait_that_runs_out_kernel<<<1, 32, 0, stream>>>(status, code, limit);
+  EK_RETURN_LAUNCH_STATUS();
 }

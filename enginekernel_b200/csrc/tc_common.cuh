@@ -34,14 +34,19 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
       : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
   return ok;
 }
-// Bounded wait: false (and a code in *status) if the phase never completes.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status, int code) {
-  for (uint32_t i = 0; i < kWaitLimit; ++i) {
+// Bounded wait: false (and a code in *status) if the phase does not complete within `limit`
+// rounds.  The first code recorded wins; the host reads and clears the word.
+__device__ __forceinline__ bool mbar_wait_limit(uint32_t bar, uint32_t parity, int* status, int code,
+                                                uint32_t limit) {
+  for (uint32_t i = 0; i < limit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
     if (i > 64) __nanosleep(128);
   }
   atomicCAS(status, 0, code);
   return false;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status, int code) {
+  return mbar_wait_limit(bar, parity, status, code, kWaitLimit);
 }
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1,
                                             uint32_t bar) {

@@ -435,11 +435,25 @@ def tc_status(device):
 
 
 def check_tc_status(device):
-    """Synchronises; raises if a tensor-core GEMM gave up waiting (1 producer, 2 MMA, 3 epilogue)."""
+    """Synchronises; raises if a kernel gave up a bounded barrier wait since the last check (products:
+    1 producer, 2 MMA, 3 epilogue, 4 copies before exit; decode attention 41, 42; others by their
+    kernel) and clears the word, so that the next check speaks of later launches only."""
     code = int(tc_status(device).item())
     if code:
         tc_status(device).zero_()
-        raise KernelError(f"gemm_tc_bf16: a barrier wait timed out (code {code}); results are invalid")
+        raise KernelError(f"a bounded barrier wait ran out in a tensor-core kernel (code {code}); "
+                          "results since the last check are invalid")
+
+
+_wait_that_runs_out = Function("gemm_tc_bf16", "ek_tc_wait_that_runs_out", [_P, c_int, ctypes.c_uint, _P])
+
+
+def wait_that_runs_out(device, code=77, limit=4096):
+    """Launch one thread that waits ``limit`` rounds for a barrier nothing completes, gives up and
+    records ``code`` in the device's status word - what a kernel does when a wait of its own runs
+    out.  The kernel ends by itself; :func:`check_tc_status` then raises."""
+    with torch.cuda.device(device):
+        _wait_that_runs_out(_ptr(tc_status(device)), int(code), int(limit), _stream())
 
 
 TC_MAX_CLUSTER = 8          # blocks of a thread-block cluster (the portable limit)

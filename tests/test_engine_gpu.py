@@ -336,3 +336,42 @@ def test_unusual_head_shapes(tmp_path, shape):
     want = plain.logits(model, ids)
     assert helpers.rel_err(helpers.whole(eng, ids), want) <= helpers.TOL["bfloat16"]
     assert helpers.rel_err(helpers.tail_one_by_one(eng, ids, 20), want) <= helpers.TOL["bfloat16"]
+
+
+def poison_free_pages(engine, value=1e4):
+    """Fill every cache page no sequence holds with large finite keys and values of both signs:
+    enough to move any logit whose attention read them, too small to overflow."""
+    for g in engine.cache.groups:
+        if g.page_group is None:
+            continue
+        free = torch.tensor(sorted(g.page_group.pool._free), dtype=torch.long, device=g.pages.device)
+        if free.numel() == 0:
+            continue
+        shape = g.pages[:, :, free].shape
+        signs = torch.where(torch.arange(shape[-1], device=g.pages.device) % 2 == 0, value, -value)
+        g.pages[:, :, free] = signs.to(g.pages.dtype).expand(shape)
+    torch.cuda.synchronize()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("tag", ["B", "D", "E"])
+def test_stale_pages_change_nothing(folders, plains, tag, dtype):
+    """Pages handed to a sequence hold whatever their last owner (or nobody) left there.  With every
+    free page filled with +-1e4 before each batch, logits and generated tokens are what they were:
+    no kernel reads a key beyond a sequence's length, not even with a weight of almost nothing."""
+    from enginekernel_b200 import Engine
+    cfg = CONFIGS[tag][0]
+    eng = Engine(folders[tag], dtype, max_tokens=12 * 64, max_batch=3)
+    seqs = tiny_models.random_prompts(cfg, [70, 5, 130], seed=71)
+    wants = [plain.logits(plains[tag], s) for s in seqs]
+    for round_ in range(2):                       # the second round reuses pages the first one wrote
+        poison_free_pages(eng)
+        got = helpers.batch_then_steps(eng, seqs, [64, 3, 120])
+        for s, g, w in zip(seqs, got, wants):
+            err = helpers.rel_err(g, w)
+            assert err <= helpers.TOL[dtype], (tag, dtype, round_, len(s), err)
+    prompts = [s[:n] for s, n in zip(seqs, (63, 5, 100))]
+    poison_free_pages(eng)
+    for p, toks in zip(prompts, eng.generate_all(prompts, 20)):
+        check_tokens_against_plain(plains[tag], p, toks, dtype)
+    assert eng.cache.free_tokens() == eng.cache.num_pages * 64

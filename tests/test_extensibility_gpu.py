@@ -47,18 +47,31 @@ def define_toy():
             self.w = tensors[self.spec.weights["w"]].float()
 
         def forward(self, x, ctx, entry, writes_cache=True):
-            out = torch.empty(ctx.n_tokens, self.hidden, dtype=torch.float32, device=x.device)
-            cu = ctx.host_cu_seqlens
-            for b in range(ctx.n_seqs):
-                lo, hi = cu[b], cu[b + 1]
-                state = entry.state[ctx.host_token_slot[lo]]
-                xs = x[lo:hi].float()
-                sums = state[:self.hidden] + torch.cumsum(xs, 0)
-                counts = state[self.hidden] + torch.arange(1, hi - lo + 1, device=x.device)
-                out[lo:hi] = (sums / counts[:, None]) @ self.w.t()
-                if writes_cache:
-                    state[:self.hidden] = sums[-1]
-                    state[self.hidden] = counts[-1]
+            """Device tensors only (no host copy of positions or slots, nothing that waits for the
+            device), so the same code runs in steps the host lays out and inside the captured
+            decode step of ``generate``.  Rows whose position is negative belong to sequences that
+            have ended: they contribute nothing and leave the state alone."""
+            t, h = ctx.n_tokens, self.hidden
+            dev = x.device
+            pos, slots = ctx.positions[:t].long(), ctx.token_slot[:t].long()
+            active = pos >= 0
+            xs = torch.where(active[:, None], x[:t].float(), torch.zeros((), device=dev))
+            index = torch.arange(t, device=dev)
+            cu = ctx.cu_seqlens[:ctx.n_seqs + 1].long()
+            seq = torch.searchsorted(cu[1:].contiguous(), index, right=True)   # each token's sequence
+            start = cu[seq]
+            running = torch.cumsum(xs, 0)
+            before = torch.where((start > 0)[:, None], running[(start - 1).clamp(min=0)],
+                                 torch.zeros((), device=dev))
+            state = entry.state                                       # [slots, hidden + 1]
+            mine = state[slots]
+            sums = mine[:, :h] + running - before
+            counts = mine[:, h] + (index - start + 1)
+            out = (sums / counts[:, None]) @ self.w.t()
+            if writes_cache:
+                last = cu[1:] - 1                                     # the last token of each sequence
+                new = torch.cat([sums[last], counts[last, None]], dim=1)
+                state.index_copy_(0, slots[last], torch.where(active[last][:, None], new, state[slots[last]]))
             return out.to(self.dtype)
 
     @dataclasses.dataclass(frozen=True)
@@ -179,6 +192,183 @@ def test_toy_architecture_with_a_stateful_mixer(tmp_path, dtype):
     finally:
         registry.unregister_part("mixer", "running_mean")
         registry.unregister_architecture("ToyMixedForCausalLM")
+
+
+def toy_greedy(folder, prompt, n):
+    ids, out = list(prompt), []
+    for _ in range(n):
+        out.append(int(plain_logits(folder, ids)[-1].argmax()))
+        ids.append(out[-1])
+    return out
+
+
+def test_stateful_mixer_inside_the_captured_decode_step(tmp_path):
+    """The toy architecture through ``generate_all`` with the CUDA graph on: the mixer's state is
+    advanced inside the captured step by device code only, six requests go through an engine of
+    two slots in three batches (a slot's state must start from zero each time), a request with a
+    budget of 3 ends while its batch mate goes on.  Tokens against the plain toy model, 32-bit."""
+    from enginekernel_b200 import Engine, registry
+    from enginekernel_b200.weights import write_random_model
+    ToyConfig = define_toy()
+    try:
+        folder = write_random_model(str(tmp_path / "toy"), ToyConfig.from_dict(RAW), seed=4)
+        eng = Engine(folder, "float32", max_tokens=512, max_batch=2, use_graph=True)
+        g = torch.Generator().manual_seed(3)
+        prompts = [torch.randint(0, 97, (n,), generator=g).tolist() for n in (30, 4, 11, 60, 2, 17)]
+        budgets = [20, 20, 3, 20, 20, 12]
+        got = eng.generate_all(prompts, budgets)
+        want = [toy_greedy(folder, p, n) for p, n in zip(prompts, budgets)]
+        assert got == want
+        assert max(len(set(w)) for w in want) >= 4        # not one repeated token
+        assert eng.cache.book.open_slots() == []
+        # the captured step really ran (a graph exists) and the host never laid those steps out
+        assert any(st.graph is not None for st in eng.backend._states.values())
+        again = eng.generate_all(prompts[::-1], budgets[::-1])
+        assert again == want[::-1]
+    finally:
+        registry.unregister_part("mixer", "running_mean")
+        registry.unregister_architecture("ToyMixedForCausalLM")
+
+
+# -- a layer that sees all keys beside a layer that sees a window of them ----------------------
+WINDOW = 100
+WINDOW_RAW = {"architectures": ["ToyWindowForCausalLM"], "hidden_size": 72, "vocab_size": 113, "heads": 4,
+              "kv_heads": 2, "head_dim": 64, "ff_width": 96, "eps": 1e-6, "theta": 10000.0,
+              "window": WINDOW, "max_positions": 1024}
+
+
+def define_window_toy():
+    from enginekernel_b200 import registry
+    from enginekernel_b200.config.base import ModelConfig, key
+    from enginekernel_b200.parts.spec import LayerSpec, ModelSpec, PartSpec, RunSpec, TensorSpec
+
+    @dataclasses.dataclass(frozen=True)
+    class WindowConfig(ModelConfig):
+        architecture = "ToyWindowForCausalLM"
+        hidden_size: int = key("hidden_size")
+        vocab_size: int = key("vocab_size")
+        heads: int = key("heads")
+        kv_heads: int = key("kv_heads")
+        head_dim: int = key("head_dim")
+        width: int = key("ff_width")
+        eps: float = key("eps")
+        theta: float = key("theta")
+        window: int = key("window")
+        max_positions: int = key("max_positions")
+
+    def build(cfg):
+        h = cfg.hidden_size
+
+        def layer(p, window):
+            norms = {n: PartSpec("rms_norm", {"size": h, "eps": cfg.eps}, {"gain": f"{p}.{n}.gain"})
+                     for n in ("pre_mixer", "pre_feed_forward")}
+            attn = PartSpec("attention", {
+                "hidden_size": h, "num_heads": cfg.heads, "num_kv_heads": cfg.kv_heads,
+                "head_dim": cfg.head_dim, "scale": cfg.head_dim ** -0.5, "qk_norm_eps": cfg.eps,
+                "window": window,
+                "position": PartSpec("rope_neox", {"head_dim": cfg.head_dim, "theta": cfg.theta,
+                                                   "rotary_dim": cfg.head_dim})},
+                {"q": f"{p}.q", "k": f"{p}.k", "v": f"{p}.v", "o": f"{p}.o",
+                 "q_norm": f"{p}.qn", "k_norm": f"{p}.kn"})
+            ff = PartSpec("gated_mlp", {"hidden_size": h, "intermediate_size": cfg.width},
+                          {"gate": f"{p}.ff.gate", "up": f"{p}.ff.up", "down": f"{p}.ff.down"})
+            return LayerSpec(PartSpec("pre_norm"), attn, ff, norms)
+
+        return ModelSpec(
+            hidden_size=h, vocab_size=cfg.vocab_size, max_positions=cfg.max_positions,
+            embedding=TensorSpec("embed", (cfg.vocab_size, h), "embedding"),
+            layers=[layer("l0", None), layer("l1", cfg.window), layer("l2", cfg.window)],
+            schedule=[RunSpec(0, 0), RunSpec(1, 1), RunSpec(2, 2)],
+            final_norm=PartSpec("rms_norm", {"size": h, "eps": cfg.eps}, {"gain": "final.gain"}),
+            lm_head=TensorSpec("head", (cfg.vocab_size, h)))
+
+    registry.register_architecture("ToyWindowForCausalLM", WindowConfig, build, replace=True)
+    return WindowConfig
+
+
+def window_plain_logits(folder, ids, window=WINDOW):
+    c = WINDOW_RAW
+    w = plain.read_weights(folder, torch.float32)
+    s, nh, nkv, d, eps = len(ids), c["heads"], c["kv_heads"], c["head_dim"], c["eps"]
+    cos, sin = plain.rope_tables(s, d, c["theta"], torch.float32)
+    r = w["embed"][torch.tensor(ids)]
+    for p, win in (("l0", None), ("l1", window), ("l2", window)):
+        a = plain.rms_norm(r, w[f"{p}.pre_mixer.gain"], eps)
+        q = plain.qk_norm_rope((a @ w[f"{p}.q"].t()).view(s, nh, d), w[f"{p}.qn"], cos, sin, eps)
+        k = plain.qk_norm_rope((a @ w[f"{p}.k"].t()).view(s, nkv, d), w[f"{p}.kn"], cos, sin, eps)
+        v = (a @ w[f"{p}.v"].t()).view(s, nkv, d)
+        r = r + plain.causal_gqa_attention(q, k, v, d ** -0.5, window=win) @ w[f"{p}.o"].t()
+        m = plain.rms_norm(r, w[f"{p}.pre_feed_forward.gain"], eps)
+        g, u = m @ w[f"{p}.ff.gate"].t(), m @ w[f"{p}.ff.up"].t()
+        r = r + (torch.nn.functional.silu(g) * u) @ w[f"{p}.ff.down"].t()
+    return plain.rms_norm(r, w["final.gain"], eps) @ w["head"].t()
+
+
+def sharpen_window_toy(folder):
+    """Make single keys matter: larger query and key matrices in the windowed layers, so that the
+    softmax is peaked and the key at the window's edge carries visible weight."""
+    import os
+    from safetensors.torch import load_file, save_file
+    path = os.path.join(folder, "model.safetensors")
+    tensors = load_file(path)
+    for name in ("l1.q", "l1.k", "l2.q", "l2.k", "l1.v", "l2.v", "l1.o", "l2.o"):
+        tensors[name] = (tensors[name].float() * 6).to(tensors[name].dtype)
+    save_file(tensors, path)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_windowed_layers_through_the_engine(tmp_path, dtype):
+    """A model with one layer that sees every key and two that see the last 100: two page groups.
+    A 300-token prompt runs in pieces of at most 128 tokens (pages behind the window are given
+    back after each piece), then 80 tokens one by one across page boundaries.  The plain model
+    with a window of 99 or 101 is far outside the tolerance, so an edge that is off by one shows."""
+    from enginekernel_b200 import Engine, registry
+    from enginekernel_b200.weights import write_random_model
+    WindowConfig = define_window_toy()
+    try:
+        folder = write_random_model(str(tmp_path / "window"), WindowConfig.from_dict(WINDOW_RAW), seed=6)
+        sharpen_window_toy(folder)
+        g = torch.Generator().manual_seed(2)
+        ids = torch.randint(0, 113, (380,), generator=g).tolist()
+        want = window_plain_logits(folder, ids)
+        for wrong in (WINDOW - 1, WINDOW + 1):
+            assert helpers.rel_err(window_plain_logits(folder, ids, wrong)[WINDOW:], want[WINDOW:]) > \
+                20 * helpers.TOL["float32"], "the test would not see a window edge that is off by one"
+        eng = Engine(folder, dtype, max_tokens=1024, max_batch=2, max_step_tokens=128)
+        groups = {g_.spec.window: g_.page_group for g_ in eng.cache.groups}
+        assert set(groups) == {None, WINDOW}
+        total = eng.cache.num_pages
+        slot = eng.open_sequence()
+        rows = [eng.step([(slot, ids[:300], list(range(300)))]).cpu()]
+        assert len(groups[None].pages_of(slot)) == 5                  # 300 tokens
+        assert len(groups[WINDOW].pages_of(slot)) <= 3                # keys 201.. : pages 3 and 4
+        for tok in ids[300:]:
+            rows.append(eng.step([(slot, [tok], [0])]).cpu())
+            assert len(groups[WINDOW].pages_of(slot)) <= 3
+        got = torch.cat(rows, 0)
+        assert helpers.rel_err(got, want) <= helpers.TOL[dtype]
+        assert len(groups[None].pages_of(slot)) == 6
+        eng.close_sequence(slot)
+        assert groups[None].pool.available() == total and groups[WINDOW].pool.available() == total
+        # a second sequence in the same slot, in a batch with a short one, from a reused slot
+        got = helpers.batch_then_steps(eng, [ids[:250], ids[5:40]], [200, 30])
+        assert helpers.rel_err(got[0], want[:250]) <= helpers.TOL[dtype]
+        # generation through the captured decode step crosses the window's edge while decoding;
+        # sampled with a fixed seed so that the tokens vary (greedy repeats one token here)
+        if dtype == "float32":
+            prompts = [ids[:90], ids[100:130]]
+            tokens = eng.generate_all(prompts, 40, temperature=1.0, seed=99)
+            for b, (p, t) in enumerate(zip(prompts, tokens)):
+                seq, ref = list(p), []
+                for step in range(40):
+                    row = window_plain_logits(folder, seq)[-1]
+                    ref.append(plain.sample_token(row, 1.0, 0, 99, b, step))
+                    seq.append(ref[-1])
+                assert t == ref
+                assert len(set(ref)) >= 8
+        assert groups[None].pool.available() == total and groups[WINDOW].pool.available() == total
+    finally:
+        registry.unregister_architecture("ToyWindowForCausalLM")
 
 
 # -- a feed-forward with routing and another position encoding ---------------------------------

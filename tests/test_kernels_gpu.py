@@ -739,3 +739,37 @@ def test_decode_advance():
     assert tokens.tolist() == [11, 2, 3, 4, 15]
     assert draws.tolist() == [1, 1, 0, 1, 1] and remaining.tolist() == [4, 4, 5, 0, 4]
     assert (out[[0, 1, 3]] == -7).all()
+
+
+def test_a_wait_that_runs_out_reaches_the_caller_and_is_cleared():
+    """Every barrier wait in the tensor-core kernels gives up after a limit, records a code in the
+    device's status word and lets its kernel end.  Here a one-thread kernel waits 4,096 rounds for a
+    barrier that nothing completes (it ends by itself, in well under a millisecond): the check
+    raises with the code, the word is clear afterwards, and a product right after it is correct."""
+    k = K()
+    from enginekernel_b200.ops.lib import KernelError
+    k.check_tc_status(DEV)                                   # clean before
+    t0 = torch.cuda.Event(enable_timing=True)
+    t1 = torch.cuda.Event(enable_timing=True)
+    t0.record()
+    k.wait_that_runs_out(DEV, code=77, limit=4096)
+    t1.record()
+    torch.cuda.synchronize()
+    assert t0.elapsed_time(t1) < 100.0                       # milliseconds: the wait was bounded
+    with pytest.raises(KernelError, match="code 77"):
+        k.check_tc_status(DEV)
+    k.check_tc_status(DEV)                                   # cleared by the check that raised
+    assert int(k.tc_status(DEV).item()) == 0
+    x = rnd(8, 256, dtype=torch.bfloat16, seed=1)
+    w = rnd(384, 256, dtype=torch.bfloat16, seed=2, scale=0.05)
+    out = torch.empty(8, 384, device=DEV)
+    k.gemm_tc_bf16(out, x, w, k.EPI_F32, swap=True)
+    assert rel(out, x.double() @ w.double().t()) <= 1e-5
+    k.check_tc_status(DEV)
+    # the first code wins until the word is read
+    k.wait_that_runs_out(DEV, code=5, limit=256)
+    k.wait_that_runs_out(DEV, code=6, limit=256)
+    with pytest.raises(KernelError, match="code 5"):
+        k.check_tc_status(DEV)
+    with pytest.raises(KernelError):
+        k.wait_that_runs_out(DEV, code=1, limit=10**9)       # refused: only short waits
