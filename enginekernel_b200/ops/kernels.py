@@ -527,7 +527,7 @@ def gemm_tc_bf16(out, x, w, epilogue=EPI_BF16, n_rows=None, swap=None, k_split=N
         ld_stream = stream.stride(0)
     if lib.recording():
         moved = 2 * (n * k + m * k) + m * n_out * out.element_size() + (8 * m * n if residual is not None else 0)
-        lib.annotate(bytes=moved, flops=2 * m * n * k)
+        lib.annotate(bytes=moved, flops=2 * m * n * k, label=f"{n}x{k}")
     _gemm_tc(_ptr(out), _ptr(x), _ptr(w), m, n, k, x.stride(0), w.stride(0), out.stride(0),
              epilogue, 1 if swap else 0, k_split, 1 if cluster else 0, _ptr(partials), _ptr(tickets),
              _SPLIT_PARTIAL_FLOATS, _SPLIT_TICKETS, _ptr(ss_in), ss_tiles, int(size), float(eps),

@@ -83,11 +83,13 @@ def recording() -> bool:
     return _recorder is not None
 
 
-def annotate(bytes: int = 0, flops: int = 0) -> None:
+def annotate(bytes: int = 0, flops: int = 0, label: str = "") -> None:
     """Called by a launcher just before its launch while a record is active: the bytes the
-    launch has to read and write and the floating-point operations it has to do."""
+    launch has to read and write and the floating-point operations it has to do.  ``label``
+    (a shape, say) tells launches of one entry point apart in the record: the entry is named
+    ``entry_point[label]``."""
     global _pending_cost
-    _pending_cost = {"bytes": int(bytes), "flops": int(flops)}
+    _pending_cost = {"bytes": int(bytes), "flops": int(flops), "label": label}
 
 
 def record_library_call(name: str, again, bytes: int = 0, flops: int = 0) -> None:
@@ -166,5 +168,6 @@ class Function:
         if _recorder is not None:
             global _pending_cost
             head, cost, _pending_cost = args[:-1], _pending_cost or {}, None
-            _recorder.append((self.name, lambda stream: check(fn(*head, stream), self.name), cost))
+            name = f"{self.name}[{cost['label']}]" if cost.get("label") else self.name
+            _recorder.append((name, lambda stream: check(fn(*head, stream), self.name), cost))
         check(fn(*args), self.name)

@@ -95,6 +95,6 @@ def _library_product(x, w, out):
     if lib.recording():
         m, k = x.shape
         n = w.shape[0]
-        lib.record_library_call("library_matmul", lambda: torch.matmul(x, w.t(), out=out),
+        lib.record_library_call(f"library_matmul[{n}x{k}]", lambda: torch.matmul(x, w.t(), out=out),
                                 bytes=x.element_size() * (m * k + n * k) + out.element_size() * m * n,
                                 flops=2 * m * n * k)
