@@ -105,11 +105,17 @@ __global__ void qk_norm_rope_kv_kernel(T* qkv, int row_stride,
 }
 
 
-// Wide form for 16-bit rows whose head size is 64, 128 or 256 and fully rotated: a lane holds
-// 8 neighbouring dimensions (one 16-byte load), D/8 lanes a head, and a block takes every
-// head of one token, all loads issued before the first use.  The rotation partner (j + D/2)
-// sits in the lane D/16 further on, so it comes by shuffle; nothing goes through shared
-// memory.  Same arithmetic and rounding as the kernel above.
+// Wide form for 16-bit rows whose head size is 64, 128 or 256 and fully rotated: a block takes
+// every head of one token, D/8 lanes a head.  A lane holds 4 neighbouring dimensions of the head's
+// first half and the 4 they turn with in the second half (two 8-byte loads, each a full 128-byte
+// line over the head's lanes), so the rotation needs no exchange between lanes; only the sum of
+// squares of the head norm goes through shuffles.  The kernel is bound by instruction issue, not by
+// memory (with the arithmetic taken out it runs at the copy bandwidth), so the gain and the angle
+// are multiplied once per token and lane - four products per pair of dimensions, for q and for k -
+// and a head costs a lane two multiply-adds and one multiply per value:
+//     y_lo = rstd * (x_lo * (g_lo cos) - x_hi * (g_hi sin)),   y_hi = rstd * (x_hi * (g_hi cos) + x_lo * (g_lo sin))
+// which is gain * x * rstd rotated, with the 32-bit products taken in another order.  All loads of
+// a token are issued before the first use.
 constexpr int kWideThreads = 256;
 constexpr int kWidePasses = 4;
 
@@ -130,37 +136,59 @@ qk_norm_rope_kv_wide_kernel(bf16* qkv, int row_stride, const float* __restrict__
   const int n_heads = write_kv ? n_q_heads + 2 * n_kv : n_q_heads;
   const int lih = threadIdx.x % LPH;               // lane in head
   const int head0 = threadIdx.x / LPH;
+  const int d0 = 4 * lih;                          // this lane's dimensions: d0.. and half + d0..
   bf16* row = qkv + (size_t)t * row_stride;
   // the first heads are asked for before the position is known: one round trip less in the chain
-  uint4 raw[kWidePasses];
+  uint2 raw_lo[kWidePasses], raw_hi[kWidePasses];
   auto load_heads = [&](int base) {
 #pragma unroll
     for (int p = 0; p < kWidePasses; ++p) {
       const int head = base + p * HPP + head0;
-      if (head < n_heads) raw[p] = *reinterpret_cast<const uint4*>(row + (size_t)head * D + lih * 8);
+      if (head < n_heads) {
+        raw_lo[p] = *reinterpret_cast<const uint2*>(row + (size_t)head * D + d0);
+        raw_hi[p] = *reinterpret_cast<const uint2*>(row + (size_t)head * D + half + d0);
+      }
     }
   };
   load_heads(0);
   const int pos = positions[t];
   if (pos < 0) return;
-  const bool low = lih < LPH / 2;
   // the lanes of this head within the warp: heads of one warp may take different branches
   const unsigned seg = LPH == 32 ? 0xffffffffu
                                  : ((1u << (LPH & 31)) - 1u) << ((threadIdx.x & 31) / LPH * LPH);
-  const int j0 = (lih % (LPH / 2)) * 8;            // angle index of this lane's first pair
   size_t page_base = 0;
   if (write_kv) {
     const int page = cache.block_table[(size_t)token_slot[t] * cache.table_stride + pos / EK_PAGE];
     page_base = page_offset(cache, page, 0, pos);
   }
-  float cs[8], sn[8];
+  // gain x angle, once per token and lane, for the query heads (most of a token's heads); a key
+  // head takes its own four products when it comes
+  float cs[4], sn[4];
   {
-    const float4* c4 = reinterpret_cast<const float4*>(cos_tab + (size_t)pos * half + j0);
-    const float4* s4 = reinterpret_cast<const float4*>(sin_tab + (size_t)pos * half + j0);
-    const float4 a = c4[0], b = c4[1], c = s4[0], d = s4[1];
-    cs[0] = a.x; cs[1] = a.y; cs[2] = a.z; cs[3] = a.w; cs[4] = b.x; cs[5] = b.y; cs[6] = b.z; cs[7] = b.w;
-    sn[0] = c.x; sn[1] = c.y; sn[2] = c.z; sn[3] = c.w; sn[4] = d.x; sn[5] = d.y; sn[6] = d.z; sn[7] = d.w;
+    const float4 c4 = *reinterpret_cast<const float4*>(cos_tab + (size_t)pos * half + d0);
+    const float4 s4 = *reinterpret_cast<const float4*>(sin_tab + (size_t)pos * half + d0);
+    cs[0] = c4.x; cs[1] = c4.y; cs[2] = c4.z; cs[3] = c4.w;
+    sn[0] = s4.x; sn[1] = s4.y; sn[2] = s4.z; sn[3] = s4.w;
   }
+  auto products = [&](const float* gain, float* lc, float* hs, float* hc, float* ls) {
+    float gl[4] = {1.f, 1.f, 1.f, 1.f}, gh[4] = {1.f, 1.f, 1.f, 1.f};
+    if (gain) {
+      const float4 l4 = *reinterpret_cast<const float4*>(gain + d0);
+      const float4 h4 = *reinterpret_cast<const float4*>(gain + half + d0);
+      gl[0] = l4.x; gl[1] = l4.y; gl[2] = l4.z; gl[3] = l4.w;
+      gh[0] = h4.x; gh[1] = h4.y; gh[2] = h4.z; gh[3] = h4.w;
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      lc[i] = gl[i] * cs[i];
+      hs[i] = gh[i] * sn[i];
+      hc[i] = gh[i] * cs[i];
+      ls[i] = gl[i] * sn[i];
+    }
+  };
+  float q_lc[4], q_hs[4], q_hc[4], q_ls[4];
+  products(q_gain, q_lc, q_hs, q_hc, q_ls);
+  const bool q_norm = q_gain != nullptr, k_norm = k_gain != nullptr;
   for (int base = 0; base < n_heads; base += HPP * kWidePasses) {
     if (base > 0) load_heads(base);
 #pragma unroll
@@ -170,52 +198,58 @@ qk_norm_rope_kv_wide_kernel(bf16* qkv, int row_stride, const float* __restrict__
       if (head >= n_heads) continue;
       const bool is_q = head < n_q_heads;
       const bool is_k = !is_q && head < n_q_heads + n_kv;
-      bf16* dst = row + (size_t)head * D + lih * 8;
+      bf16* dst = row + (size_t)head * D + d0;
       if (!is_q) {
         const int kv_head = is_k ? head - n_q_heads : head - n_q_heads - n_kv;
-        dst = (bf16*)(is_k ? cache.k : cache.v) + page_base + (size_t)kv_head * EK_PAGE * D + lih * 8;
+        dst = (bf16*)(is_k ? cache.k : cache.v) + page_base + (size_t)kv_head * EK_PAGE * D + d0;
       }
       if (!is_q && !is_k) {
-        *reinterpret_cast<uint4*>(dst) = raw[p];
+        *reinterpret_cast<uint2*>(dst) = raw_lo[p];
+        *reinterpret_cast<uint2*>(dst + half) = raw_hi[p];
         continue;
       }
-      const float* gain = is_q ? q_gain : k_gain;
-      float x[8];
+      float lo[4], hi[4];
       {
-        const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw[p]);
+        const __nv_bfloat162* l2 = reinterpret_cast<const __nv_bfloat162*>(&raw_lo[p]);
+        const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw_hi[p]);
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const float2 f = __bfloat1622float2(h2[i]);
-          x[2 * i] = f.x;
-          x[2 * i + 1] = f.y;
+        for (int i = 0; i < 2; ++i) {
+          const float2 f = __bfloat1622float2(l2[i]), g = __bfloat1622float2(h2[i]);
+          lo[2 * i] = f.x; lo[2 * i + 1] = f.y;
+          hi[2 * i] = g.x; hi[2 * i + 1] = g.y;
         }
       }
-      if (gain) {
+      float rstd = 1.f;
+      if (is_q ? q_norm : k_norm) {
         float ss = 0.f;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) ss += x[i] * x[i];
+        for (int i = 0; i < 4; ++i) ss += lo[i] * lo[i] + hi[i] * hi[i];
 #pragma unroll
         for (int o = LPH / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(seg, ss, o, LPH);
-        const float rstd = rsqrtf(ss / (float)D + eps);
-        const float4 g0 = *reinterpret_cast<const float4*>(gain + lih * 8);
-        const float4 g1 = *reinterpret_cast<const float4*>(gain + lih * 8 + 4);
-        const float g[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
-#pragma unroll
-        for (int i = 0; i < 8; ++i) x[i] = x[i] * rstd * g[i];
+        rstd = rsqrtf(ss / (float)D + eps);
       }
-      uint32_t w[4];
-      float y[8];
+      float ylo[4], yhi[4];
+      if (is_q) {
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const float partner = __shfl_xor_sync(seg, x[i], LPH / 2, LPH);
-        y[i] = low ? x[i] * cs[i] - partner * sn[i] : x[i] * cs[i] + partner * sn[i];
-      }
+        for (int i = 0; i < 4; ++i) {
+          ylo[i] = (lo[i] * q_lc[i] - hi[i] * q_hs[i]) * rstd;
+          yhi[i] = (hi[i] * q_hc[i] + lo[i] * q_ls[i]) * rstd;
+        }
+      } else {
+        float k_lc[4], k_hs[4], k_hc[4], k_ls[4];
+        products(k_gain, k_lc, k_hs, k_hc, k_ls);
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        __nv_bfloat162 h = __floats2bfloat162_rn(y[2 * i], y[2 * i + 1]);
-        w[i] = *reinterpret_cast<uint32_t*>(&h);
+        for (int i = 0; i < 4; ++i) {
+          ylo[i] = (lo[i] * k_lc[i] - hi[i] * k_hs[i]) * rstd;
+          yhi[i] = (hi[i] * k_hc[i] + lo[i] * k_ls[i]) * rstd;
+        }
       }
-      *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
+      __nv_bfloat162 l0 = __floats2bfloat162_rn(ylo[0], ylo[1]), l1 = __floats2bfloat162_rn(ylo[2], ylo[3]);
+      __nv_bfloat162 h0 = __floats2bfloat162_rn(yhi[0], yhi[1]), h1 = __floats2bfloat162_rn(yhi[2], yhi[3]);
+      *reinterpret_cast<uint2*>(dst) =
+          make_uint2(*reinterpret_cast<uint32_t*>(&l0), *reinterpret_cast<uint32_t*>(&l1));
+      *reinterpret_cast<uint2*>(dst + half) =
+          make_uint2(*reinterpret_cast<uint32_t*>(&h0), *reinterpret_cast<uint32_t*>(&h1));
     }
   }
 }
