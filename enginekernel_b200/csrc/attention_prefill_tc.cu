@@ -70,8 +70,8 @@ __device__ __forceinline__ float2 add2(float2 a, float2 b) {
 template <int D>
 __global__ void __launch_bounds__(kFaThreads, 2)
 attention_prefill_tc_kernel(bf16* __restrict__ out, const __grid_constant__ CUtensorMap map_q,
-                            const int* positions, const int* token_slot, const int* cu_seqlens,
-                            int n_seqs, const __grid_constant__ CUtensorMap map_k,
+                            const int4* __restrict__ tiles,
+                            const __grid_constant__ CUtensorMap map_k,
                             const __grid_constant__ CUtensorMap map_v, const int* block_table,
                             int table_stride, int n_kv_heads, int n_q_heads, float scale_log2,
                             int window, int tok_per_tile, int* status) {
@@ -87,37 +87,27 @@ attention_prefill_tc_kernel(bf16* __restrict__ out, const __grid_constant__ CUte
   unsigned char* v_s = k_s + kFaKStages * DB * kSub;           // V stages x DB x [64 x 64]
   uint64_t* bars = (uint64_t*)(v_s + kFaVStages * DB * kSub);
   uint32_t* tmem_slot = (uint32_t*)(bars + kFaBars);
-  int* tile_info = (int*)(tmem_slot + 1);                      // 3 ints
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int kv_head = blockIdx.x;             // heads fastest: blocks start longest key range first
   const int group = n_q_heads / n_kv_heads;
 
   pdl_launch_dependents();
+  // The tile's tokens, position and slot come from a table made once per step (sequence bounds,
+  // positions and slots were uploaded before the step's first kernel, and the table is made
+  // before its first attention kernel): one 16-byte load instead of a search through the
+  // sequences and two more dependent loads in every block of every layer.
+  const int4 tile = __ldg(&tiles[blockIdx.y]);     // first token, tokens, position of the first, slot
+  const int t_first = tile.x, n_tok = tile.y;
+  if (n_tok <= 0) return;                          // the table is padded to the grid's size
   if (tid == 128) {
     tma_prefetch_map(&map_q);
     tma_prefetch_map(&map_k);
     tma_prefetch_map(&map_v);
   }
-  // Sequence bounds, positions, slots and block tables were uploaded before the step's first
-  // kernel, so they are read without waiting for the kernel ahead.
   const uint32_t bar0 = smem_u32(bars);
   auto bar = [&](int i) { return bar0 + 8u * i; };
   if (tid == 0) {
-    int idx = blockIdx.y, found = -1, first = 0, count = 0;
-    for (int b = 0; b < n_seqs; ++b) {
-      const int n = cu_seqlens[b + 1] - cu_seqlens[b];
-      const int tiles = (n + tok_per_tile - 1) / tok_per_tile;
-      if (idx < tiles) {
-        const int tile = tiles - 1 - idx;          // long key ranges first
-        found = b;
-        first = cu_seqlens[b] + tile * tok_per_tile;
-        count = min(tok_per_tile, n - tile * tok_per_tile);
-        break;
-      }
-      idx -= tiles;
-    }
-    tile_info[0] = first; tile_info[1] = count; tile_info[2] = found;
     for (int i = 0; i < kFaBars; ++i) mbar_init(bar(i), (i == kBarPFull || i == kBarPFull + 1) ? 4 : 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -126,13 +116,12 @@ attention_prefill_tc_kernel(bf16* __restrict__ out, const __grid_constant__ CUte
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const int t_first = tile_info[0], n_tok = tile_info[1];
   const int n_rows = n_tok * group;
   const bool misplaced = (smem_u32(smem) & 1023u) != 0;   // never seen; the swizzled tiles would be wrong
-  const int pos0 = (tile_info[2] < 0 || misplaced) ? -1 : positions[t_first];
-  if (pos0 < 0) {                                  // no tile, or rows of a finished sequence: zeros
+  const int pos0 = misplaced ? -1 : tile.z;
+  if (pos0 < 0) {                                  // rows of a finished sequence: zeros
     if (misplaced && tid == 0) atomicCAS(status, 0, 19);
-    if (tile_info[2] >= 0 && !misplaced) {
+    if (!misplaced) {
       pdl_wait();                                  // the rows may still be read by a kernel ahead
       for (int i = tid; i < n_rows * D; i += kFaThreads) {
         const int r = i / D, d = i % D;
@@ -145,7 +134,7 @@ attention_prefill_tc_kernel(bf16* __restrict__ out, const __grid_constant__ CUte
     if (warp == 4) tmem_dealloc(tmem_base, kTmemCols);
     return;
   }
-  const int* table = block_table + (size_t)token_slot[t_first] * table_stride;
+  const int* table = block_table + (size_t)tile.w * table_stride;
   const int hi_tile = pos0 + n_tok - 1;
   const int lo_tile = window > 0 ? max(0, pos0 - window + 1) : 0;
   const int kt_lo = lo_tile / kFaKeys, kt_hi = hi_tile / kFaKeys;
@@ -356,9 +345,51 @@ attention_prefill_tc_kernel(bf16* __restrict__ out, const __grid_constant__ CUte
   if (warp == 4) tmem_dealloc(tmem_base, kTmemCols);
 }
 
+// The table of tiles of a prompt step: entry = (first token, tokens, position of the first token,
+// slot), `tok_per_tile` consecutive new tokens of one sequence each.  Long key ranges come first:
+// the tiles are listed by their place in their sequence, last places first, over all sequences, so
+// that the blocks that run longest start first and the short ones fill the gaps at the end.
+// Entries past the last tile have 0 tokens.  One block; sequences are walked by thread 0 of it
+// (a step has at most a few hundred).
+constexpr int kFaTileThreads = 1024;         // also the most sequences a step may bring
+
+__global__ void __launch_bounds__(kFaTileThreads)
+attention_prefill_tiles_kernel(int4* tiles, int max_tiles, const int* cu_seqlens, const int* positions,
+                               const int* token_slot, int n_seqs, int tok_per_tile) {
+  __shared__ int count_s[kFaTileThreads], start_s[kFaTileThreads], len_s[kFaTileThreads];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int tid = threadIdx.x;
+  if (tid < n_seqs) {
+    const int a = cu_seqlens[tid], n = cu_seqlens[tid + 1] - a;
+    start_s[tid] = a;
+    len_s[tid] = n;
+    count_s[tid] = (n + tok_per_tile - 1) / tok_per_tile;
+  }
+  __syncthreads();
+  int most = 0, total = 0;
+  for (int b = 0; b < n_seqs; ++b) {
+    most = max(most, count_s[b]);
+    total += count_s[b];
+  }
+  // tile r of sequence b stands behind every tile with a later place r' > r and behind the tiles
+  // with the same place of the sequences before b
+  for (int p = tid; p < most * n_seqs; p += kFaTileThreads) {
+    const int r = most - 1 - p / n_seqs, b = p % n_seqs;
+    if (r >= count_s[b]) continue;
+    int at = 0;
+    for (int c = 0; c < n_seqs; ++c) at += max(0, count_s[c] - 1 - r) + (c < b && count_s[c] > r ? 1 : 0);
+    if (at < max_tiles) {
+      const int first = start_s[b] + r * tok_per_tile;
+      tiles[at] = make_int4(first, min(tok_per_tile, len_s[b] - r * tok_per_tile), positions[first],
+                            token_slot[first]);
+    }
+  }
+  for (int i = total + tid; i < max_tiles; i += kFaTileThreads) tiles[i] = make_int4(0, 0, -1, 0);
+}
+
 template <int D>
-static int launch_fa(bf16* out, const bf16* q, int q_row_stride, const int* positions,
-                     const int* token_slot, const int* cu_seqlens, int n_seqs, int n_tokens,
+static int launch_fa(bf16* out, const bf16* q, int q_row_stride, const int4* tiles, int n_tiles, int n_tokens,
                      const void* k_pages, const void* v_pages, long long page_rows,
                      const int* block_table, int table_stride, int n_q_heads, int n_kv_heads,
                      float scale, int window, int* status, cudaStream_t stream) {
@@ -383,38 +414,49 @@ static int launch_fa(bf16* out, const bf16* q, int q_row_stride, const int* posi
     configured[device] = true;
   }
   prefer_carveout((const void*)kernel, 100);
-  const int tiles = (n_tokens + tok_per_tile - 1) / tok_per_tile + n_seqs;   // upper bound
-  if (tiles > 65535) return EK_ERR_ARG;
-  dim3 grid(n_kv_heads, tiles);
-  return (int)launch_pdl(kernel, grid, dim3(kFaThreads), smem, stream, out, mq, positions,
-                         token_slot, cu_seqlens, n_seqs, mk, mv, block_table, table_stride, n_kv_heads,
-                         n_q_heads, scale * 1.4426950408889634f, window, tok_per_tile, status);
+  if (n_tiles > 65535) return EK_ERR_ARG;
+  dim3 grid(n_kv_heads, n_tiles);
+  return (int)launch_pdl(kernel, grid, dim3(kFaThreads), smem, stream, out, mq, tiles, mk, mv, block_table,
+                         table_stride, n_kv_heads, n_q_heads, scale * 1.4426950408889634f, window,
+                         tok_per_tile, status);
 }
 
 }  // namespace ek
 
+// The table of tiles that ek_attention_prefill_tc walks, for one step's sequences: `tiles` holds
+// `max_tiles` >= ceil(n_tokens / tok_per_tile) + n_seqs entries of 4 ints; tok_per_tile is
+// 128 / (query heads per KV head).  Made once per step, used by every layer.
+EK_EXPORT int ek_attention_prefill_tiles(int* tiles, int max_tiles, const int* cu_seqlens,
+                                         const int* positions, const int* token_slot, int n_seqs,
+                                         int tok_per_tile, cudaStream_t stream) {
+  using namespace ek;
+  if (n_seqs <= 0 || max_tiles <= 0) return 0;
+  if (n_seqs > kFaTileThreads || tok_per_tile <= 0 || !tiles || ((uintptr_t)tiles & 15)) return EK_ERR_ARG;
+  return (int)launch_pdl(attention_prefill_tiles_kernel, dim3(1), dim3(kFaTileThreads), 0, stream, (int4*)tiles,
+                         max_tiles, cu_seqlens, positions, token_slot, n_seqs, tok_per_tile);
+}
+
 // head_dim 64 or 128; the group (query heads per KV head) must divide 128; q rows 16-byte
-// aligned; n_pages = number of pages in k_pages / v_pages ([pages, kv heads, 64, head_dim]).
-EK_EXPORT int ek_attention_prefill_tc(void* out, const void* q, int q_row_stride,
-                                      const int* positions, const int* token_slot,
-                                      const int* cu_seqlens, int n_seqs, int n_tokens,
+// aligned; n_pages = number of pages in k_pages / v_pages ([pages, kv heads, 64, head_dim]);
+// `tiles` / n_tiles: the table ek_attention_prefill_tiles made for this step and group size.
+EK_EXPORT int ek_attention_prefill_tc(void* out, const void* q, int q_row_stride, const int* tiles,
+                                      int n_tiles, int n_tokens,
                                       const void* k_pages, const void* v_pages, int n_pages,
                                       const int* block_table, int table_stride, int n_q_heads,
                                       int n_kv_heads, int head_dim, float scale, int window,
                                       int* status, cudaStream_t stream) {
   using namespace ek;
-  if (n_tokens <= 0 || n_seqs <= 0) return 0;
+  if (n_tokens <= 0 || n_tiles <= 0) return 0;
   if ((head_dim != 64 && head_dim != 128) || n_kv_heads <= 0 || n_q_heads % n_kv_heads ||
       kFaRows % (n_q_heads / n_kv_heads) || q_row_stride % 8 || ((uintptr_t)q & 15) || !status ||
-      !(scale > 0.f) ||
-      n_pages <= 0)
+      !(scale > 0.f) || n_pages <= 0 || !tiles || ((uintptr_t)tiles & 15))
     return EK_ERR_ARG;
   const long long page_rows = (long long)n_pages * n_kv_heads * EK_PAGE;
   if (head_dim == 64)
-    return launch_fa<64>((bf16*)out, (const bf16*)q, q_row_stride, positions, token_slot, cu_seqlens,
-                         n_seqs, n_tokens, k_pages, v_pages, page_rows, block_table, table_stride,
+    return launch_fa<64>((bf16*)out, (const bf16*)q, q_row_stride, (const int4*)tiles, n_tiles, n_tokens,
+                         k_pages, v_pages, page_rows, block_table, table_stride,
                          n_q_heads, n_kv_heads, scale, window, status, stream);
-  return launch_fa<128>((bf16*)out, (const bf16*)q, q_row_stride, positions, token_slot, cu_seqlens,
-                        n_seqs, n_tokens, k_pages, v_pages, page_rows, block_table, table_stride,
+  return launch_fa<128>((bf16*)out, (const bf16*)q, q_row_stride, (const int4*)tiles, n_tiles, n_tokens,
+                        k_pages, v_pages, page_rows, block_table, table_stride,
                         n_q_heads, n_kv_heads, scale, window, status, stream);
 }

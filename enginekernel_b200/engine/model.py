@@ -124,6 +124,8 @@ class DecoderModel:
         """Run every scheduled block; returns (stream, pending) with the last block's
         output not yet added to the stream."""
         t = ctx.n_tokens
+        for run in self.spec.schedule:                 # what mixers share between layers of this step
+            self.blocks[run.layer].mixer.begin_step(ctx)
         stream = ctx.workspace.get("stream", (t, self.spec.hidden_size), torch.float32)
         kernels.embed(stream, self.embedding, ctx.token_ids, t)
         pending = None

@@ -338,8 +338,12 @@ def attention_prefill_bf16(out, q, n_tokens, positions, token_slot, cu_seqlens, 
 
 
 _attn_prefill_tc = Function("attention_prefill_tc", "ek_attention_prefill_tc",
-                            [_P, _P, c_int, _P, _P, _P, c_int, c_int, _P, _P, c_int, _P, c_int, c_int,
+                            [_P, _P, c_int, _P, c_int, c_int, _P, _P, c_int, _P, c_int, c_int,
                              c_int, c_int, c_float, c_int, _P, _P])
+_attn_prefill_tiles = Function("attention_prefill_tc", "ek_attention_prefill_tiles",
+                               [_P, c_int, _P, _P, _P, c_int, c_int, _P])
+PREFILL_TC_ROWS = 128       # (token, query head of a group) rows a block of attention_prefill_tc owns
+PREFILL_TC_MAX_SEQS = 1024
 
 
 def attention_prefill_tc_supported(dtype, head_dim, n_q_heads, n_kv_heads):
@@ -347,11 +351,34 @@ def attention_prefill_tc_supported(dtype, head_dim, n_q_heads, n_kv_heads):
     return dtype == torch.bfloat16 and head_dim in (64, 128) and 128 % group == 0
 
 
+def attention_prefill_tiles(tiles, n_tokens, positions, token_slot, cu_seqlens, n_seqs, n_q_heads, n_kv_heads):
+    """Fill ``tiles`` (int32 [>= tiles_needed, 4]) with the table of tiles that
+    :func:`attention_prefill_tc` walks for this step's sequences and this group size: (first token,
+    tokens, position of the first, slot) per tile, long key ranges first, padded with empty tiles.
+    It is read by the attention kernels before they wait for the kernel ahead of them, so it has
+    to be made before the step's first kernel (:func:`embed`, a plain launch), not just before the
+    attention; returns the number of entries to pass on."""
+    _need_cuda(tiles, positions, token_slot, cu_seqlens)
+    tok_per_tile = PREFILL_TC_ROWS // (n_q_heads // n_kv_heads)
+    need = -(-n_tokens // tok_per_tile) + n_seqs
+    _need(tiles.dtype == torch.int32 and tiles.is_contiguous() and tiles.numel() >= 4 * need
+          and tiles.data_ptr() % 16 == 0, "attention_prefill_tiles: int32 [tiles, 4], 16-byte aligned")
+    _need(n_seqs <= PREFILL_TC_MAX_SEQS, f"attention_prefill_tc: at most {PREFILL_TC_MAX_SEQS} sequences a step")
+    _need(cu_seqlens.dtype == torch.int32 and cu_seqlens.numel() >= n_seqs + 1, "attention: cu_seqlens")
+    _attn_prefill_tiles(_ptr(tiles), need, _ptr(cu_seqlens), _ptr(positions), _ptr(token_slot), n_seqs,
+                        tok_per_tile, _stream())
+    return need
+
+
 def attention_prefill_tc(out, q, n_tokens, positions, token_slot, cu_seqlens, n_seqs, k_pages,
-                         v_pages, block_table, n_q_heads, n_kv_heads, head_dim, scale, window=None):
+                         v_pages, block_table, n_q_heads, n_kv_heads, head_dim, scale, window=None,
+                         tiles=None, n_tiles=0):
     """:func:`attention_prefill_bf16` on tcgen05 tensor cores (head sizes 64 and 128, groups
-    that divide 128): TMA-fed pages, scores and P.V in TMEM."""
-    _need_cuda(out, q, positions, token_slot, cu_seqlens, k_pages, v_pages, block_table)
+    that divide 128): TMA-fed pages, scores and P.V in TMEM.  ``tiles`` / ``n_tiles``: the table
+    :func:`attention_prefill_tiles` made for this step (made once, before the step's first
+    kernel, and used by every layer); without it the table is made here and the stream is
+    waited for, which suits a single call, not a model's step."""
+    _need_cuda(out, q, positions, token_slot, cu_seqlens, k_pages, v_pages, block_table, tiles)
     _need(attention_prefill_tc_supported(q.dtype, head_dim, n_q_heads, n_kv_heads),
           "attention_prefill_tc: bfloat16, head size 64 or 128, a group size that divides 128")
     _need(out.dtype == q.dtype == k_pages.dtype, "attention: one dtype for q, cache and out")
@@ -360,11 +387,17 @@ def attention_prefill_tc(out, q, n_tokens, positions, token_slot, cu_seqlens, n_
           "attention: dense, 16-byte aligned q rows")
     _need(k_pages.is_contiguous() and v_pages.is_contiguous() and k_pages.dim() == 4
           and k_pages.shape[1:] == (n_kv_heads, PAGE, head_dim), "attention: pages [P, NKV, 64, D]")
-    _need(cu_seqlens.dtype == torch.int32 and cu_seqlens.numel() >= n_seqs + 1, "attention: cu_seqlens")
+    if tiles is None:
+        tok_per_tile = PREFILL_TC_ROWS // (n_q_heads // n_kv_heads)
+        tiles = torch.empty((-(-n_tokens // tok_per_tile) + n_seqs, 4), dtype=torch.int32, device=q.device)
+        n_tiles = attention_prefill_tiles(tiles, n_tokens, positions, token_slot, cu_seqlens, n_seqs,
+                                          n_q_heads, n_kv_heads)
+        torch.cuda.current_stream().synchronize()
+    _need(tiles.dtype == torch.int32 and tiles.numel() >= 4 * n_tiles and tiles.data_ptr() % 16 == 0,
+          "attention_prefill_tc: the table of tiles")
     _attention_cost(q, n_tokens, positions, n_q_heads, n_kv_heads, head_dim, window, True)
-    _attn_prefill_tc(_ptr(out), _ptr(q), q.stride(0), _ptr(positions), _ptr(token_slot),
-                     _ptr(cu_seqlens), n_seqs, n_tokens, _ptr(k_pages), _ptr(v_pages),
-                     k_pages.shape[0], _ptr(block_table), block_table.stride(0), n_q_heads,
+    _attn_prefill_tc(_ptr(out), _ptr(q), q.stride(0), _ptr(tiles), n_tiles, n_tokens, _ptr(k_pages),
+                     _ptr(v_pages), k_pages.shape[0], _ptr(block_table), block_table.stride(0), n_q_heads,
                      n_kv_heads, head_dim, float(scale), int(window or 0),
                      _ptr(tc_status(q.device)), _stream())
 

@@ -63,6 +63,21 @@ class Attention(Mixer):
         if self.position is not None:
             self.position.prepare(max_positions)
 
+    def begin_step(self, ctx):
+        """The table of tiles of the tcgen05 prompt attention, once per step and group size."""
+        if ctx.is_decode or not kernels.attention_prefill_tc_supported(
+                self.dtype, self.head_dim, self.num_heads, self.num_kv_heads):
+            return
+        key = ("prefill_tc_tiles", self.num_heads // self.num_kv_heads)
+        if key in ctx.shared:
+            return
+        per_tile = kernels.PREFILL_TC_ROWS // (self.num_heads // self.num_kv_heads)
+        rows = -(-ctx.n_tokens // per_tile) + ctx.n_seqs
+        tiles = ctx.workspace.get(f"prefill_tc_tiles_{per_tile}", (rows, 4), torch.int32)
+        n = kernels.attention_prefill_tiles(tiles, ctx.n_tokens, ctx.positions, ctx.token_slot, ctx.cu_seqlens,
+                                            ctx.n_seqs, self.num_heads, self.num_kv_heads)
+        ctx.shared[key] = (tiles, n)
+
     def load(self, tensors):
         w = self.spec.weights
         self.w_qkv = torch.cat([tensors[w["q"]], tensors[w["k"]], tensors[w["v"]]], dim=0) \
@@ -123,10 +138,15 @@ class Attention(Mixer):
             if kernels.attention_prefill_tc_supported(self.dtype, self.head_dim, self.num_heads,
                                                       self.num_kv_heads):
                 prefill = kernels.attention_prefill_tc      # tcgen05: head sizes 64 and 128
+            extra = {}
+            if prefill is kernels.attention_prefill_tc:
+                made = ctx.shared.get(("prefill_tc_tiles", self.num_heads // self.num_kv_heads))
+                if made is not None:                 # (made in begin_step; a part driven alone has none)
+                    extra = dict(tiles=made[0], n_tiles=made[1])
             prefill(
                 out, qkv, t, ctx.positions, ctx.token_slot, ctx.cu_seqlens, ctx.n_seqs,
                 entry.k_pages, entry.v_pages, entry.block_table, self.num_heads, self.num_kv_heads,
-                self.head_dim, self.scale, self.window)
+                self.head_dim, self.scale, self.window, **extra)
             return
         if ctx.is_decode and t <= 65535 and kernels.attention_decode_tma_supported(
                 self.dtype, self.head_dim, self.num_heads, self.num_kv_heads):

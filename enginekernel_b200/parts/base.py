@@ -87,6 +87,9 @@ class StepContext:
     host_positions: Optional[List[int]] = None
     host_token_slot: Optional[List[int]] = None
     host_cu_seqlens: Optional[List[int]] = None
+    #: What parts make once per step and share between layers (filled in ``begin_step``), by a key
+    #: of the part's choosing.
+    shared: Dict[object, object] = dataclasses.field(default_factory=dict)
 
 
 @dataclasses.dataclass
@@ -170,6 +173,11 @@ class Mixer(Part):
 
     def prepare(self, max_positions: int) -> None:
         """Called once the longest position is known (tables and the like)."""
+
+    def begin_step(self, ctx: StepContext) -> None:
+        """Called for every scheduled mixer before the step's first kernel: the place for what
+        depends on the step's sequences but not on the layer (put it into ``ctx.shared``).
+        Kernels launched here are complete before any kernel of the step starts."""
 
     def forward(self, x, ctx: StepContext, entry, writes_cache: bool):
         raise NotImplementedError
