@@ -183,6 +183,11 @@ def e2e_new_tokens(steps, context, prompts):
     return max(2, min(max(steps, 128), context - max(len(p) for p in prompts)))
 
 
+def measure_entry(slot, prompt):
+    from enginekernel_b200.engine.runner import StepEntry
+    return StepEntry(slot, prompt[:PREFILL_TOKENS], [min(len(prompt), PREFILL_TOKENS) - 1])
+
+
 def timed_generate(engine, prompts, n_new):
     """One whole ``generate`` call on the host's clock: (seconds, seconds to the first token)."""
     import torch
@@ -306,6 +311,8 @@ def main(argv=None) -> int:
     ap.add_argument("--batch", type=int, default=0, help="sequences in the batch (default: the shape's)")
     ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 and 64")
     ap.add_argument("--skip-kernels", action="store_true", help="leave out the per-kernel tables")
+    ap.add_argument("--prefill-seqs", type=int, default=1,
+                    help="sequences of 2,048 tokens in the prompt step of the per-kernel table")
     args = ap.parse_args(argv)
 
     if args.impl == "reference":
@@ -333,7 +340,8 @@ def main(argv=None) -> int:
     with_points = args.shape == "4b" and not args.skip_points
     biggest = max(batch, 64 if with_points else 1)
     engine = Engine.from_config(cfg, seed=0, dtype="bfloat16", max_tokens=biggest * context,
-                                max_batch=biggest, max_len=context)
+                                max_batch=biggest, max_len=context,
+                                max_step_tokens=max(8192, args.prefill_seqs * PREFILL_TOKENS))
     L, H, NH, NKV, D, I, V = (cfg.num_hidden_layers, cfg.hidden_size, cfg.num_attention_heads,
                               cfg.num_key_value_heads, cfg.head_dim, cfg.intermediate_size,
                               cfg.vocab_size)
@@ -421,13 +429,16 @@ def main(argv=None) -> int:
     kernels = {}
     if main_run["kernels"] is not None:
         kernels["decode"] = main_run["kernels"]
-        slot = engine.open_sequence()
+        n_pre = max(1, min(args.prefill_seqs, biggest))
+        many = make_prompts("4b", n_pre, V, seed=1)
+        slots = [engine.open_sequence() for _ in many]
         try:
             kernels["prefill"] = measure.prefill_step_table(
-                lambda: engine.step([(slot, one, [PREFILL_TOKENS - 1])]), pk)
-            kernels["prefill"]["tokens"] = PREFILL_TOKENS
+                lambda: engine.runner.step([measure_entry(s, p) for s, p in zip(slots, many)]), pk)
+            kernels["prefill"]["tokens"] = n_pre * PREFILL_TOKENS
         finally:
-            engine.close_sequence(slot)
+            for s in slots:
+                engine.close_sequence(s)
 
     # ---- end to end through Engine.generate --------------------------------------------
     host_prompts = make_prompts(args.shape, batch, V)
