@@ -10,9 +10,11 @@
 
 namespace ek {
 
+// resid[t] = table[ids[t]] * scale (+ pos_table[positions[t]] if the model has learned positions)
 template <typename T>
 __global__ void embed_kernel(float* __restrict__ resid, const T* __restrict__ table,
-                             const int* ids, int hidden, int vocab) {
+                             const int* ids, int hidden, int vocab, float scale,
+                             const T* __restrict__ pos_table, const int* positions, int max_positions) {
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x;
@@ -20,7 +22,20 @@ __global__ void embed_kernel(float* __restrict__ resid, const T* __restrict__ ta
   id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
   const T* row = table + (size_t)id * hidden;
   float* out = resid + (size_t)t * hidden;
-  for (int i = threadIdx.x; i < hidden; i += blockDim.x) out[i] = to_f<T>(row[i]);
+  const T* prow = nullptr;
+  if (pos_table != nullptr) {
+    const int p = positions[t];                // rows of finished sequences (negative) get no position
+    if (p >= 0) prow = pos_table + (size_t)min(p, max_positions - 1) * hidden;
+  }
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x)
+    out[i] = to_f<T>(row[i]) * scale + (prow ? to_f<T>(prow[i]) : 0.f);
+}
+
+__global__ void scale_f32_kernel(float* x, size_t n, float scale) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) x[i] *= scale;
 }
 
 
@@ -237,14 +252,18 @@ using namespace ek;
 
 #define EK_INSTANTIATE(SUFFIX, T)                                                               \
   EK_EXPORT int ek_embed_##SUFFIX(float* resid, const void* table, const int* ids, int n_tokens, \
-                                  int hidden, int vocab, cudaStream_t stream) {                 \
+                                  int hidden, int vocab, float scale, const void* pos_table,    \
+                                  const int* positions, int max_positions, cudaStream_t stream) { \
     if (n_tokens <= 0) return 0;                                                                \
+    if (pos_table && (!positions || max_positions <= 0)) return EK_ERR_ARG;                     \
     /* A plain launch, on purpose: the first kernel of a step starts only when everything   */ \
     /* before it on the stream has finished and is visible.  The kernels behind it may then */ \
     /* read per-step state (positions, slots) before their own griddepcontrol.wait even     */ \
     /* when the step before was not a graph launch of its own (eager decode).               */ \
     embed_kernel<T><<<dim3(n_tokens), dim3(256), 0, stream>>>(resid, (const T*)table, ids,     \
-                                                               hidden, vocab);                  \
+                                                               hidden, vocab, scale,            \
+                                                               (const T*)pos_table, positions,  \
+                                                               max_positions);                  \
     EK_RETURN_LAUNCH_STATUS();                                                                  \
   }                                                                                             \
   EK_EXPORT int ek_rmsnorm_##SUFFIX(void* y, float* resid, const void* add, const float* gain,  \
@@ -266,3 +285,10 @@ using namespace ek;
 
 EK_INSTANTIATE(f32, float)
 EK_INSTANTIATE(bf16, ek::bf16)
+
+// x[i] *= scale for n 32-bit values (logits of a model with a logit multiplier)
+EK_EXPORT int ek_scale_f32(float* x, long long n, float scale, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  return (int)ek::launch_pdl(ek::scale_f32_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, x,
+                             (size_t)n, scale);
+}

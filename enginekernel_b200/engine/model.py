@@ -32,6 +32,8 @@ def expected_tensors(spec: ModelSpec) -> Dict[str, TensorSpec]:
     out: Dict[str, TensorSpec] = {spec.embedding.name: spec.embedding}
     if spec.lm_head.optional_alias is None:
         out[spec.lm_head.name] = spec.lm_head
+    if spec.position_table is not None:
+        out[spec.position_table.name] = spec.position_table
     for ts in _part_tensors("norm", spec.final_norm):
         out[ts.name] = ts
     for layer in spec.layers:
@@ -66,7 +68,7 @@ class DecoderModel:
             norms = {n: lookup_part("norm", s.kind)(s, dtype, device) for n, s in layer.norms.items()}
             self.blocks.append(block_cls(layer.block, dtype, device, mixer, ff, norms))
         self.final_norm = lookup_part("norm", spec.final_norm.kind)(spec.final_norm, dtype, device)
-        self.embedding = self.lm_head = None
+        self.embedding = self.lm_head = self.position_table = None
         self._prepared_for = 0
 
     # -- weights ---------------------------------------------------------------
@@ -78,6 +80,8 @@ class DecoderModel:
             self.lm_head = self.embedding            # tied (engine/ek_model.py:134)
         else:
             self.lm_head = tensors[s.lm_head.name].to(self.dtype).contiguous()
+        if s.position_table is not None:
+            self.position_table = tensors[s.position_table.name].to(self.dtype).contiguous()
         self.final_norm.load(tensors)
         for block in self.blocks:
             block.mixer.load(tensors)
@@ -127,7 +131,8 @@ class DecoderModel:
         for run in self.spec.schedule:                 # what mixers share between layers of this step
             self.blocks[run.layer].mixer.begin_step(ctx)
         stream = ctx.workspace.get("stream", (t, self.spec.hidden_size), torch.float32)
-        kernels.embed(stream, self.embedding, ctx.token_ids, t)
+        kernels.embed(stream, self.embedding, ctx.token_ids, t, scale=self.spec.embedding_multiplier,
+                      pos_table=self.position_table, positions=ctx.positions)
         pending = None
         schedule = self.spec.schedule
         for i, run in enumerate(schedule):
@@ -150,7 +155,10 @@ class DecoderModel:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.device)
         h = self.final_norm.forward(stream, ctx, add=pending, rows=rows, n_rows=n_rows,
                                     write_back=False)
-        return linear(h, self.lm_head, ctx, "logits", n_rows=n_rows, out_dtype=torch.float32)
+        out = linear(h, self.lm_head, ctx, "logits", n_rows=n_rows, out_dtype=torch.float32)
+        if self.spec.logit_multiplier != 1.0:
+            kernels.scale_(out, self.spec.logit_multiplier)
+        return out
 
     def forward(self, ctx: StepContext, cache, rows, n_rows: int):
         stream, pending = self.hidden(ctx, cache)

@@ -88,23 +88,43 @@ def _per_dtype(module, name, argtypes):
 
 
 # ------------------------------------------------------------------ elementwise
-_embed = _per_dtype("elementwise", "ek_embed", [_P, _P, _P, c_int, c_int, c_int, _P])
+_embed = _per_dtype("elementwise", "ek_embed", [_P, _P, _P, c_int, c_int, c_int, c_float, _P, _P, c_int, _P])
+_scale_f32 = Function("elementwise", "ek_scale_f32", [_P, c_longlong, c_float, _P])
 _rmsnorm = _per_dtype("elementwise", "ek_rmsnorm",
                       [_P, _P, _P, _P, _P, c_float, c_int, c_int, c_int, _P])
 _add_residual = _per_dtype("elementwise", "ek_add_residual", [_P, _P, c_longlong, _P])
 _silu_mul = _per_dtype("elementwise", "ek_silu_mul", [_P, _P, c_int, c_int, _P])
 
 
-def embed(resid, table, ids, n_tokens):
-    """resid[t, :] = table[ids[t], :] as 32-bit, for the first ``n_tokens`` ids."""
-    _need_cuda(resid, table, ids)
+def embed(resid, table, ids, n_tokens, scale=1.0, pos_table=None, positions=None):
+    """resid[t, :] = table[ids[t], :] * scale as 32-bit, for the first ``n_tokens`` ids; with
+    ``pos_table`` [positions, hidden] also + pos_table[positions[t], :] (rows whose position is
+    negative get none).  A plain launch: the first kernel of a step."""
+    _need_cuda(resid, table, ids, pos_table, positions)
     _need(resid.dtype == torch.float32 and ids.dtype == torch.int32, "embed: resid f32, ids int32")
     _need(table.is_contiguous() and resid.is_contiguous(), "embed: contiguous tensors")
     vocab, hidden = table.shape
     _need(resid.shape[-1] == hidden and resid.shape[0] >= n_tokens, "embed: resid shape")
+    max_positions = 0
+    if pos_table is not None:
+        _need(pos_table.dtype == table.dtype and pos_table.is_contiguous() and pos_table.shape[-1] == hidden
+              and positions is not None and positions.dtype == torch.int32,
+              "embed: position table [positions, hidden] in the embedding's dtype, int32 positions")
+        max_positions = pos_table.shape[0]
     if lib.recording():
-        lib.annotate(bytes=n_tokens * hidden * (table.element_size() + 4))
-    _embed[table.dtype](_ptr(resid), _ptr(table), _ptr(ids), n_tokens, hidden, vocab, _stream())
+        lib.annotate(bytes=n_tokens * hidden * (table.element_size() * (2 if pos_table is not None else 1) + 4))
+    _embed[table.dtype](_ptr(resid), _ptr(table), _ptr(ids), n_tokens, hidden, vocab, float(scale),
+                        _ptr(pos_table), _ptr(positions), max_positions, _stream())
+
+
+def scale_(x, scale, n=None):
+    """x *= scale in place (32-bit values; the first ``n`` of them)."""
+    _need_cuda(x)
+    _need(x.dtype == torch.float32 and x.is_contiguous(), "scale_: contiguous 32-bit values")
+    count = x.numel() if n is None else n
+    if lib.recording():
+        lib.annotate(bytes=8 * count)
+    _scale_f32(_ptr(x), count, float(scale), _stream())
 
 
 def rmsnorm(y, resid, gain, eps, add=None, rows=None, n_rows=None, write_back=True):

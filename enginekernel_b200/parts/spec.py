@@ -72,6 +72,12 @@ class ModelSpec:
     schedule: List[RunSpec]
     final_norm: PartSpec
     lm_head: TensorSpec            # optional_alias set when tied to the embedding
+    #: what goes into the residual stream for token t: embedding[id] * embedding_multiplier, plus
+    #: position_table[position] if the model has learned absolute positions ([max_positions, hidden])
+    embedding_multiplier: float = 1.0
+    position_table: Optional[TensorSpec] = None
+    #: logits = logit_multiplier * (final norm . lm_head^T)
+    logit_multiplier: float = 1.0
 
     def num_cache_entries(self) -> int:
         used = [r.cache for r in self.schedule if r.cache is not None]
@@ -80,6 +86,10 @@ class ModelSpec:
     def check(self) -> None:
         if not self.schedule:
             raise ValueError("a model needs at least one scheduled layer")
+        if self.position_table is not None and tuple(self.position_table.shape) != (self.max_positions,
+                                                                                     self.hidden_size):
+            raise ValueError(f"the position table must be [{self.max_positions}, {self.hidden_size}], "
+                             f"not {tuple(self.position_table.shape)}")
         written = set()
         for i, run in enumerate(self.schedule):
             if not 0 <= run.layer < len(self.layers):

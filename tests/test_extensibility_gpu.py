@@ -552,6 +552,112 @@ def test_toy_routed_feed_forward_and_another_position_encoding(tmp_path, dtype):
         registry.unregister_architecture("ToyRoutedForCausalLM")
 
 
+# -- learned absolute positions, an embedding multiplier, a logit multiplier --------------------
+LEARNED_RAW = {"architectures": ["ToyLearnedForCausalLM"], "hidden_size": 56, "vocab_size": 101, "heads": 2,
+               "kv_heads": 1, "head_dim": 32, "ff_width": 72, "eps": 1e-5, "embedding_multiplier": 3.0,
+               "logit_multiplier": 0.25, "max_positions": 200}
+
+
+def define_learned_toy():
+    from enginekernel_b200 import registry
+    from enginekernel_b200.config.base import ModelConfig, key
+    from enginekernel_b200.parts.spec import LayerSpec, ModelSpec, PartSpec, RunSpec, TensorSpec
+
+    @dataclasses.dataclass(frozen=True)
+    class LearnedConfig(ModelConfig):
+        architecture = "ToyLearnedForCausalLM"
+        hidden_size: int = key("hidden_size")
+        vocab_size: int = key("vocab_size")
+        heads: int = key("heads")
+        kv_heads: int = key("kv_heads")
+        head_dim: int = key("head_dim")
+        width: int = key("ff_width")
+        eps: float = key("eps")
+        embedding_multiplier: float = key("embedding_multiplier")
+        logit_multiplier: float = key("logit_multiplier")
+        max_positions: int = key("max_positions")
+
+    def build(cfg):
+        h = cfg.hidden_size
+
+        def layer(p):
+            norms = {n: PartSpec("rms_norm", {"size": h, "eps": cfg.eps}, {"gain": f"{p}.{n}.gain"})
+                     for n in ("pre_mixer", "pre_feed_forward")}
+            attn = PartSpec("attention", {                      # no rotation: positions are learned
+                "hidden_size": h, "num_heads": cfg.heads, "num_kv_heads": cfg.kv_heads,
+                "head_dim": cfg.head_dim, "scale": cfg.head_dim ** -0.5, "qk_norm_eps": None,
+                "window": None, "position": None},
+                {"q": f"{p}.q", "k": f"{p}.k", "v": f"{p}.v", "o": f"{p}.o"})
+            ff = PartSpec("gated_mlp", {"hidden_size": h, "intermediate_size": cfg.width},
+                          {"gate": f"{p}.ff.gate", "up": f"{p}.ff.up", "down": f"{p}.ff.down"})
+            return LayerSpec(PartSpec("pre_norm"), attn, ff, norms)
+
+        return ModelSpec(
+            hidden_size=h, vocab_size=cfg.vocab_size, max_positions=cfg.max_positions,
+            embedding=TensorSpec("embed", (cfg.vocab_size, h), "embedding"),
+            layers=[layer("l0"), layer("l1")], schedule=[RunSpec(0, 0), RunSpec(1, 1)],
+            final_norm=PartSpec("rms_norm", {"size": h, "eps": cfg.eps}, {"gain": "final.gain"}),
+            lm_head=TensorSpec("head", (cfg.vocab_size, h)),
+            embedding_multiplier=cfg.embedding_multiplier,
+            position_table=TensorSpec("positions", (cfg.max_positions, h), "embedding"),
+            logit_multiplier=cfg.logit_multiplier)
+
+    registry.register_architecture("ToyLearnedForCausalLM", LearnedConfig, build, replace=True)
+    return LearnedConfig
+
+
+def learned_plain_logits(folder, ids):
+    c = LEARNED_RAW
+    w = plain.read_weights(folder, torch.float32)
+    s, nh, nkv, d, eps = len(ids), c["heads"], c["kv_heads"], c["head_dim"], c["eps"]
+    r = w["embed"][torch.tensor(ids)] * c["embedding_multiplier"] + w["positions"][:s]
+    for p in ("l0", "l1"):
+        a = plain.rms_norm(r, w[f"{p}.pre_mixer.gain"], eps)
+        q = (a @ w[f"{p}.q"].t()).view(s, nh, d)
+        k = (a @ w[f"{p}.k"].t()).view(s, nkv, d)
+        v = (a @ w[f"{p}.v"].t()).view(s, nkv, d)
+        r = r + plain.causal_gqa_attention(q, k, v, d ** -0.5) @ w[f"{p}.o"].t()
+        m = plain.rms_norm(r, w[f"{p}.pre_feed_forward.gain"], eps)
+        g, u = m @ w[f"{p}.ff.gate"].t(), m @ w[f"{p}.ff.up"].t()
+        r = r + (torch.nn.functional.silu(g) * u) @ w[f"{p}.ff.down"].t()
+    return c["logit_multiplier"] * (plain.rms_norm(r, w["final.gain"], eps) @ w["head"].t())
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_learned_positions_and_multipliers_at_the_model_level(tmp_path, dtype):
+    """What stands around the blocks is data too: an architecture with learned absolute positions
+    (no rotation in its attention), an embedding multiplier and a logit multiplier, registered from
+    here.  The positions matter: the same tokens shifted by one position give other logits."""
+    from enginekernel_b200 import Engine, registry
+    from enginekernel_b200.weights import write_random_model
+    LearnedConfig = define_learned_toy()
+    try:
+        folder = write_random_model(str(tmp_path / "learned"), LearnedConfig.from_dict(LEARNED_RAW), seed=12)
+        eng = Engine(folder, dtype, max_tokens=1024, max_batch=4)
+        g = torch.Generator().manual_seed(5)
+        seqs = [torch.randint(0, 101, (n,), generator=g).tolist() for n in (90, 3, 41)]
+        wants = [learned_plain_logits(folder, s) for s in seqs]
+        shifted = learned_plain_logits(folder, [seqs[0][0]] + seqs[0])[1:]
+        assert helpers.rel_err(shifted, wants[0]) > 5 * helpers.TOL["bfloat16"], "the positions do not matter"
+        tol = helpers.TOL[dtype]
+        for s, w in zip(seqs, wants):
+            assert helpers.rel_err(helpers.whole(eng, s), w) <= tol
+            assert helpers.rel_err(helpers.tail_one_by_one(eng, s, 32), w) <= tol
+        got = helpers.batch_then_steps(eng, seqs, [60, 2, 41])
+        for gl, w in zip(got, wants):
+            assert helpers.rel_err(gl, w) <= tol
+        if dtype == "float32":                     # through the captured decode step
+            tokens = eng.generate_all([s[:20] for s in seqs[::2]], 16, temperature=1.0, seed=3)
+            for b, (p, t) in enumerate(zip([s[:20] for s in seqs[::2]], tokens)):
+                seq, ref = list(p), []
+                for step in range(16):
+                    ref.append(plain.sample_token(learned_plain_logits(folder, seq)[-1], 1.0, 0, 3, b, step))
+                    seq.append(ref[-1])
+                assert t == ref
+    finally:
+        registry.unregister_architecture("ToyLearnedForCausalLM")
+
+
 def test_unknown_kinds_are_named():
     from enginekernel_b200 import registry
     with pytest.raises(registry.RegistryError, match="attention"):
