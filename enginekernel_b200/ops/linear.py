@@ -41,8 +41,11 @@ def linear(x, w, ctx, name: str, n_rows=None, out_dtype=None, defer=None):
     """``x`` [M, K] (dense rows), ``w`` [N, K] -> [M, N] from the step's workspace.
 
     ``x`` may be a :class:`~enginekernel_b200.parts.base.DeferredNorm` (the product scales its
-    rows).  ``defer=(stream, norm)``: if this step's products can carry it, the result is added to
-    ``stream`` here and a DeferredNorm for ``norm`` is returned instead of the result."""
+    rows).  ``defer=(stream, norm)``: the caller will add the result to ``stream`` and apply
+    ``norm`` next, and this product may do part of that: with few rows the result is added to
+    ``stream`` here and a DeferredNorm for ``norm`` is returned; with many rows (bfloat16) the
+    library product adds its 32-bit result to ``stream`` and None is returned (nothing left to add:
+    the norm is called without ``add``).  Otherwise the plain result comes back."""
     from ..parts.base import DeferredNorm
     row_scale = None
     if isinstance(x, DeferredNorm):
@@ -61,6 +64,15 @@ def linear(x, w, ctx, name: str, n_rows=None, out_dtype=None, defer=None):
             kernels.gemm_tc_bf16(scaled, x, w, kernels.EPI_BF16, n_rows=m, swap=True,
                                  row_scale=row_scale, residual=(stream, gain, ss))
             return DeferredNorm(scaled, ss, tiles, n, float(eps))
+    if (defer is not None and row_scale is None and out_dtype is None and w.dtype == torch.bfloat16
+            and m > SMALL_ROWS):
+        # many rows (a prompt): the library product adds its 32-bit result to the stream itself
+        # (bfloat16 operands, 32-bit C and D), so the norm that follows only reads the stream
+        stream = defer[0]
+        if stream.dtype == torch.float32 and stream.shape[-1] == n and stream.is_contiguous() \
+                and stream.shape[0] >= m:
+            _library_product_add(stream[:m], x[:m], w)
+            return None
     if row_scale is not None and not (w.dtype == torch.bfloat16 and m <= SMALL_ROWS and tc_takes(x, w)):
         raise kernels.KernelError("a deferred norm reached a product that cannot scale its rows")
     if w.dtype == torch.float32:
@@ -86,6 +98,18 @@ def linear(x, w, ctx, name: str, n_rows=None, out_dtype=None, defer=None):
     else:
         _library_product(x[:m], w, out)
     return out
+
+
+def _library_product_add(stream, x, w):
+    """stream += x . w^T by the library, accumulated and added in 32-bit (no rounding of the
+    product to 16 bits on its way into the residual stream)."""
+    torch.addmm(stream, x, w.t(), out_dtype=torch.float32, out=stream)
+    if lib.recording():
+        m, k = x.shape
+        n = w.shape[0]
+        lib.record_library_call(f"library_addmm[{n}x{k}]",
+                                lambda: torch.addmm(stream, x, w.t(), out_dtype=torch.float32, out=stream),
+                                bytes=x.element_size() * (m * k + n * k) + 8 * m * n, flops=2 * m * n * k)
 
 
 def _library_product(x, w, out):

@@ -17,7 +17,8 @@ reference folds it into ``add_rms_norm``, engine/ek_model.py:291-296, 326-334).
 
 A norm may be *deferred*: a part that is told which norm follows it (``defer=(stream, norm)``)
 may add its output to the stream itself and return a :class:`DeferredNorm` instead of a
-tensor, and a part may be given a :class:`DeferredNorm` instead of normalised activations.
+tensor (or None, if it only did the add: the norm is then called with nothing to add), and a
+part may be given a :class:`DeferredNorm` instead of normalised activations.
 Both are optional: a part says so with ``defers_norm`` / ``takes_deferred_norm`` and a norm
 with ``deferrable()``; everything else goes through the norm's own ``forward``.
 """
