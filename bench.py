@@ -326,6 +326,7 @@ def main(argv=None) -> int:
     from enginekernel_b200 import Engine, SamplingParams, measure
     from enginekernel_b200.config import Qwen3Config
     from enginekernel_b200.ops.lib import loaded_libraries
+    from enginekernel_b200.engine.runner import DEFAULT_MAX_STEP_TOKENS
 
     _, _, work = SHAPES[args.shape]
     raw = shape_config(args.shape)
@@ -341,7 +342,7 @@ def main(argv=None) -> int:
     biggest = max(batch, 64 if with_points else 1)
     engine = Engine.from_config(cfg, seed=0, dtype="bfloat16", max_tokens=biggest * context,
                                 max_batch=biggest, max_len=context,
-                                max_step_tokens=max(8192, args.prefill_seqs * PREFILL_TOKENS))
+                                max_step_tokens=max(DEFAULT_MAX_STEP_TOKENS, args.prefill_seqs * PREFILL_TOKENS))
     L, H, NH, NKV, D, I, V = (cfg.num_hidden_layers, cfg.hidden_size, cfg.num_attention_heads,
                               cfg.num_key_value_heads, cfg.head_dim, cfg.intermediate_size,
                               cfg.vocab_size)

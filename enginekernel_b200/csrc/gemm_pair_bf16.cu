@@ -1,0 +1,524 @@
+// out = x . w^T for many rows (prompts) on pairs of SMs: tcgen05.mma.cta_group::2 with a
+// 256 x 256 tile a pair.  x [M, K] and w [N, K] are bfloat16 and K-major.
+//
+// Two blocks form a cluster and share one MMA: each stages HALF of both operands (128 rows of x,
+// 128 rows of w, 64 values of K a stage, by TMA with the 128-byte swizzle), the first block's
+// thread issues the MMAs for both, and each block's tensor memory receives the 128 rows of the
+// tile that it staged, 256 columns wide.  Against one block a tile this halves what an SM has to
+// fetch per multiply-add (32 KB instead of 48 KB for 128 x 256 x 64), which is what limits a
+// tcgen05 product whose operands come from L2.
+//
+// The kernel is persistent: the pairs that fit the GPU walk the list of tiles (groups of 8 row
+// tiles, so that the pairs running together share operands in L2).  Roles in a block:
+//   warps 0..7       epilogue: two threads a row (TMEM lane) of the block's half tile, one for
+//                    each half of the tile's columns (warps w and w + 4 reach the same lanes)
+//   warp 8, 1 thread TMA producer of this block's operand halves (ring of kPairStages stages); the
+//                    copies of both blocks complete on the FIRST block's barrier
+//   warp 9, 1 thread (first block only) MMA issuer; frees a stage in both blocks and hands a
+//                    finished accumulator to both blocks' epilogues by tcgen05.commit to both
+// Two accumulators of 256 columns fill the tensor memory, so the epilogue of a tile runs under the
+// MMAs of the next.  Epilogues: bfloat16 result; 32-bit result ADDED to a residual stream;
+// SwiGLU (the first block stages 128 gate rows and the second the matching 128 up rows, so the
+// tile's columns j and 128 + j are one output's gate and up); and for the q/k/v product of an
+// attention layer with heads of 128 the per-head RMSNorm of q and k, the rotation by the token's
+// position and the write of k and v into the paged cache (a tile is two whole heads of 256 tokens
+// and a thread holds one token's row of both, so norm and rotation need no exchange; same
+// arithmetic as qk_norm_rope_kv_wide_kernel, on the 32-bit sums, with one rounding).
+//
+// Every barrier wait is bounded; a wait that runs out records a code in `status`, the block stops
+// taking tiles, and both blocks of the pair still meet at the end before the tensor memory is
+// freed.  The reference calls cuBLAS for these products (engine/ek_model.py:203-209, 298, 311).
+#include "tc_common.cuh"
+
+namespace ek {
+
+enum { PAIR_EPI_BF16 = 0, PAIR_EPI_ADD_F32 = 1, PAIR_EPI_SWIGLU = 2, PAIR_EPI_QKV_ROPE = 3 };
+
+constexpr int kPairRows = 128;                 // rows of x and of w that ONE block stages
+constexpr int kPairTile = 256;                 // the pair's tile: 256 rows of x by 256 rows of w
+constexpr int kPairStages = 6;
+constexpr int kPairThreads = 320;
+constexpr int kPairEpilogueWarps = 8;
+constexpr int kPairGroup = 8;                  // row tiles walked together
+constexpr uint32_t kPairHalfBytes = kPairRows * kTcBK * 2;          // one operand half of a stage
+constexpr uint32_t kPairStageBytes = 2 * kPairHalfBytes;            // x half + w half
+constexpr uint32_t kPairTxBytes = 2 * kPairStageBytes;              // both blocks' copies
+constexpr size_t kPairSmem = (size_t)kPairStages * kPairStageBytes + (2 * kPairStages + 4) * 8 + 16;
+
+struct PairParams {
+  void* out;          // bfloat16 [M, N] (or [M, N / 2] with SwiGLU), or the 32-bit stream [M, N]
+  int ldo;
+  int M, N;           // rows of x; rows of w (both halves together with SwiGLU)
+  int k_blocks;
+  int tiles_m, tiles_n, n_pairs;
+  int swiglu_half;    // row of w where the up half starts
+  int* status;
+  // PAIR_EPI_QKV_ROPE: out is the q/k/v buffer [M, (NQ + 2 NKV) * 128], of which only q is written
+  const int* positions;     // [M]; a negative position: the row is skipped
+  const int* slots;         // [M]
+  const float* q_gain;      // [128] or null
+  const float* k_gain;
+  const float* cos_tab;     // [positions][64]
+  const float* sin_tab;
+  PagedKV cache;
+  int n_q_heads;
+  int write_kv;
+  float qk_eps;
+};
+
+// 16 values, rounded to bfloat16, to 32 bytes at `dst` (16-byte aligned).
+__device__ __forceinline__ void store_bf16x16(bf16* dst, const float* v) {
+#pragma unroll
+  for (int j = 0; j < 16; j += 8) {
+    uint32_t w[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      __nv_bfloat162 h = __floats2bfloat162_rn(v[j + 2 * e], v[j + 2 * e + 1]);
+      w[e] = *reinterpret_cast<uint32_t*>(&h);
+    }
+    *reinterpret_cast<uint4*>(dst + j) = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+}
+
+// bfloat16 x bfloat16 -> float, both K-major, M = 256 over the pair, N = 256.
+__host__ __device__ constexpr uint32_t pair_idesc() {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kPairTile >> 3) << 17) | ((uint32_t)(kPairTile >> 4) << 24);
+}
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// The address of the same shared-memory place in block `rank` of the cluster.
+__device__ __forceinline__ uint32_t map_to_rank(uint32_t own, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(own), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// A tile of this block's shared memory whose bytes complete on a barrier that may stand in the
+// other block of the pair.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int c0, int c1,
+                                                 uint32_t bar_cluster_addr) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar_cluster_addr) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t dst_smem, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem),
+               "r"(cols) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+// All MMAs issued so far by this thread: when they are done, one arrival on the barrier at this
+// place in BOTH blocks of the pair.
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+      ::"r"(bar), "h"((uint16_t)3) : "memory");
+}
+__device__ __forceinline__ void tc_mma_pair(uint32_t d_tmem, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                            uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n\t}"
+      ::"r"(d_tmem), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+}
+
+// The i-th tile of the list: row tiles in groups of kPairGroup, inside a group the row tile runs
+// fastest, so that pairs working side by side share rows of x and of w.
+__device__ __forceinline__ void pair_tile(const PairParams& prm, int t, int& tile_m, int& tile_n) {
+  const int per_group = kPairGroup * prm.tiles_n;
+  const int g = t / per_group, r = t - g * per_group;
+  const int rows = min(kPairGroup, prm.tiles_m - g * kPairGroup);
+  tile_n = r / rows;
+  tile_m = g * kPairGroup + (r - tile_n * rows);
+}
+
+template <int EPI>
+__global__ void __launch_bounds__(kPairThreads, 1)
+gemm_pair_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+                      const PairParams prm) {
+  extern __shared__ __align__(1024) unsigned char smem[];
+  uint64_t* bars = (uint64_t*)(smem + (size_t)kPairStages * kPairStageBytes);
+  // full[S] (used in the first block), empty[S], acc_full[2], acc_empty[2] (used in the first block)
+  const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + kPairStages),
+                 acc_full0 = smem_u32(bars + 2 * kPairStages), acc_empty0 = smem_u32(bars + 2 * kPairStages + 2);
+  uint32_t* tmem_slot = (uint32_t*)(bars + 2 * kPairStages + 4);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const uint32_t rank = cluster_rank();
+  const int pair = blockIdx.x >> 1;
+  const int n_tiles = prm.tiles_m * prm.tiles_n;
+
+  if (tid == 0) {
+    tma_prefetch_map(&map_x);
+    tma_prefetch_map(&map_w);
+    for (int s = 0; s < kPairStages; ++s) {
+      mbar_init(full0 + 8 * s, 1);
+      mbar_init(empty0 + 8 * s, 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(acc_full0 + 8 * b, 1);
+      mbar_init(acc_empty0 + 8 * b, 2 * kPairEpilogueWarps);   // a lane of each epilogue warp of both blocks
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == kPairEpilogueWarps) tmem_alloc_pair(smem_u32(tmem_slot), 512);
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync();                              // the other block's barriers exist before anything reaches them
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  pdl_launch_dependents();
+  pdl_wait();
+
+  bool ok = (smem_u32(smem) & 1023u) == 0;
+  if (!ok && tid == 0) atomicCAS(prm.status, 0, 49);
+
+  if (tid == 32 * kPairEpilogueWarps) {
+    // ------------------------------------------------------------------ TMA producer
+    const uint32_t full_first = map_to_rank(full0, 0);       // the first block's barriers
+    int c = 0;                                                // stage fillings so far
+    for (int t = pair; t < n_tiles && ok; t += prm.n_pairs) {
+      int tile_m, tile_n;
+      pair_tile(prm, t, tile_m, tile_n);
+      const int x_row = tile_m * kPairTile + (int)rank * kPairRows;
+      const int w_row = EPI == PAIR_EPI_SWIGLU ? (int)rank * prm.swiglu_half + tile_n * kPairRows
+                                               : tile_n * kPairTile + (int)rank * kPairRows;
+      for (int kb = 0; kb < prm.k_blocks; ++kb, ++c) {
+        const int s = c % kPairStages;
+        if (c >= kPairStages) {
+          ok = mbar_wait(empty0 + 8 * s, ((c / kPairStages) & 1) ^ 1, prm.status, 41);
+          if (!ok) break;
+        }
+        if (rank == 0) mbar_expect_tx(full0 + 8 * s, kPairTxBytes);
+        const uint32_t dst = smem_u32(smem + (size_t)s * kPairStageBytes);
+        tma_load_2d_pair(dst, &map_x, kb * kTcBK, x_row, full_first + 8 * s);
+        tma_load_2d_pair(dst + kPairHalfBytes, &map_w, kb * kTcBK, w_row, full_first + 8 * s);
+      }
+    }
+  } else if (tid == 32 * (kPairEpilogueWarps + 1) && rank == 0) {
+    // ------------------------------------------------------------------ MMA issuer (first block)
+    constexpr uint32_t idesc = pair_idesc();
+    int c = 0, i = 0;                          // stages consumed, tiles done
+    for (int t = pair; t < n_tiles && ok; t += prm.n_pairs, ++i) {
+      const int buf = i & 1;
+      if (i >= 2) {                            // the epilogues of tile i - 2 have read this accumulator
+        ok = mbar_wait(acc_empty0 + 8 * buf, ((i >> 1) & 1) ^ 1, prm.status, 42);
+        if (!ok) break;
+        tc_fence_after();
+      }
+      const uint32_t acc = tmem_base + (uint32_t)(buf * kPairTile);
+      for (int kb = 0; kb < prm.k_blocks; ++kb, ++c) {
+        const int s = c % kPairStages;
+        ok = mbar_wait(full0 + 8 * s, (c / kPairStages) & 1, prm.status, 43);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t base = smem_u32(smem + (size_t)s * kPairStageBytes);
+        const uint64_t da = smem_desc_k_sw128(base), db = smem_desc_k_sw128(base + kPairHalfBytes);
+#pragma unroll
+        for (int k = 0; k < kTcBK / 16; ++k)
+          tc_mma_pair(acc, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, (kb || k) ? 1u : 0u);
+        tc_commit_pair(empty0 + 8 * s);        // the stage is free in both blocks once these are done
+      }
+      if (!ok) break;
+      tc_commit_pair(acc_full0 + 8 * buf);     // the tile's accumulator is complete in both blocks
+    }
+  } else if (warp < kPairEpilogueWarps) {
+    // ------------------------------------------------------------------ epilogue
+    const uint32_t acc_empty_first = map_to_rank(acc_empty0, 0);
+    const int quarter = warp & 3, side = warp >> 2;       // lanes 32 quarter ..., columns' half
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+    int i = 0;
+    for (int t = pair; t < n_tiles && ok; t += prm.n_pairs, ++i) {
+      int tile_m, tile_n;
+      pair_tile(prm, t, tile_m, tile_n);
+      const int buf = i & 1;
+      ok = mbar_wait(acc_full0 + 8 * buf, (i >> 1) & 1, prm.status, 44);
+      if (!ok) break;
+      tc_fence_after();
+      const int m = tile_m * kPairTile + (int)rank * kPairRows + quarter * 32 + lane;
+      const uint32_t acc = lane_addr + (uint32_t)(buf * kPairTile);
+      if (EPI == PAIR_EPI_SWIGLU) {
+        const int n0 = tile_n * kPairRows;     // outputs of this tile: n0 .. n0 + 127
+        bf16* o = (bf16*)prm.out + (size_t)m * prm.ldo + n0;
+#pragma unroll 1
+        for (int c0 = side * (kPairRows / 2); c0 < (side + 1) * (kPairRows / 2); c0 += 32) {
+          float g[32], u[32];
+          tmem_ld32_nowait(acc + c0, g);
+          tmem_ld32_nowait(acc + kPairRows + c0, u);
+          tmem_ld_wait();
+          if (m < prm.M) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              uint32_t w[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const float a = g[j + 2 * e], b = g[j + 2 * e + 1];
+                __nv_bfloat162 h = __floats2bfloat162_rn(__fdividef(a, 1.f + __expf(-a)) * u[j + 2 * e],
+                                                         __fdividef(b, 1.f + __expf(-b)) * u[j + 2 * e + 1]);
+                w[e] = *reinterpret_cast<uint32_t*>(&h);
+              }
+              const int n = n0 + c0 + j;
+              if (n + 8 <= prm.swiglu_half) {
+                *reinterpret_cast<uint4*>(o + c0 + j) = make_uint4(w[0], w[1], w[2], w[3]);
+              } else {
+                const bf16* h = reinterpret_cast<const bf16*>(w);
+                for (int e = 0; e < 8; ++e)
+                  if (n + e < prm.swiglu_half) o[c0 + j + e] = h[e];
+              }
+            }
+          }
+        }
+      } else if (EPI == PAIR_EPI_QKV_ROPE) {
+        // the tile holds two heads of this thread's token: columns 0..127 (warps 0..3 take that one)
+        // and 128..255 (warps 4..7); the head is the same for a whole warp, so the branches below
+        // do not split a warp around tcgen05.ld
+        const int n_kv = prm.cache.heads, nq = prm.n_q_heads;
+        const int head = 2 * tile_n + side;
+        const bool is_q = head < nq, is_k = !is_q && head < nq + n_kv, is_v = !is_q && !is_k && head < nq + 2 * n_kv;
+        const int pos = m < prm.M ? prm.positions[m] : -1;
+        const uint32_t hacc = acc + (uint32_t)(side * 128);
+        bf16* dst = nullptr;
+        if (is_q) {
+          dst = (bf16*)prm.out + (size_t)m * prm.ldo + (size_t)head * 128;
+        } else if ((is_k || is_v) && prm.write_kv && pos >= 0) {
+          const int page = prm.cache.block_table[(size_t)prm.slots[m] * prm.cache.table_stride + pos / EK_PAGE];
+          const int kv_head = is_k ? head - nq : head - nq - n_kv;
+          dst = (bf16*)(is_k ? prm.cache.k : prm.cache.v) + page_offset(prm.cache, page, kv_head, pos);
+        }
+        const bool store = pos >= 0 && dst != nullptr;
+        if (is_v && prm.write_kv) {               // values: rounded and stored
+#pragma unroll 1
+          for (int c0 = 0; c0 < 128; c0 += 32) {
+            float v[32];
+            tmem_ld32_nowait(hacc + c0, v);
+            tmem_ld_wait();
+            if (store) {
+              store_bf16x16(dst + c0, v);
+              store_bf16x16(dst + c0 + 16, v + 16);
+            }
+          }
+        } else if (is_q || (is_k && prm.write_kv)) {
+          const float* gain = is_q ? prm.q_gain : prm.k_gain;
+          float rstd = 1.f;
+          if (gain) {
+            float ss[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 1
+            for (int c0 = 0; c0 < 128; c0 += 32) {
+              float v[32];
+              tmem_ld32_nowait(hacc + c0, v);
+              tmem_ld_wait();
+#pragma unroll
+              for (int e = 0; e < 32; ++e) ss[e & 3] = fmaf(v[e], v[e], ss[e & 3]);
+            }
+            rstd = rsqrtf(((ss[0] + ss[1]) + (ss[2] + ss[3])) * (1.f / 128.f) + prm.qk_eps);
+          }
+          const float* cs = prm.cos_tab + (size_t)max(pos, 0) * 64;
+          const float* sn = prm.sin_tab + (size_t)max(pos, 0) * 64;
+#pragma unroll 1
+          for (int c0 = 0; c0 < 64; c0 += 16) {
+            // gain * cos and gain * sin of these 16 pairs first: their loads fly while TMEM is read
+            float glc[16], gls[16], ghc[16], ghs[16];
+#pragma unroll
+            for (int e = 0; e < 16; e += 4) {
+              const float4 c4 = *reinterpret_cast<const float4*>(cs + c0 + e);
+              const float4 s4 = *reinterpret_cast<const float4*>(sn + c0 + e);
+              float4 gl = make_float4(1.f, 1.f, 1.f, 1.f), gh = gl;
+              if (gain) {
+                gl = *reinterpret_cast<const float4*>(gain + c0 + e);
+                gh = *reinterpret_cast<const float4*>(gain + 64 + c0 + e);
+              }
+              glc[e] = gl.x * c4.x; glc[e + 1] = gl.y * c4.y; glc[e + 2] = gl.z * c4.z; glc[e + 3] = gl.w * c4.w;
+              gls[e] = gl.x * s4.x; gls[e + 1] = gl.y * s4.y; gls[e + 2] = gl.z * s4.z; gls[e + 3] = gl.w * s4.w;
+              ghc[e] = gh.x * c4.x; ghc[e + 1] = gh.y * c4.y; ghc[e + 2] = gh.z * c4.z; ghc[e + 3] = gh.w * c4.w;
+              ghs[e] = gh.x * s4.x; ghs[e + 1] = gh.y * s4.y; ghs[e + 2] = gh.z * s4.z; ghs[e + 3] = gh.w * s4.w;
+            }
+            float lo[16], hi[16];
+            tmem_ld16_nowait(hacc + c0, lo);
+            tmem_ld16_nowait(hacc + 64 + c0, hi);
+            tmem_ld_wait();
+            if (store) {
+#pragma unroll
+              for (int e = 0; e < 16; ++e) {
+                const float a = lo[e], b = hi[e];
+                lo[e] = rstd * (a * glc[e] - b * ghs[e]);
+                hi[e] = rstd * (b * ghc[e] + a * gls[e]);
+              }
+              store_bf16x16(dst + c0, lo);
+              store_bf16x16(dst + 64 + c0, hi);
+            }
+          }
+        }
+      } else {
+        const int n0 = tile_n * kPairTile;
+#pragma unroll 1
+        for (int c0 = side * (kPairTile / 2); c0 < (side + 1) * (kPairTile / 2); c0 += 32) {
+          float v[32];
+          tmem_ld32_nowait(acc + c0, v);
+          tmem_ld_wait();
+          if (m < prm.M && n0 + c0 < prm.N) {
+            if (EPI == PAIR_EPI_ADD_F32) {
+              float* o = (float*)prm.out + (size_t)m * prm.ldo + n0 + c0;
+              if (n0 + c0 + 32 <= prm.N) {
+                float4 old[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) old[j] = *reinterpret_cast<const float4*>(o + 4 * j);
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                  *reinterpret_cast<float4*>(o + 4 * j) = make_float4(old[j].x + v[4 * j], old[j].y + v[4 * j + 1],
+                                                                      old[j].z + v[4 * j + 2], old[j].w + v[4 * j + 3]);
+              } else {
+                for (int e = 0; e < 32; ++e)
+                  if (n0 + c0 + e < prm.N) o[e] += v[e];
+              }
+            } else {
+              bf16* o = (bf16*)prm.out + (size_t)m * prm.ldo + n0 + c0;
+              if (n0 + c0 + 32 <= prm.N) {
+#pragma unroll
+                for (int j = 0; j < 32; j += 8) {
+                  uint32_t w[4];
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) {
+                    __nv_bfloat162 h = __floats2bfloat162_rn(v[j + 2 * e], v[j + 2 * e + 1]);
+                    w[e] = *reinterpret_cast<uint32_t*>(&h);
+                  }
+                  *reinterpret_cast<uint4*>(o + j) = make_uint4(w[0], w[1], w[2], w[3]);
+                }
+              } else {
+                for (int e = 0; e < 32; ++e)
+                  if (n0 + c0 + e < prm.N) o[e] = __float2bfloat16_rn(v[e]);
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();                       // the accumulator has been read: the MMAs of tile i + 2 may overwrite it
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(acc_empty_first + 8 * buf);
+    }
+  }
+
+  const int failed = __syncthreads_or(ok ? 0 : 1);
+  if (failed)
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);   // let copies in flight land
+  tc_fence_before();
+  cluster_sync();                              // neither block's shared or tensor memory is in use any more
+  if (warp == kPairEpilogueWarps) tmem_dealloc_pair(tmem_base, 512);
+}
+
+template <int EPI>
+static int launch_pair(const CUtensorMap& mx, const CUtensorMap& mw, PairParams prm, cudaStream_t stream) {
+  auto kernel = gemm_pair_bf16_kernel<EPI>;
+  static int pairs_that_fit[kMaxDevices] = {};
+  int device = 0;
+  cudaError_t e = cudaGetDevice(&device);
+  if (e != cudaSuccess) return (int)e;
+  if (device < 0 || device >= kMaxDevices) return EK_ERR_ARG;
+  cudaLaunchConfig_t cfg = {};
+  cfg.blockDim = dim3(kPairThreads);
+  cfg.dynamicSmemBytes = kPairSmem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  if (pairs_that_fit[device] == 0) {
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kPairSmem);
+    if (e != cudaSuccess) return (int)e;
+    prefer_carveout((const void*)kernel, 100);
+    // how many pairs the device holds at once (not every SM need have a free neighbour)
+    cfg.gridDim = dim3(2 * (sm_count() / 2));
+    cfg.numAttrs = 1;
+    int clusters = 0;
+    e = cudaOccupancyMaxActiveClusters(&clusters, kernel, &cfg);
+    if (e != cudaSuccess) return (int)e;
+    if (clusters < 1) return EK_ERR_ARG;
+    pairs_that_fit[device] = clusters;
+  }
+  const int n_tiles = prm.tiles_m * prm.tiles_n;
+  prm.n_pairs = n_tiles < pairs_that_fit[device] ? n_tiles : pairs_that_fit[device];
+  cfg.gridDim = dim3(2 * prm.n_pairs);
+  cfg.numAttrs = 2;
+  return (int)cudaLaunchKernelEx(&cfg, kernel, mx, mw, prm);
+}
+
+}  // namespace ek
+
+// epilogue 0: out[M, N] = x . w^T in bfloat16; 1: out[M, N] (32-bit) += x . w^T; 2: out[M, N / 2] =
+// silu(x . wg^T) * (x . wu^T) in bfloat16 with w = [N / 2 gate rows; N / 2 up rows].  K, ldx, ldw
+// must be multiples of 8, ldo of 8 (4 for the 32-bit form), the pointers 16-byte aligned.
+EK_EXPORT int ek_gemm_pair_bf16(void* out, const void* x, const void* w, int M, int N, int K, int ldx, int ldw,
+                                int ldo, int epilogue, int* status, cudaStream_t stream) {
+  using namespace ek;
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0 || K % 8 || ldx % 8 || ldw % 8 || !status || epilogue < 0 || epilogue > 2 ||
+      ((uintptr_t)x & 15) || ((uintptr_t)w & 15) || ((uintptr_t)out & 15) ||
+      ldo % (epilogue == PAIR_EPI_ADD_F32 ? 4 : 8) || (epilogue == PAIR_EPI_SWIGLU && (N & 1)))
+    return EK_ERR_ARG;
+  PairParams prm{};
+  prm.out = out; prm.ldo = ldo; prm.M = M; prm.N = N; prm.status = status;
+  prm.k_blocks = (K + kTcBK - 1) / kTcBK;
+  prm.swiglu_half = N / 2;
+  prm.tiles_m = (M + kPairTile - 1) / kPairTile;
+  prm.tiles_n = epilogue == PAIR_EPI_SWIGLU ? (N / 2 + kPairRows - 1) / kPairRows : (N + kPairTile - 1) / kPairTile;
+  if ((long long)prm.tiles_m * prm.tiles_n > (1ll << 30)) return EK_ERR_ARG;
+  CUtensorMap mx, mw;
+  int rc;
+  if ((rc = tensor_map(x, M, K, ldx, kPairRows, &mx))) return rc;
+  if ((rc = tensor_map(w, N, K, ldw, kPairRows, &mw))) return rc;
+  if (epilogue == PAIR_EPI_BF16) rc = launch_pair<PAIR_EPI_BF16>(mx, mw, prm, stream);
+  else if (epilogue == PAIR_EPI_ADD_F32) rc = launch_pair<PAIR_EPI_ADD_F32>(mx, mw, prm, stream);
+  else rc = launch_pair<PAIR_EPI_SWIGLU>(mx, mw, prm, stream);
+  return rc;
+}
+
+// The q/k/v product of an attention layer whose heads are 128 wide and fully rotated, for many
+// rows: qkv = x . w^T, then per head the RMSNorm of q and k (gains may be null), the rotation by
+// cos/sin[position] ([P, 64] each), q to `out` [M, (NQ + 2 NKV) * 128] (its k and v columns are
+// not written) and, with write_kv, k and v into the pages at the token's place.  Rows whose
+// position is negative are skipped.
+EK_EXPORT int ek_gemm_pair_qkv_rope(void* out, const void* x, const void* w, int M, int K, int ldx, int ldw,
+                                    int ldo, const float* q_gain, const float* k_gain, float qk_eps,
+                                    const float* cos_tab, const float* sin_tab, const int* positions,
+                                    const int* token_slot, void* k_pages, void* v_pages,
+                                    const int* block_table, int table_stride, int n_q_heads, int n_kv_heads,
+                                    int write_kv, int* status, cudaStream_t stream) {
+  using namespace ek;
+  if (M <= 0) return 0;
+  if (K <= 0 || K % 8 || ldx % 8 || ldw % 8 || ldo % 8 || !status || n_q_heads <= 0 || n_kv_heads <= 0 ||
+      !positions || !token_slot || !cos_tab || !sin_tab || !k_pages || !v_pages || !block_table ||
+      ((uintptr_t)x & 15) || ((uintptr_t)w & 15) || ((uintptr_t)out & 15) || ((uintptr_t)cos_tab & 15) ||
+      ((uintptr_t)sin_tab & 15) || ((uintptr_t)q_gain & 15) || ((uintptr_t)k_gain & 15) ||
+      ((uintptr_t)k_pages & 15) || ((uintptr_t)v_pages & 15))
+    return EK_ERR_ARG;
+  PairParams prm{};
+  prm.out = out; prm.ldo = ldo; prm.M = M; prm.status = status;
+  prm.N = (n_q_heads + 2 * n_kv_heads) * 128;
+  prm.k_blocks = (K + kTcBK - 1) / kTcBK;
+  prm.tiles_m = (M + kPairTile - 1) / kPairTile;
+  prm.tiles_n = (prm.N + kPairTile - 1) / kPairTile;
+  if ((long long)prm.tiles_m * prm.tiles_n > (1ll << 30)) return EK_ERR_ARG;
+  prm.positions = positions; prm.slots = token_slot;
+  prm.q_gain = q_gain; prm.k_gain = k_gain; prm.qk_eps = qk_eps;
+  prm.cos_tab = cos_tab; prm.sin_tab = sin_tab;
+  prm.cache = PagedKV{k_pages, v_pages, block_table, table_stride, n_kv_heads, 128};
+  prm.n_q_heads = n_q_heads; prm.write_kv = write_kv;
+  CUtensorMap mx, mw;
+  int rc;
+  if ((rc = tensor_map(x, M, K, ldx, kPairRows, &mx))) return rc;
+  if ((rc = tensor_map(w, prm.N, K, ldw, kPairRows, &mw))) return rc;
+  return launch_pair<PAIR_EPI_QKV_ROPE>(mx, mw, prm, stream);
+}

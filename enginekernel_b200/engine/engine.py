@@ -21,7 +21,7 @@ from ..sampling.params import SamplingParams
 from .decode import DeviceBackend
 from .generate import GenerationLoop
 from .loading import load_model, parse_dtype, random_model
-from .runner import ModelRunner, StepEntry
+from .runner import DEFAULT_MAX_STEP_TOKENS, ModelRunner, StepEntry
 
 DEFAULT_MAX_TOKENS = 65536
 
@@ -40,12 +40,13 @@ class Engine:
     def __init__(self, model_path: Optional[str] = None, dtype="bfloat16", *,
                  max_tokens: int = DEFAULT_MAX_TOKENS, max_batch: int = 64,
                  max_len: Optional[int] = None, device="cuda:0", use_graph: bool = True,
-                 max_step_tokens: int = 8192, _model=None, _config=None):
+                 max_step_tokens: int = DEFAULT_MAX_STEP_TOKENS, _model=None, _config=None):
         """``model_path``: a folder with ``config.json`` and safetensors files.
         ``max_tokens``: tokens the cache holds over all live sequences (each sequence
         counted in whole pages of 64); ``max_batch``: most sequences in one batch;
         ``max_len``: longest sequence (default: the smaller of ``max_tokens`` and the
-        model's position limit)."""
+        model's position limit); ``max_step_tokens``: the most tokens one pass over the model
+        takes (longer prompt batches are cut into pieces)."""
         self.device = _require_cuda(device)
         torch.cuda.set_device(self.device)
         self.dtype = parse_dtype(dtype)

@@ -85,8 +85,16 @@ class PlanBuffers:
         self.dev.copy_(self.host, non_blocking=True)
 
 
+# Tokens one pass over the model takes at most; a step that brings more is cut into pieces.  Bigger
+# pieces fill the GPU better (Qwen3-0.6B shape, 64 prompts of 7,936 tokens: 1,048 ms to the first
+# token with pieces of 8,192, 986 ms with 32,768); the workspaces grow with them (about 100 KB a
+# token at the Qwen3-4B shape).
+DEFAULT_MAX_STEP_TOKENS = 32768
+
+
 class ModelRunner:
-    def __init__(self, model: DecoderModel, cache: SequenceCache, max_step_tokens: int = 8192):
+    def __init__(self, model: DecoderModel, cache: SequenceCache,
+                 max_step_tokens: int = DEFAULT_MAX_STEP_TOKENS):
         self.model, self.cache = model, cache
         self.device = model.device
         self.max_step_tokens = max_step_tokens

@@ -361,7 +361,7 @@ _attn_prefill_tc = Function("attention_prefill_tc", "ek_attention_prefill_tc",
                             [_P, _P, c_int, _P, c_int, c_int, _P, _P, c_int, _P, c_int, c_int,
                              c_int, c_int, c_float, c_int, _P, _P])
 _attn_prefill_tiles = Function("attention_prefill_tc", "ek_attention_prefill_tiles",
-                               [_P, c_int, _P, _P, _P, c_int, c_int, _P])
+                               [_P, c_int, _P, _P, _P, c_int, c_int, c_int, _P])
 PREFILL_TC_ROWS = 128       # (token, query head of a group) rows a block of attention_prefill_tc owns
 PREFILL_TC_MAX_SEQS = 1024
 
@@ -371,10 +371,27 @@ def attention_prefill_tc_supported(dtype, head_dim, n_q_heads, n_kv_heads):
     return dtype == torch.bfloat16 and head_dim in (64, 128) and 128 % group == 0
 
 
-def attention_prefill_tiles(tiles, n_tokens, positions, token_slot, cu_seqlens, n_seqs, n_q_heads, n_kv_heads):
+_l2_bytes = {}
+PREFILL_BAND_L2_SHARE = 0.5
+
+
+def prefill_band_tokens(n_kv_heads, head_dim, device=None) -> int:
+    """Tokens of context whose 16-bit keys and values of one layer fill ``PREFILL_BAND_L2_SHARE`` of
+    the device's L2: the sequences that the prompt attention works on together."""
+    index = torch.cuda.current_device() if device is None or torch.device(device).index is None \
+        else torch.device(device).index
+    if index not in _l2_bytes:
+        _l2_bytes[index] = int(torch.cuda.get_device_properties(index).L2_cache_size)
+    return max(1, int(_l2_bytes[index] * PREFILL_BAND_L2_SHARE) // (4 * n_kv_heads * head_dim))
+
+
+def attention_prefill_tiles(tiles, n_tokens, positions, token_slot, cu_seqlens, n_seqs, n_q_heads, n_kv_heads,
+                            head_dim):
     """Fill ``tiles`` (int32 [>= tiles_needed, 4]) with the table of tiles that
-    :func:`attention_prefill_tc` walks for this step's sequences and this group size: (first token,
-    tokens, position of the first, slot) per tile, long key ranges first, padded with empty tiles.
+    :func:`attention_prefill_tc` walks for this step's sequences and these head counts: (first token,
+    tokens, position of the first, slot) per tile; the sequences in bands whose keys and values fit
+    L2 together (longest context first), inside a band the longest key ranges first; padded with
+    empty tiles.
     It is read by the attention kernels before they wait for the kernel ahead of them, so it has
     to be made before the step's first kernel (:func:`embed`, a plain launch), not just before the
     attention; returns the number of entries to pass on."""
@@ -386,7 +403,7 @@ def attention_prefill_tiles(tiles, n_tokens, positions, token_slot, cu_seqlens, 
     _need(n_seqs <= PREFILL_TC_MAX_SEQS, f"attention_prefill_tc: at most {PREFILL_TC_MAX_SEQS} sequences a step")
     _need(cu_seqlens.dtype == torch.int32 and cu_seqlens.numel() >= n_seqs + 1, "attention: cu_seqlens")
     _attn_prefill_tiles(_ptr(tiles), need, _ptr(cu_seqlens), _ptr(positions), _ptr(token_slot), n_seqs,
-                        tok_per_tile, _stream())
+                        tok_per_tile, prefill_band_tokens(n_kv_heads, head_dim, tiles.device), _stream())
     return need
 
 
@@ -411,7 +428,7 @@ def attention_prefill_tc(out, q, n_tokens, positions, token_slot, cu_seqlens, n_
         tok_per_tile = PREFILL_TC_ROWS // (n_q_heads // n_kv_heads)
         tiles = torch.empty((-(-n_tokens // tok_per_tile) + n_seqs, 4), dtype=torch.int32, device=q.device)
         n_tiles = attention_prefill_tiles(tiles, n_tokens, positions, token_slot, cu_seqlens, n_seqs,
-                                          n_q_heads, n_kv_heads)
+                                          n_q_heads, n_kv_heads, head_dim)
         torch.cuda.current_stream().synchronize()
     _need(tiles.dtype == torch.int32 and tiles.numel() >= 4 * n_tiles and tiles.data_ptr() % 16 == 0,
           "attention_prefill_tc: the table of tiles")
@@ -587,6 +604,42 @@ def gemm_tc_bf16(out, x, w, epilogue=EPI_BF16, n_rows=None, swap=None, k_split=N
              _ptr(stream), ld_stream, _ptr(gain), _ptr(ss_out), _ptr(tc_status(x.device)), _stream())
 
 
+_gemm_pair = Function("gemm_pair_bf16", "ek_gemm_pair_bf16",
+                      [_P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P])
+PAIR_EPI_BF16, PAIR_EPI_ADD_F32, PAIR_EPI_SWIGLU = 0, 1, 2
+
+
+def gemm_pair_takes(out, x, w, epilogue) -> bool:
+    """Whether :func:`gemm_pair_bf16` can address these operands (16-byte aligned rows)."""
+    return (x.dtype == w.dtype == torch.bfloat16 and w.shape[1] % 8 == 0 and x.stride(0) % 8 == 0
+            and w.stride(0) % 8 == 0 and x.stride(-1) == 1 and w.stride(-1) == 1 and out.stride(-1) == 1
+            and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0
+            and out.stride(0) % (4 if epilogue == PAIR_EPI_ADD_F32 else 8) == 0)
+
+
+def gemm_pair_bf16(out, x, w, epilogue=PAIR_EPI_BF16, n_rows=None):
+    """The product for many rows on pairs of SMs (``tcgen05.mma.cta_group::2``, 256 x 256 tiles, a
+    persistent launch).  ``PAIR_EPI_BF16``: out [M, N] = x . w^T in bfloat16; ``PAIR_EPI_ADD_F32``:
+    out [M, N] (32-bit) += x . w^T; ``PAIR_EPI_SWIGLU``: out [M, N / 2] = silu(x . wg^T) * (x . wu^T)
+    with w = [gate rows; up rows]."""
+    _need_cuda(out, x, w)
+    m = n_rows if n_rows is not None else x.shape[0]
+    n, k = w.shape
+    _need(gemm_pair_takes(out, x, w, epilogue) and x.shape[-1] == k,
+          "gemm_pair_bf16: bfloat16 operands with dense, 16-byte aligned rows of matching inner size")
+    _need(epilogue in (PAIR_EPI_BF16, PAIR_EPI_ADD_F32, PAIR_EPI_SWIGLU), "gemm_pair_bf16: epilogue")
+    _need(epilogue != PAIR_EPI_SWIGLU or n % 2 == 0, "gemm_pair_bf16: SwiGLU needs gate and up rows")
+    n_out = n // 2 if epilogue == PAIR_EPI_SWIGLU else n
+    _need(out.shape[-1] == n_out and out.shape[0] >= m and x.shape[0] >= m, "gemm_pair_bf16: out shape")
+    _need(out.dtype == (torch.float32 if epilogue == PAIR_EPI_ADD_F32 else torch.bfloat16),
+          "gemm_pair_bf16: out dtype")
+    if lib.recording():
+        moved = 2 * (n * k + m * k) + m * n_out * (8 if epilogue == PAIR_EPI_ADD_F32 else 2)
+        lib.annotate(bytes=moved, flops=2 * m * n * k, label=f"{n}x{k}")
+    _gemm_pair(_ptr(out), _ptr(x), _ptr(w), m, n, k, x.stride(0), w.stride(0), out.stride(0), epilogue,
+               _ptr(tc_status(x.device)), _stream())
+
+
 _gemm_tc_qkv = Function("gemm_tc_bf16", "ek_gemm_tc_qkv_rope",
                         [_P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P, c_int, c_int, c_float,
                          _P, _P, c_float, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, _P, _P])
@@ -636,6 +689,43 @@ def gemm_tc_qkv_rope(qkv, x, w, n_rows, q_gain, k_gain, qk_eps, cos, sin, positi
                  _ptr(cos), _ptr(sin), _ptr(positions), _ptr(token_slot), _ptr(k_pages), _ptr(v_pages),
                  _ptr(block_table), block_table.stride(0), n_q_heads, n_kv_heads, 1 if write_kv else 0,
                  _ptr(tc_status(x.device)), _stream())
+
+
+_gemm_pair_qkv = Function("gemm_pair_bf16", "ek_gemm_pair_qkv_rope",
+                          [_P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P, _P, c_float, _P, _P, _P, _P, _P,
+                           _P, _P, c_int, c_int, c_int, c_int, _P, _P])
+
+
+def gemm_pair_qkv_rope(qkv, x, w, n_rows, q_gain, k_gain, qk_eps, cos, sin, positions, token_slot, k_pages,
+                       v_pages, block_table, n_q_heads, n_kv_heads, write_kv=True):
+    """The q/k/v product of many rows (the pair kernel) with the per-head RMSNorm of q and k, the rotation
+    and the cache write in its epilogue (heads of 128, fully rotated).  Of ``qkv`` only the q columns are
+    written; k and v go to the pages.  Rows with a negative position are skipped."""
+    _need_cuda(qkv, x, w, cos, sin, positions, token_slot, k_pages, v_pages, block_table)
+    m, (n, k) = n_rows, w.shape
+    _need(x.dtype == w.dtype == qkv.dtype == k_pages.dtype == v_pages.dtype == torch.bfloat16,
+          "gemm_pair_qkv_rope: bfloat16 operands, result and cache")
+    _need(n == (n_q_heads + 2 * n_kv_heads) * QKV_ROPE_HEAD_DIM and gemm_pair_takes(qkv, x, w, PAIR_EPI_BF16)
+          and x.shape[-1] == k and x.shape[0] >= m,
+          "gemm_pair_qkv_rope: heads of 128, dense 16-byte aligned operand rows")
+    _need(qkv.shape[-1] == n and qkv.shape[0] >= m, "gemm_pair_qkv_rope: qkv [rows, (NQ + 2 NKV) * 128]")
+    _need(cos.dtype == torch.float32 and sin.dtype == torch.float32 and cos.is_contiguous()
+          and sin.is_contiguous() and cos.shape[-1] == QKV_ROPE_HEAD_DIM // 2,
+          "gemm_pair_qkv_rope: 32-bit tables of 64 columns")
+    for g in (q_gain, k_gain):
+        _need(g is None or (g.is_cuda and g.dtype == torch.float32 and g.numel() == QKV_ROPE_HEAD_DIM),
+              "qk gains: 32-bit [128]")
+    _need(k_pages.is_contiguous() and v_pages.is_contiguous() and k_pages.dim() == 4
+          and k_pages.shape[1:] == (n_kv_heads, PAGE, QKV_ROPE_HEAD_DIM), "attention: pages [P, NKV, 64, 128]")
+    _need(block_table.dtype == torch.int32 and positions.dtype == torch.int32
+          and token_slot.dtype == torch.int32 and positions.numel() >= m and token_slot.numel() >= m,
+          "gemm_pair_qkv_rope: int32 indices, one per row")
+    if lib.recording():
+        lib.annotate(bytes=2 * (n * k + m * k + m * n), flops=2 * m * n * k, label=f"{n}x{k}")
+    _gemm_pair_qkv(_ptr(qkv), _ptr(x), _ptr(w), m, k, x.stride(0), w.stride(0), qkv.stride(0),
+                   _ptr(q_gain), _ptr(k_gain), float(qk_eps), _ptr(cos), _ptr(sin), _ptr(positions),
+                   _ptr(token_slot), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.stride(0),
+                   n_q_heads, n_kv_heads, 1 if write_kv else 0, _ptr(tc_status(x.device)), _stream())
 
 
 # ------------------------------------------------------------------ sampling and decode state

@@ -3,7 +3,9 @@
 * float32: the hand-written FFMA kernel (no tensor-core mode of reduced precision).
 * bfloat16, at most 64 rows (decode): the tcgen05 kernel in its swapped form - weights on the
   128-row side of the MMA, TMA-streamed, K split over blocks.
-* bfloat16, more rows (prefill): the library product, where the reference also calls a
+* bfloat16, more rows (prefill): the tcgen05 kernel on pairs of SMs (256 x 256 tiles, a
+  persistent launch) where its tiles fill the GPU's pairs evenly, with the residual add or
+  SwiGLU in its epilogue; else the library product, where the reference also calls a
   library (``torch.matmul`` on cuBLAS, engine/ek_model.py:298,311,203-209).
 """
 
@@ -37,6 +39,33 @@ def row_scale_of(deferred):
     return deferred.ss, deferred.size, deferred.eps
 
 
+PAIR_MIN_FILL = 0.8       # of the last wave of tiles; below it the library's smaller tiles win
+PAIR_ADDS_TO_STREAM = False
+
+
+def pair_fill(m, n_tiles_n, device) -> float:
+    """How evenly the pair product's tiles fill the GPU: tiles / (waves * pairs of SMs)."""
+    tiles = -(-m // 256) * n_tiles_n
+    pairs = max(1, kernels.sm_count(device) // 2)
+    return tiles / (-(-tiles // pairs) * pairs)
+
+
+def pair_product_wins(out, x, w, m, epilogue) -> bool:
+    """Whether a product of ``m`` rows goes to the kernel on pairs of SMs.  Its plain and its adding
+    form run at the library's speed (0.95-1.05 of it, launch by launch), and a long prompt step is
+    bound by the power cap, where the library's adding product came out ahead (8 x 2,048 tokens of
+    the Qwen3-4B shape: 112.0 ms a step with the library adding, 115.0 ms with this kernel); so the
+    kernel takes the products whose epilogue saves a kernel and a round trip - SwiGLU, and q/k/v
+    with norm, rotation and cache write - and the library the ones that add to the stream."""
+    if epilogue == kernels.PAIR_EPI_ADD_F32 and not PAIR_ADDS_TO_STREAM:
+        return False
+    if m <= SMALL_ROWS or not kernels.gemm_pair_takes(out, x, w, epilogue):
+        return False
+    n = w.shape[0]
+    n_tiles = -(-(n // 2) // 128) if epilogue == kernels.PAIR_EPI_SWIGLU else -(-n // 256)
+    return pair_fill(m, n_tiles, x.device) >= PAIR_MIN_FILL
+
+
 def linear(x, w, ctx, name: str, n_rows=None, out_dtype=None, defer=None):
     """``x`` [M, K] (dense rows), ``w`` [N, K] -> [M, N] from the step's workspace.
 
@@ -44,8 +73,8 @@ def linear(x, w, ctx, name: str, n_rows=None, out_dtype=None, defer=None):
     rows).  ``defer=(stream, norm)``: the caller will add the result to ``stream`` and apply
     ``norm`` next, and this product may do part of that: with few rows the result is added to
     ``stream`` here and a DeferredNorm for ``norm`` is returned; with many rows (bfloat16) the
-    library product adds its 32-bit result to ``stream`` and None is returned (nothing left to add:
-    the norm is called without ``add``).  Otherwise the plain result comes back."""
+    product adds its 32-bit result to ``stream`` and None is returned (nothing left to add: the
+    norm is called without ``add``).  Otherwise the plain result comes back."""
     from ..parts.base import DeferredNorm
     row_scale = None
     if isinstance(x, DeferredNorm):
@@ -66,12 +95,15 @@ def linear(x, w, ctx, name: str, n_rows=None, out_dtype=None, defer=None):
             return DeferredNorm(scaled, ss, tiles, n, float(eps))
     if (defer is not None and row_scale is None and out_dtype is None and w.dtype == torch.bfloat16
             and m > SMALL_ROWS):
-        # many rows (a prompt): the library product adds its 32-bit result to the stream itself
+        # many rows (a prompt): the product adds its 32-bit result to the stream itself
         # (bfloat16 operands, 32-bit C and D), so the norm that follows only reads the stream
         stream = defer[0]
         if stream.dtype == torch.float32 and stream.shape[-1] == n and stream.is_contiguous() \
                 and stream.shape[0] >= m:
-            _library_product_add(stream[:m], x[:m], w)
+            if pair_product_wins(stream, x, w, m, kernels.PAIR_EPI_ADD_F32):
+                kernels.gemm_pair_bf16(stream, x, w, kernels.PAIR_EPI_ADD_F32, n_rows=m)
+            else:
+                _library_product_add(stream[:m], x[:m], w)
             return None
     if row_scale is not None and not (w.dtype == torch.bfloat16 and m <= SMALL_ROWS and tc_takes(x, w)):
         raise kernels.KernelError("a deferred norm reached a product that cannot scale its rows")
@@ -95,6 +127,8 @@ def linear(x, w, ctx, name: str, n_rows=None, out_dtype=None, defer=None):
     elif want_f32:
         # 32-bit logits for many rows: 128 x 128 tiles with the accumulator stored as it is
         kernels.gemm_tc_bf16(out, x, w, epi, n_rows=m, swap=False)
+    elif pair_product_wins(out, x, w, m, kernels.PAIR_EPI_BF16):
+        kernels.gemm_pair_bf16(out, x, w, kernels.PAIR_EPI_BF16, n_rows=m)
     else:
         _library_product(x[:m], w, out)
     return out

@@ -19,7 +19,7 @@ from __future__ import annotations
 import torch
 
 from ..ops import kernels
-from ..ops.linear import linear, row_scale_of, tc_takes
+from ..ops.linear import linear, pair_product_wins, row_scale_of, tc_takes
 from ..registry import lookup_part, register_part
 from .base import DeferredNorm, Mixer
 from .spec import CacheSpec, TensorSpec
@@ -63,19 +63,22 @@ class Attention(Mixer):
         if self.position is not None:
             self.position.prepare(max_positions)
 
+    def _tiles_key(self):
+        return ("prefill_tc_tiles", self.num_heads // self.num_kv_heads, self.num_kv_heads * self.head_dim)
+
     def begin_step(self, ctx):
-        """The table of tiles of the tcgen05 prompt attention, once per step and group size."""
+        """The table of tiles of the tcgen05 prompt attention, once per step and shape of the heads."""
         if ctx.is_decode or not kernels.attention_prefill_tc_supported(
                 self.dtype, self.head_dim, self.num_heads, self.num_kv_heads):
             return
-        key = ("prefill_tc_tiles", self.num_heads // self.num_kv_heads)
+        key = self._tiles_key()
         if key in ctx.shared:
             return
         per_tile = kernels.PREFILL_TC_ROWS // (self.num_heads // self.num_kv_heads)
         rows = -(-ctx.n_tokens // per_tile) + ctx.n_seqs
-        tiles = ctx.workspace.get(f"prefill_tc_tiles_{per_tile}", (rows, 4), torch.int32)
+        tiles = ctx.workspace.get(f"prefill_tc_tiles_{key[1]}_{key[2]}", (rows, 4), torch.int32)
         n = kernels.attention_prefill_tiles(tiles, ctx.n_tokens, ctx.positions, ctx.token_slot, ctx.cu_seqlens,
-                                            ctx.n_seqs, self.num_heads, self.num_kv_heads)
+                                            ctx.n_seqs, self.num_heads, self.num_kv_heads, self.head_dim)
         ctx.shared[key] = (tiles, n)
 
     def load(self, tensors):
@@ -110,6 +113,17 @@ class Attention(Mixer):
             out = ctx.workspace.get("attn_out", (t, self.num_heads * self.head_dim), self.dtype)
             self._attend(out, qkv, ctx, entry)
             return linear(out, self.w_o, ctx, "attn_proj", n_rows=t, defer=defer)
+        if self._fuses_rope_of_many_rows(x, ctx):
+            # many rows, heads of 128: the same on the epilogue of the product on pairs of SMs
+            qkv = ctx.workspace.get("qkv", (t, self.w_qkv.shape[0]), self.dtype)
+            kernels.gemm_pair_qkv_rope(
+                qkv, x, self.w_qkv, t, self.q_gain, self.k_gain,
+                self.qk_norm_eps if self.qk_norm_eps is not None else 0.0, pos.cos, pos.sin,
+                ctx.positions, ctx.token_slot, entry.k_pages, entry.v_pages, entry.block_table,
+                self.num_heads, self.num_kv_heads, write_kv=writes_cache)
+            out = ctx.workspace.get("attn_out", (t, self.num_heads * self.head_dim), self.dtype)
+            self._attend(out, qkv, ctx, entry)
+            return linear(out, self.w_o, ctx, "attn_proj", n_rows=t, defer=defer)
         qkv = linear(x, self.w_qkv, ctx, "qkv", n_rows=t)
         kernels.qk_norm_rope_kv(
             qkv, t, self.q_gain, self.k_gain,
@@ -128,6 +142,15 @@ class Attention(Mixer):
                 and self.head_dim == kernels.QKV_ROPE_HEAD_DIM and pos is not None
                 and getattr(pos, "rotary_dim", 0) == self.head_dim and tc_takes(xin, self.w_qkv))
 
+    def _fuses_rope_of_many_rows(self, x, ctx):
+        pos = self.position
+        if (isinstance(x, DeferredNorm) or self.dtype != torch.bfloat16
+                or self.head_dim != kernels.QKV_ROPE_HEAD_DIM or pos is None
+                or getattr(pos, "rotary_dim", 0) != self.head_dim):
+            return False
+        qkv = ctx.workspace.get("qkv", (ctx.n_tokens, self.w_qkv.shape[0]), self.dtype)
+        return pair_product_wins(qkv, x, self.w_qkv, ctx.n_tokens, kernels.PAIR_EPI_BF16)
+
     def _attend(self, out, qkv, ctx, entry):
         t = ctx.n_tokens
         visible = min(ctx.max_context, self.window) if self.window else ctx.max_context
@@ -140,7 +163,7 @@ class Attention(Mixer):
                 prefill = kernels.attention_prefill_tc      # tcgen05: head sizes 64 and 128
             extra = {}
             if prefill is kernels.attention_prefill_tc:
-                made = ctx.shared.get(("prefill_tc_tiles", self.num_heads // self.num_kv_heads))
+                made = ctx.shared.get(self._tiles_key())
                 if made is not None:                 # (made in begin_step; a part driven alone has none)
                     extra = dict(tiles=made[0], n_tiles=made[1])
             prefill(

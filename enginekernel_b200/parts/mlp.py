@@ -11,7 +11,7 @@ from __future__ import annotations
 import torch
 
 from ..ops import kernels
-from ..ops.linear import linear, row_scale_of, tc_takes
+from ..ops.linear import linear, pair_product_wins, row_scale_of, tc_takes
 from ..registry import register_part
 from .base import DeferredNorm, FeedForward
 from .spec import TensorSpec
@@ -57,9 +57,16 @@ class GatedMLP(FeedForward):
             act = ctx.workspace.get("mlp_act", (t, self.inter), self.dtype)
             kernels.gemm_tc_bf16(act, x, self.w_gate_up, kernels.EPI_SWIGLU, n_rows=t, swap=True,
                                  row_scale=row_scale)
+        elif row_scale is not None:
+            raise kernels.KernelError("a deferred norm reached a product that cannot scale its rows")
+        elif self.dtype == torch.bfloat16 and pair_product_wins(
+                ctx.workspace.get("mlp_act", (t, self.inter), self.dtype), x, self.w_gate_up, t,
+                kernels.PAIR_EPI_SWIGLU):
+            # many rows: the pair of blocks that shares a tile stages gate rows in one block and the
+            # matching up rows in the other, and the epilogue forms silu(gate) * up from the 32-bit sums
+            act = ctx.workspace.get("mlp_act", (t, self.inter), self.dtype)
+            kernels.gemm_pair_bf16(act, x, self.w_gate_up, kernels.PAIR_EPI_SWIGLU, n_rows=t)
         else:
-            if row_scale is not None:
-                raise kernels.KernelError("a deferred norm reached a product that cannot scale its rows")
             gu = linear(x, self.w_gate_up, ctx, "mlp_gate_up", n_rows=t)
             act = ctx.workspace.get("mlp_act", (t, self.inter), self.dtype)
             kernels.silu_mul(act, gu, n_rows=t)

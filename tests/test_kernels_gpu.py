@@ -613,6 +613,153 @@ def test_gemm_tc_direct(m, n, k_):
     k.check_tc_status(DEV)
 
 
+@pytest.mark.parametrize("lengths,starts,group,d", [((5, 300, 64, 129), (0, 0, 0, 0), 4, 128),
+                                                     ((40, 33), (1000, 10), 2, 64),
+                                                     ((1,) * 37, (0,) * 37, 8, 128), ((700,), (0,), 1, 64),
+                                                     ((9000, 3000, 8000, 70, 12000), (0, 4000, 100, 0, 0), 4, 128)])
+def test_prefill_tile_table(lengths, starts, group, d):
+    """The table of tiles of the tcgen05 prompt attention: every token in exactly one tile, a tile
+    within one sequence; the sequences by the length of their context in bands that fit L2, the bands
+    one after another, inside a band the last tiles of its sequences first; empty entries behind."""
+    k = K()
+    n_q, n_kv = 8 * group, 8
+    per = k.PREFILL_TC_ROWS // group
+    cu = [0]
+    pos, slot = [], []
+    for b, (n, a) in enumerate(zip(lengths, starts)):
+        cu.append(cu[-1] + n)
+        pos += list(range(a, a + n))
+        slot += [10 + b] * n
+    n_tokens = cu[-1]
+    as_dev = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    tiles = torch.full((-(-n_tokens // per) + len(lengths) + 5, 4), -7, dtype=torch.int32, device=DEV)
+    n = k.attention_prefill_tiles(tiles, n_tokens, as_dev(pos), as_dev(slot), as_dev(cu), len(lengths), n_q, n_kv, d)
+    got = tiles[:n].cpu().tolist()
+    assert bool((tiles[n:] == -7).all())                    # nothing written past what was asked for
+    live = [e for e in got if e[1] > 0]
+    assert all(e[1] == 0 for e in got[len(live):])          # the empty entries stand behind
+    covered = sorted(t for first, count, _, _ in live for t in range(first, first + count))
+    assert covered == list(range(n_tokens))
+    budget = k.prefill_band_tokens(n_kv, d, DEV)
+    order = sorted(range(len(lengths)), key=lambda b: (-(starts[b] + lengths[b]), b))
+    bands, held = [[]], 0
+    for b in order:
+        if bands[-1] and held + starts[b] + lengths[b] > budget:
+            bands.append([])
+            held = 0
+        bands[-1].append(b)
+        held += starts[b] + lengths[b]
+    if len(lengths) == 5:
+        assert len(bands) > 1                               # (the long case does not fit one band)
+    want = []
+    for band in bands:
+        most = max(-(-lengths[b] // per) for b in band)
+        for r in reversed(range(most)):
+            for b in band:
+                if r < -(-lengths[b] // per):
+                    want.append([cu[b] + r * per, min(per, lengths[b] - r * per), starts[b] + r * per, 10 + b])
+    assert live == want
+
+
+@pytest.mark.parametrize("m,n,k_", [(256, 256, 64), (300, 528, 200), (65, 1040, 72), (1000, 6144, 2560),
+                                    (2048, 2560, 4096), (5000, 784, 320)])
+def test_gemm_pair(m, n, k_):
+    """The product on pairs of SMs (tcgen05.mma.cta_group::2, 256 x 256 tiles, persistent), its three
+    epilogues, with edges that are no multiples of a tile and more tiles than pairs."""
+    k = K()
+    x = rnd(m, k_, dtype=torch.bfloat16, seed=3)
+    w = rnd(n, k_, dtype=torch.bfloat16, seed=4, scale=0.05)
+    want = x.double() @ w.double().t()
+    out16 = torch.full((m + 3, n), 9.0, dtype=torch.bfloat16, device=DEV)
+    k.gemm_pair_bf16(out16, x, w, k.PAIR_EPI_BF16, n_rows=m)
+    k.check_tc_status(DEV)
+    assert rel(out16[:m], want) <= 4e-3
+    assert bool((out16[m:] == 9.0).all())                 # rows beyond the product stay as they were
+    base = rnd(m, n, seed=5)
+    stream = base.clone()
+    k.gemm_pair_bf16(stream, x, w, k.PAIR_EPI_ADD_F32)
+    assert rel(stream, base.double() + want) <= 1e-5
+    inter = n // 2
+    act = torch.empty(m, inter, dtype=torch.bfloat16, device=DEV)
+    k.gemm_pair_bf16(act, x, w, k.PAIR_EPI_SWIGLU)
+    g, u = want[:, :inter], want[:, inter:]
+    assert rel(act, g / (1 + torch.exp(-g)) * u) <= 4e-3
+    k.check_tc_status(DEV)
+
+
+@pytest.mark.parametrize("m,nq,nkv,hidden,gains", [(300, 4, 2, 320, True), (1000, 3, 1, 136, True),
+                                                   (777, 8, 8, 512, False)])
+def test_gemm_pair_qkv_rope(m, nq, nkv, hidden, gains):
+    """The q/k/v product of many rows with head norm, rotation and cache write in its epilogue,
+    against the same product followed by the rotation kernel, and against 64-bit arithmetic; an
+    odd number of heads leaves the last tile half empty."""
+    k = K()
+    d, dtype = 128, torch.bfloat16
+    eps, theta, n_slots, max_len = 1e-6, 10000.0, 7, 400
+    n = (nq + 2 * nkv) * d
+    x = rnd(m, hidden, dtype=dtype, seed=1)
+    w = rnd(n, hidden, dtype=dtype, seed=2, scale=0.05)
+    qg = 1 + 0.1 * rnd(d, seed=8) if gains else None
+    kg = 1 + 0.1 * rnd(d, seed=9) if gains else None
+    inv = 1.0 / (theta ** (torch.arange(0, d, 2, dtype=torch.float32) / d))
+    freqs = torch.outer(torch.arange(max_len, dtype=torch.float32), inv)
+    cos, sin = freqs.cos().to(DEV), freqs.sin().to(DEV)
+    g = torch.Generator().manual_seed(m)
+    # every token its own cache place; some rows are dead
+    place = torch.randperm(n_slots * max_len, generator=g)[:m]
+    slot_of, pos_of = place // max_len, place % max_len
+    pos_of[torch.rand(m, generator=g) < 0.1] = -1
+    positions, slots = pos_of.to(torch.int32).to(DEV), slot_of.to(torch.int32).to(DEV)
+    live = (pos_of >= 0).to(DEV)
+    for write_kv in (True, False):
+        pa = Pages(n_slots, max_len, nkv, d, dtype, seed=3)
+        ref = torch.empty(m, n, dtype=dtype, device=DEV)
+        k.gemm_pair_bf16(ref, x, w, k.PAIR_EPI_BF16)
+        k.qk_norm_rope_kv(ref, m, qg, kg, cos, sin, d, positions, slots, pa.k, pa.v, pa.table, nq, nkv, d,
+                          eps, write_kv=write_kv)
+        pb = Pages(n_slots, max_len, nkv, d, dtype, seed=3)
+        got = torch.full((m, n), 7.0, dtype=dtype, device=DEV)
+        k.gemm_pair_qkv_rope(got, x, w, m, qg, kg, eps, cos, sin, positions, slots, pb.k, pb.v, pb.table,
+                             nq, nkv, write_kv=write_kv)
+        k.check_tc_status(DEV)
+        # one rounding instead of two: equal up to a bfloat16 ulp of the largest value
+        assert rel(got[live][:, :nq * d], ref[live][:, :nq * d]) <= 1e-2, write_kv
+        assert bool((got[~live] == 7.0).all())                # dead rows are not touched
+        assert rel(pb.k, pa.k) <= 1e-2
+        assert torch.equal(pb.v, pa.v)                        # values: the same sums, rounded once
+        if not write_kv:
+            assert pb.k.abs().sum().item() == 0 and pb.v.abs().sum().item() == 0
+    i = int(torch.nonzero(pos_of >= 0)[-1])
+    full = (x[i].double() @ w.double().t()).view(nq + 2 * nkv, d).cpu()
+    c, s_ = freqs[pos_of[i]].double().cos(), freqs[pos_of[i]].double().sin()
+
+    def rot(h, gain):
+        if gain is not None:
+            h = h * torch.rsqrt(h.pow(2).mean() + eps) * gain.double().cpu()
+        lo, hi = h[: d // 2], h[d // 2:]
+        return torch.cat([lo * c - hi * s_, hi * c + lo * s_])
+    pb = Pages(n_slots, max_len, nkv, d, dtype, seed=3)
+    got = torch.empty(m, n, dtype=dtype, device=DEV)
+    k.gemm_pair_qkv_rope(got, x, w, m, qg, kg, eps, cos, sin, positions, slots, pb.k, pb.v, pb.table, nq, nkv)
+    for h in range(nq):
+        assert rel(got[i, h * d:(h + 1) * d], rot(full[h], qg)) <= TOL[dtype]
+    page = int(pb.table[slot_of[i], pos_of[i] // 64])
+    for h in range(nkv):
+        assert rel(pb.k[page, h, pos_of[i] % 64], rot(full[nq + h], kg)) <= TOL[dtype]
+        assert rel(pb.v[page, h, pos_of[i] % 64], full[nq + nkv + h]) <= TOL[dtype]
+
+
+def test_gemm_pair_refuses_rows_it_cannot_address():
+    k = K()
+    from enginekernel_b200.ops.lib import KernelError
+    x = rnd(300, 64, dtype=torch.bfloat16)
+    w = rnd(520, 64, dtype=torch.bfloat16)
+    with pytest.raises(KernelError):                      # 260 outputs a row: rows not 16-byte aligned
+        k.gemm_pair_bf16(torch.empty(300, 260, dtype=torch.bfloat16, device=DEV), x, w, k.PAIR_EPI_SWIGLU)
+    with pytest.raises(KernelError):                      # the add form wants the 32-bit stream
+        k.gemm_pair_bf16(torch.empty(300, 520, dtype=torch.bfloat16, device=DEV), x, w, k.PAIR_EPI_ADD_F32)
+
+
 def test_launchers_refuse_what_they_cannot_do():
     k = K()
     from enginekernel_b200.ops.lib import KernelError
