@@ -52,6 +52,7 @@ struct PairParams {
   int k_blocks;
   int tiles_m, tiles_n, n_pairs;
   int swiglu_half;    // row of w where the up half starts
+  int wide;           // rows of `out` (and of the cache pages) are 32-byte aligned
   int* status;
   // PAIR_EPI_QKV_ROPE: out is the q/k/v buffer [M, (NQ + 2 NKV) * 128], of which only q is written
   const int* positions;     // [M]; a negative position: the row is skipped
@@ -66,17 +67,23 @@ struct PairParams {
   float qk_eps;
 };
 
-// 16 values, rounded to bfloat16, to 32 bytes at `dst` (16-byte aligned).
-__device__ __forceinline__ void store_bf16x16(bf16* dst, const float* v) {
+// 16 values, rounded to bfloat16, to 32 bytes at `dst`: one 32-byte store where `dst` is 32-byte
+// aligned (`wide`), else two of 16 bytes.  A thread of the epilogue writes its own row, so a warp's
+// store touches 32 rows; with 32 bytes a thread every store fills whole 32-byte sectors of L2
+// (half as many transactions as 16-byte stores, which a product with a short K is bound by).
+__device__ __forceinline__ void store_bf16x16(bf16* dst, const float* v, bool wide) {
+  uint32_t w[8];
 #pragma unroll
-  for (int j = 0; j < 16; j += 8) {
-    uint32_t w[4];
-#pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      __nv_bfloat162 h = __floats2bfloat162_rn(v[j + 2 * e], v[j + 2 * e + 1]);
-      w[e] = *reinterpret_cast<uint32_t*>(&h);
-    }
-    *reinterpret_cast<uint4*>(dst + j) = make_uint4(w[0], w[1], w[2], w[3]);
+  for (int e = 0; e < 8; ++e) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * e], v[2 * e + 1]);
+    w[e] = *reinterpret_cast<uint32_t*>(&h);
+  }
+  if (wide) {
+    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(dst), "r"(w[0]), "r"(w[1]),
+                 "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]) : "memory");
+  } else {
+    *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
+    *reinterpret_cast<uint4*>(dst + 8) = make_uint4(w[4], w[5], w[6], w[7]);
   }
 }
 
@@ -258,23 +265,14 @@ gemm_pair_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
           tmem_ld_wait();
           if (m < prm.M) {
 #pragma unroll
-            for (int j = 0; j < 32; j += 8) {
-              uint32_t w[4];
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                const float a = g[j + 2 * e], b = g[j + 2 * e + 1];
-                __nv_bfloat162 h = __floats2bfloat162_rn(__fdividef(a, 1.f + __expf(-a)) * u[j + 2 * e],
-                                                         __fdividef(b, 1.f + __expf(-b)) * u[j + 2 * e + 1]);
-                w[e] = *reinterpret_cast<uint32_t*>(&h);
-              }
-              const int n = n0 + c0 + j;
-              if (n + 8 <= prm.swiglu_half) {
-                *reinterpret_cast<uint4*>(o + c0 + j) = make_uint4(w[0], w[1], w[2], w[3]);
-              } else {
-                const bf16* h = reinterpret_cast<const bf16*>(w);
-                for (int e = 0; e < 8; ++e)
-                  if (n + e < prm.swiglu_half) o[c0 + j + e] = h[e];
-              }
+            for (int e = 0; e < 32; ++e) g[e] = __fdividef(g[e], 1.f + __expf(-g[e])) * u[e];
+            const int n = n0 + c0;
+            if (n + 32 <= prm.swiglu_half) {
+              store_bf16x16(o + c0, g, prm.wide);
+              store_bf16x16(o + c0 + 16, g + 16, prm.wide);
+            } else {
+              for (int e = 0; e < 32; ++e)
+                if (n + e < prm.swiglu_half) o[c0 + e] = __float2bfloat16_rn(g[e]);
             }
           }
         }
@@ -303,8 +301,8 @@ gemm_pair_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
             tmem_ld32_nowait(hacc + c0, v);
             tmem_ld_wait();
             if (store) {
-              store_bf16x16(dst + c0, v);
-              store_bf16x16(dst + c0 + 16, v + 16);
+              store_bf16x16(dst + c0, v, prm.wide);
+              store_bf16x16(dst + c0 + 16, v + 16, prm.wide);
             }
           }
         } else if (is_q || (is_k && prm.write_kv)) {
@@ -353,8 +351,8 @@ gemm_pair_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
                 lo[e] = rstd * (a * glc[e] - b * ghs[e]);
                 hi[e] = rstd * (b * ghc[e] + a * gls[e]);
               }
-              store_bf16x16(dst + c0, lo);
-              store_bf16x16(dst + 64 + c0, hi);
+              store_bf16x16(dst + c0, lo, prm.wide);
+              store_bf16x16(dst + 64 + c0, hi, prm.wide);
             }
           }
         }
@@ -368,7 +366,20 @@ gemm_pair_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
           if (m < prm.M && n0 + c0 < prm.N) {
             if (EPI == PAIR_EPI_ADD_F32) {
               float* o = (float*)prm.out + (size_t)m * prm.ldo + n0 + c0;
-              if (n0 + c0 + 32 <= prm.N) {
+              if (n0 + c0 + 32 <= prm.N && prm.wide) {
+                float old[32];
+#pragma unroll
+                for (int j = 0; j < 32; j += 8)
+                  asm volatile("ld.global.v8.f32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                               : "=f"(old[j]), "=f"(old[j + 1]), "=f"(old[j + 2]), "=f"(old[j + 3]), "=f"(old[j + 4]),
+                                 "=f"(old[j + 5]), "=f"(old[j + 6]), "=f"(old[j + 7]) : "l"(o + j) : "memory");
+#pragma unroll
+                for (int j = 0; j < 32; j += 8)
+                  asm volatile("st.global.v8.f32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(o + j),
+                               "f"(old[j] + v[j]), "f"(old[j + 1] + v[j + 1]), "f"(old[j + 2] + v[j + 2]),
+                               "f"(old[j + 3] + v[j + 3]), "f"(old[j + 4] + v[j + 4]), "f"(old[j + 5] + v[j + 5]),
+                               "f"(old[j + 6] + v[j + 6]), "f"(old[j + 7] + v[j + 7]) : "memory");
+              } else if (n0 + c0 + 32 <= prm.N) {
                 float4 old[8];
 #pragma unroll
                 for (int j = 0; j < 8; ++j) old[j] = *reinterpret_cast<const float4*>(o + 4 * j);
@@ -383,16 +394,8 @@ gemm_pair_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
             } else {
               bf16* o = (bf16*)prm.out + (size_t)m * prm.ldo + n0 + c0;
               if (n0 + c0 + 32 <= prm.N) {
-#pragma unroll
-                for (int j = 0; j < 32; j += 8) {
-                  uint32_t w[4];
-#pragma unroll
-                  for (int e = 0; e < 4; ++e) {
-                    __nv_bfloat162 h = __floats2bfloat162_rn(v[j + 2 * e], v[j + 2 * e + 1]);
-                    w[e] = *reinterpret_cast<uint32_t*>(&h);
-                  }
-                  *reinterpret_cast<uint4*>(o + j) = make_uint4(w[0], w[1], w[2], w[3]);
-                }
+                store_bf16x16(o, v, prm.wide);
+                store_bf16x16(o + 16, v + 16, prm.wide);
               } else {
                 for (int e = 0; e < 32; ++e)
                   if (n0 + c0 + e < prm.N) o[e] = __float2bfloat16_rn(v[e]);
@@ -470,6 +473,7 @@ EK_EXPORT int ek_gemm_pair_bf16(void* out, const void* x, const void* w, int M, 
     return EK_ERR_ARG;
   PairParams prm{};
   prm.out = out; prm.ldo = ldo; prm.M = M; prm.N = N; prm.status = status;
+  prm.wide = (((uintptr_t)out & 31) == 0 && ldo % (epilogue == PAIR_EPI_ADD_F32 ? 8 : 16) == 0) ? 1 : 0;
   prm.k_blocks = (K + kTcBK - 1) / kTcBK;
   prm.swiglu_half = N / 2;
   prm.tiles_m = (M + kPairTile - 1) / kPairTile;
@@ -506,6 +510,8 @@ EK_EXPORT int ek_gemm_pair_qkv_rope(void* out, const void* x, const void* w, int
     return EK_ERR_ARG;
   PairParams prm{};
   prm.out = out; prm.ldo = ldo; prm.M = M; prm.status = status;
+  prm.wide = (((uintptr_t)out & 31) == 0 && ldo % 16 == 0 && ((uintptr_t)k_pages & 31) == 0 &&
+              ((uintptr_t)v_pages & 31) == 0) ? 1 : 0;
   prm.N = (n_q_heads + 2 * n_kv_heads) * 128;
   prm.k_blocks = (K + kTcBK - 1) / kTcBK;
   prm.tiles_m = (M + kPairTile - 1) / kPairTile;

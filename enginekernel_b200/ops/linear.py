@@ -52,11 +52,12 @@ def pair_fill(m, n_tiles_n, device) -> float:
 
 def pair_product_wins(out, x, w, m, epilogue) -> bool:
     """Whether a product of ``m`` rows goes to the kernel on pairs of SMs.  Its plain and its adding
-    form run at the library's speed (0.95-1.05 of it, launch by launch), and a long prompt step is
+    form run at the library's speed launch by launch (0.96-1.02 of it), and a long prompt step is
     bound by the power cap, where the library's adding product came out ahead (8 x 2,048 tokens of
-    the Qwen3-4B shape: 112.0 ms a step with the library adding, 115.0 ms with this kernel); so the
-    kernel takes the products whose epilogue saves a kernel and a round trip - SwiGLU, and q/k/v
-    with norm, rotation and cache write - and the library the ones that add to the stream."""
+    the Qwen3-4B shape: 111.3 ms a step with the library adding, 113.2 ms with this kernel, 117.5 ms
+    with the library for every product); so the kernel takes the products whose epilogue saves a
+    kernel and a round trip through memory - SwiGLU, and q/k/v with norm, rotation and cache write -
+    and the library the ones that add to the stream."""
     if epilogue == kernels.PAIR_EPI_ADD_F32 and not PAIR_ADDS_TO_STREAM:
         return False
     if m <= SMALL_ROWS or not kernels.gemm_pair_takes(out, x, w, epilogue):
