@@ -139,6 +139,34 @@ __device__ __forceinline__ void tc_mma_pair(uint32_t d_tmem, uint64_t desc_a, ui
       ::"r"(d_tmem), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
 }
 
+// One stage of the pair's product in one piece of PTX: ask the NEXT stage's barrier, issue this stage's
+// four MMAs (K = 16 each, 32 bytes further along the swizzled row), commit them to this stage's "empty"
+// barrier in both blocks, and only then look at the barrier's answer - the thread does not wait for it
+// before the MMAs are on their way.  Returns whether the next stage is full.
+__device__ __forceinline__ uint32_t mma_stage_pair(uint32_t d_tmem, uint64_t da, uint64_t db, uint32_t idesc,
+                                                   uint32_t accumulate, uint32_t empty_bar, uint32_t next_full,
+                                                   uint32_t next_parity) {
+  uint32_t ready;
+  asm volatile(
+      "{\n\t.reg .pred p, q, t;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 q, [%8], %9;\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "setp.eq.b32 t, %6, %6;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%1], %2, %3, %4, {%6, %6, %6, %6, %6, %6, %6, %6}, p;\n\t"
+      "add.u64 %2, %2, 2;\n\tadd.u64 %3, %3, 2;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%1], %2, %3, %4, {%6, %6, %6, %6, %6, %6, %6, %6}, t;\n\t"
+      "add.u64 %2, %2, 2;\n\tadd.u64 %3, %3, 2;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%1], %2, %3, %4, {%6, %6, %6, %6, %6, %6, %6, %6}, t;\n\t"
+      "add.u64 %2, %2, 2;\n\tadd.u64 %3, %3, 2;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%1], %2, %3, %4, {%6, %6, %6, %6, %6, %6, %6, %6}, t;\n\t"
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%7], %10;\n\t"
+      "selp.u32 %0, 1, 0, q;\n\t}"
+      : "=r"(ready), "+r"(d_tmem), "+l"(da), "+l"(db)
+      : "r"(idesc), "r"(accumulate), "r"(0u), "r"(empty_bar), "r"(next_full), "r"(next_parity), "h"((uint16_t)3)
+      : "memory");
+  return ready;
+}
+
 // The i-th tile of the list: row tiles in groups of kPairGroup, inside a group the row tile runs
 // fastest, so that pairs working side by side share rows of x and of w.
 __device__ __forceinline__ void pair_tile(const PairParams& prm, int t, int& tile_m, int& tile_n) {
@@ -214,8 +242,15 @@ gemm_pair_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
     }
   } else if (tid == 32 * (kPairEpilogueWarps + 1) && rank == 0) {
     // ------------------------------------------------------------------ MMA issuer (first block)
+    // This thread is the pace of the kernel: a stage's four MMAs keep the tensor cores of both SMs
+    // busy for 512 cycles, and reading the stage's barrier (about 220 cycles until the answer is
+    // there), issuing them and committing took it longer than that.  So the barrier of the NEXT stage
+    // is asked before this stage's MMAs are issued and its answer looked at after them; the bounded
+    // wait is only entered when that answer was "not yet".
     constexpr uint32_t idesc = pair_idesc();
+    const uint32_t stage0 = smem_u32(smem);
     int c = 0, i = 0;                          // stages consumed, tiles done
+    uint32_t ready = 0;                        // the stage c is known to be full
     for (int t = pair; t < n_tiles && ok; t += prm.n_pairs, ++i) {
       const int buf = i & 1;
       if (i >= 2) {                            // the epilogues of tile i - 2 have read this accumulator
@@ -226,15 +261,17 @@ gemm_pair_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
       const uint32_t acc = tmem_base + (uint32_t)(buf * kPairTile);
       for (int kb = 0; kb < prm.k_blocks; ++kb, ++c) {
         const int s = c % kPairStages;
-        ok = mbar_wait(full0 + 8 * s, (c / kPairStages) & 1, prm.status, 43);
-        if (!ok) break;
+        if (!ready) {
+          ok = mbar_wait(full0 + 8 * s, (c / kPairStages) & 1, prm.status, 43);
+          if (!ok) break;
+        }
         tc_fence_after();
-        const uint32_t base = smem_u32(smem + (size_t)s * kPairStageBytes);
-        const uint64_t da = smem_desc_k_sw128(base), db = smem_desc_k_sw128(base + kPairHalfBytes);
-#pragma unroll
-        for (int k = 0; k < kTcBK / 16; ++k)
-          tc_mma_pair(acc, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, (kb || k) ? 1u : 0u);
-        tc_commit_pair(empty0 + 8 * s);        // the stage is free in both blocks once these are done
+        const int s_next = (c + 1) % kPairStages;
+        const uint32_t base = stage0 + (uint32_t)s * kPairStageBytes;
+        static_assert(kTcBK == 64, "mma_stage_pair issues four MMAs of K = 16");
+        ready = mma_stage_pair(acc, smem_desc_k_sw128(base), smem_desc_k_sw128(base + kPairHalfBytes), idesc,
+                               kb ? 1u : 0u, empty0 + 8 * s, full0 + 8 * s_next,
+                               ((c + 1) / kPairStages) & 1);
       }
       if (!ok) break;
       tc_commit_pair(acc_full0 + 8 * buf);     // the tile's accumulator is complete in both blocks
@@ -249,43 +286,23 @@ gemm_pair_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
       int tile_m, tile_n;
       pair_tile(prm, t, tile_m, tile_n);
       const int buf = i & 1;
-      ok = mbar_wait(acc_full0 + 8 * buf, (i >> 1) & 1, prm.status, 44);
-      if (!ok) break;
-      tc_fence_after();
       const int m = tile_m * kPairTile + (int)rank * kPairRows + quarter * 32 + lane;
-      const uint32_t acc = lane_addr + (uint32_t)(buf * kPairTile);
-      if (EPI == PAIR_EPI_SWIGLU) {
-        const int n0 = tile_n * kPairRows;     // outputs of this tile: n0 .. n0 + 127
-        bf16* o = (bf16*)prm.out + (size_t)m * prm.ldo + n0;
-#pragma unroll 1
-        for (int c0 = side * (kPairRows / 2); c0 < (side + 1) * (kPairRows / 2); c0 += 32) {
-          float g[32], u[32];
-          tmem_ld32_nowait(acc + c0, g);
-          tmem_ld32_nowait(acc + kPairRows + c0, u);
-          tmem_ld_wait();
-          if (m < prm.M) {
-#pragma unroll
-            for (int e = 0; e < 32; ++e) g[e] = __fdividef(g[e], 1.f + __expf(-g[e])) * u[e];
-            const int n = n0 + c0;
-            if (n + 32 <= prm.swiglu_half) {
-              store_bf16x16(o + c0, g, prm.wide);
-              store_bf16x16(o + c0 + 16, g + 16, prm.wide);
-            } else {
-              for (int e = 0; e < 32; ++e)
-                if (n + e < prm.swiglu_half) o[c0 + e] = __float2bfloat16_rn(g[e]);
-            }
-          }
-        }
-      } else if (EPI == PAIR_EPI_QKV_ROPE) {
-        // the tile holds two heads of this thread's token: columns 0..127 (warps 0..3 take that one)
-        // and 128..255 (warps 4..7); the head is the same for a whole warp, so the branches below
-        // do not split a warp around tcgen05.ld
+      // q/k/v form: the token's position, cache page and angles do not depend on the accumulator, so
+      // they are asked for before the wait for it (three dependent rounds of loads otherwise stand
+      // between the accumulator and its first store)
+      int pos = -1;
+      bf16* dst = nullptr;
+      bool is_q = false, is_k = false, is_v = false;
+      const float* cs = nullptr;
+      const float* sn = nullptr;
+      float4 c4[4], s4[4];                      // the angles of the head's first 16 pairs
+      if (EPI == PAIR_EPI_QKV_ROPE) {
         const int n_kv = prm.cache.heads, nq = prm.n_q_heads;
-        const int head = 2 * tile_n + side;
-        const bool is_q = head < nq, is_k = !is_q && head < nq + n_kv, is_v = !is_q && !is_k && head < nq + 2 * n_kv;
-        const int pos = m < prm.M ? prm.positions[m] : -1;
-        const uint32_t hacc = acc + (uint32_t)(side * 128);
-        bf16* dst = nullptr;
+        const int head = 2 * tile_n + side;     // columns 0..127 of the tile: warps 0..3; 128..255: warps 4..7
+        is_q = head < nq;
+        is_k = !is_q && head < nq + n_kv;
+        is_v = !is_q && !is_k && head < nq + 2 * n_kv;
+        pos = m < prm.M ? prm.positions[m] : -1;
         if (is_q) {
           dst = (bf16*)prm.out + (size_t)m * prm.ldo + (size_t)head * 128;
         } else if ((is_k || is_v) && prm.write_kv && pos >= 0) {
@@ -293,77 +310,121 @@ gemm_pair_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
           const int kv_head = is_k ? head - nq : head - nq - n_kv;
           dst = (bf16*)(is_k ? prm.cache.k : prm.cache.v) + page_offset(prm.cache, page, kv_head, pos);
         }
-        const bool store = pos >= 0 && dst != nullptr;
-        if (is_v && prm.write_kv) {               // values: rounded and stored
-#pragma unroll 1
-          for (int c0 = 0; c0 < 128; c0 += 32) {
-            float v[32];
-            tmem_ld32_nowait(hacc + c0, v);
-            tmem_ld_wait();
-            if (store) {
-              store_bf16x16(dst + c0, v, prm.wide);
-              store_bf16x16(dst + c0 + 16, v + 16, prm.wide);
+        if (is_q || (is_k && prm.write_kv)) {
+          cs = prm.cos_tab + (size_t)max(pos, 0) * 64;
+          sn = prm.sin_tab + (size_t)max(pos, 0) * 64;
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            c4[e] = *reinterpret_cast<const float4*>(cs + 4 * e);
+            s4[e] = *reinterpret_cast<const float4*>(sn + 4 * e);
+          }
+        }
+      }
+      ok = mbar_wait(acc_full0 + 8 * buf, (i >> 1) & 1, prm.status, 44);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t acc = lane_addr + (uint32_t)(buf * kPairTile);
+      // This thread's 128 columns of the accumulator in one go (one wait for tensor memory instead of
+      // one a chunk: with the MMAs of the next tile running, each such wait takes about a microsecond),
+      // then the accumulator is handed back and the rest works from registers.
+      float v[128];
+      {
+        const uint32_t first = EPI == PAIR_EPI_SWIGLU ? acc + (uint32_t)(side * 64) : acc + (uint32_t)(side * 128);
+        tmem_ld32_nowait(first, v);
+        tmem_ld32_nowait(first + 32, v + 32);
+        if (EPI == PAIR_EPI_SWIGLU) {            // gate columns 64 side .. + 63, then their up columns
+          tmem_ld32_nowait(first + 128, v + 64);
+          tmem_ld32_nowait(first + 160, v + 96);
+        } else {
+          tmem_ld32_nowait(first + 64, v + 64);
+          tmem_ld32_nowait(first + 96, v + 96);
+        }
+        tmem_ld_wait();
+      }
+      tc_fence_before();                       // read: the MMAs of tile i + 2 may overwrite the accumulator
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(acc_empty_first + 8 * buf);
+
+      if (EPI == PAIR_EPI_SWIGLU) {
+        const int n0 = tile_n * kPairRows + side * 64;     // this thread's outputs: n0 .. n0 + 63
+        bf16* o = (bf16*)prm.out + (size_t)m * prm.ldo + n0;
+        if (m < prm.M) {
+#pragma unroll
+          for (int c0 = 0; c0 < 64; c0 += 16) {
+#pragma unroll
+            for (int e = 0; e < 16; ++e)
+              v[c0 + e] = __fdividef(v[c0 + e], 1.f + __expf(-v[c0 + e])) * v[64 + c0 + e];
+            if (n0 + c0 + 16 <= prm.swiglu_half) {
+              store_bf16x16(o + c0, v + c0, prm.wide);
+            } else {
+              for (int e = 0; e < 16; ++e)
+                if (n0 + c0 + e < prm.swiglu_half) o[c0 + e] = __float2bfloat16_rn(v[c0 + e]);
             }
           }
-        } else if (is_q || (is_k && prm.write_kv)) {
+        }
+      } else if (EPI == PAIR_EPI_QKV_ROPE) {
+        // the tile holds two heads of this thread's token, one for each half of the epilogue warps
+        const bool store = pos >= 0 && dst != nullptr;
+        if (is_v && prm.write_kv) {               // values: rounded and stored
+          if (store) {
+#pragma unroll
+            for (int c0 = 0; c0 < 128; c0 += 16) store_bf16x16(dst + c0, v + c0, prm.wide);
+          }
+        } else if (store && (is_q || is_k)) {
           const float* gain = is_q ? prm.q_gain : prm.k_gain;
           float rstd = 1.f;
           if (gain) {
             float ss[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll 1
-            for (int c0 = 0; c0 < 128; c0 += 32) {
-              float v[32];
-              tmem_ld32_nowait(hacc + c0, v);
-              tmem_ld_wait();
 #pragma unroll
-              for (int e = 0; e < 32; ++e) ss[e & 3] = fmaf(v[e], v[e], ss[e & 3]);
-            }
+            for (int e = 0; e < 128; ++e) ss[e & 3] = fmaf(v[e], v[e], ss[e & 3]);
             rstd = rsqrtf(((ss[0] + ss[1]) + (ss[2] + ss[3])) * (1.f / 128.f) + prm.qk_eps);
           }
-          const float* cs = prm.cos_tab + (size_t)max(pos, 0) * 64;
-          const float* sn = prm.sin_tab + (size_t)max(pos, 0) * 64;
-#pragma unroll 1
+#pragma unroll
           for (int c0 = 0; c0 < 64; c0 += 16) {
-            // gain * cos and gain * sin of these 16 pairs first: their loads fly while TMEM is read
-            float glc[16], gls[16], ghc[16], ghs[16];
+            float4 cn[4], sx[4];                  // the next 16 pairs' angles fly under this step
+            if (c0 + 16 < 64) {
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                cn[e] = *reinterpret_cast<const float4*>(cs + c0 + 16 + 4 * e);
+                sx[e] = *reinterpret_cast<const float4*>(sn + c0 + 16 + 4 * e);
+              }
+            }
 #pragma unroll
             for (int e = 0; e < 16; e += 4) {
-              const float4 c4 = *reinterpret_cast<const float4*>(cs + c0 + e);
-              const float4 s4 = *reinterpret_cast<const float4*>(sn + c0 + e);
-              float4 gl = make_float4(1.f, 1.f, 1.f, 1.f), gh = gl;
+              float4 gl = make_float4(rstd, rstd, rstd, rstd), gh = gl;
               if (gain) {
-                gl = *reinterpret_cast<const float4*>(gain + c0 + e);
-                gh = *reinterpret_cast<const float4*>(gain + 64 + c0 + e);
+                const float4 a = *reinterpret_cast<const float4*>(gain + c0 + e);
+                const float4 b = *reinterpret_cast<const float4*>(gain + 64 + c0 + e);
+                gl = make_float4(a.x * rstd, a.y * rstd, a.z * rstd, a.w * rstd);
+                gh = make_float4(b.x * rstd, b.y * rstd, b.z * rstd, b.w * rstd);
               }
-              glc[e] = gl.x * c4.x; glc[e + 1] = gl.y * c4.y; glc[e + 2] = gl.z * c4.z; glc[e + 3] = gl.w * c4.w;
-              gls[e] = gl.x * s4.x; gls[e + 1] = gl.y * s4.y; gls[e + 2] = gl.z * s4.z; gls[e + 3] = gl.w * s4.w;
-              ghc[e] = gh.x * c4.x; ghc[e + 1] = gh.y * c4.y; ghc[e + 2] = gh.z * c4.z; ghc[e + 3] = gh.w * c4.w;
-              ghs[e] = gh.x * s4.x; ghs[e + 1] = gh.y * s4.y; ghs[e + 2] = gh.z * s4.z; ghs[e + 3] = gh.w * s4.w;
-            }
-            float lo[16], hi[16];
-            tmem_ld16_nowait(hacc + c0, lo);
-            tmem_ld16_nowait(hacc + 64 + c0, hi);
-            tmem_ld_wait();
-            if (store) {
+              const float4 cc = c4[e / 4], sv = s4[e / 4];
+              const float cv[4] = {cc.x, cc.y, cc.z, cc.w}, sw[4] = {sv.x, sv.y, sv.z, sv.w};
+              const float g0[4] = {gl.x, gl.y, gl.z, gl.w}, g1[4] = {gh.x, gh.y, gh.z, gh.w};
 #pragma unroll
-              for (int e = 0; e < 16; ++e) {
-                const float a = lo[e], b = hi[e];
-                lo[e] = rstd * (a * glc[e] - b * ghs[e]);
-                hi[e] = rstd * (b * ghc[e] + a * gls[e]);
+              for (int i = 0; i < 4; ++i) {
+                const float x = v[c0 + e + i] * g0[i], y = v[64 + c0 + e + i] * g1[i];   // gain * x / rms
+                v[c0 + e + i] = x * cv[i] - y * sw[i];
+                v[64 + c0 + e + i] = y * cv[i] + x * sw[i];
               }
-              store_bf16x16(dst + c0, lo, prm.wide);
-              store_bf16x16(dst + 64 + c0, hi, prm.wide);
+            }
+            store_bf16x16(dst + c0, v + c0, prm.wide);
+            store_bf16x16(dst + 64 + c0, v + 64 + c0, prm.wide);
+            if (c0 + 16 < 64) {
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                c4[e] = cn[e];
+                s4[e] = sx[e];
+              }
             }
           }
         }
       } else {
-        const int n0 = tile_n * kPairTile;
-#pragma unroll 1
-        for (int c0 = side * (kPairTile / 2); c0 < (side + 1) * (kPairTile / 2); c0 += 32) {
-          float v[32];
-          tmem_ld32_nowait(acc + c0, v);
-          tmem_ld_wait();
-          if (m < prm.M && n0 + c0 < prm.N) {
+        const int n0 = tile_n * kPairTile + side * 128;     // this thread's columns: n0 .. n0 + 127
+        if (m < prm.M) {
+#pragma unroll
+          for (int c0 = 0; c0 < 128; c0 += 32) {
+            if (n0 + c0 >= prm.N) break;
             if (EPI == PAIR_EPI_ADD_F32) {
               float* o = (float*)prm.out + (size_t)m * prm.ldo + n0 + c0;
               if (n0 + c0 + 32 <= prm.N && prm.wide) {
@@ -376,37 +437,34 @@ gemm_pair_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
 #pragma unroll
                 for (int j = 0; j < 32; j += 8)
                   asm volatile("st.global.v8.f32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(o + j),
-                               "f"(old[j] + v[j]), "f"(old[j + 1] + v[j + 1]), "f"(old[j + 2] + v[j + 2]),
-                               "f"(old[j + 3] + v[j + 3]), "f"(old[j + 4] + v[j + 4]), "f"(old[j + 5] + v[j + 5]),
-                               "f"(old[j + 6] + v[j + 6]), "f"(old[j + 7] + v[j + 7]) : "memory");
+                               "f"(old[j] + v[c0 + j]), "f"(old[j + 1] + v[c0 + j + 1]), "f"(old[j + 2] + v[c0 + j + 2]),
+                               "f"(old[j + 3] + v[c0 + j + 3]), "f"(old[j + 4] + v[c0 + j + 4]),
+                               "f"(old[j + 5] + v[c0 + j + 5]), "f"(old[j + 6] + v[c0 + j + 6]),
+                               "f"(old[j + 7] + v[c0 + j + 7]) : "memory");
               } else if (n0 + c0 + 32 <= prm.N) {
-                float4 old[8];
 #pragma unroll
-                for (int j = 0; j < 8; ++j) old[j] = *reinterpret_cast<const float4*>(o + 4 * j);
-#pragma unroll
-                for (int j = 0; j < 8; ++j)
-                  *reinterpret_cast<float4*>(o + 4 * j) = make_float4(old[j].x + v[4 * j], old[j].y + v[4 * j + 1],
-                                                                      old[j].z + v[4 * j + 2], old[j].w + v[4 * j + 3]);
+                for (int j = 0; j < 32; j += 4) {
+                  const float4 old = *reinterpret_cast<const float4*>(o + j);
+                  *reinterpret_cast<float4*>(o + j) = make_float4(old.x + v[c0 + j], old.y + v[c0 + j + 1],
+                                                                  old.z + v[c0 + j + 2], old.w + v[c0 + j + 3]);
+                }
               } else {
                 for (int e = 0; e < 32; ++e)
-                  if (n0 + c0 + e < prm.N) o[e] += v[e];
+                  if (n0 + c0 + e < prm.N) o[e] += v[c0 + e];
               }
             } else {
               bf16* o = (bf16*)prm.out + (size_t)m * prm.ldo + n0 + c0;
               if (n0 + c0 + 32 <= prm.N) {
-                store_bf16x16(o, v, prm.wide);
-                store_bf16x16(o + 16, v + 16, prm.wide);
+                store_bf16x16(o, v + c0, prm.wide);
+                store_bf16x16(o + 16, v + c0 + 16, prm.wide);
               } else {
                 for (int e = 0; e < 32; ++e)
-                  if (n0 + c0 + e < prm.N) o[e] = __float2bfloat16_rn(v[e]);
+                  if (n0 + c0 + e < prm.N) o[e] = __float2bfloat16_rn(v[c0 + e]);
               }
             }
           }
         }
       }
-      tc_fence_before();                       // the accumulator has been read: the MMAs of tile i + 2 may overwrite it
-      __syncwarp();
-      if (lane == 0) mbar_arrive_cluster(acc_empty_first + 8 * buf);
     }
   }
 
