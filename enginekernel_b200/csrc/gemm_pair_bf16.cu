@@ -139,8 +139,8 @@ __device__ __forceinline__ void tc_mma_pair(uint32_t d_tmem, uint64_t desc_a, ui
       ::"r"(d_tmem), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
 }
 
-// One stage of the pair's product in one piece of PTX: ask the NEXT stage's barrier, issue this stage's
-// four MMAs (K = 16 each, 32 bytes further along the swizzled row), commit them to this stage's "empty"
+// One stage of the pair's product in one piece of PTX: ask the NEXT stage's barrier (test_wait: it
+// answers at once and never suspends the thread, unlike try_wait), issue this stage's four MMAs (K = 16 each, 32 bytes further along the swizzled row), commit them to this stage's "empty"
 // barrier in both blocks, and only then look at the barrier's answer - the thread does not wait for it
 // before the MMAs are on their way.  Returns whether the next stage is full.
 __device__ __forceinline__ uint32_t mma_stage_pair(uint32_t d_tmem, uint64_t da, uint64_t db, uint32_t idesc,
@@ -149,7 +149,7 @@ __device__ __forceinline__ uint32_t mma_stage_pair(uint32_t d_tmem, uint64_t da,
   uint32_t ready;
   asm volatile(
       "{\n\t.reg .pred p, q, t;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 q, [%8], %9;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 q, [%8], %9;\n\t"
       "setp.ne.b32 p, %5, 0;\n\t"
       "setp.eq.b32 t, %6, %6;\n\t"
       "tcgen05.mma.cta_group::2.kind::f16 [%1], %2, %3, %4, {%6, %6, %6, %6, %6, %6, %6, %6}, p;\n\t"
