@@ -139,3 +139,30 @@ def test_whole_small_family_model_at_full_depth_batch_of_4(small_family, dtype):
         assert err <= helpers.TOL[dtype], (dtype, len(s), err)
     del eng
     torch.cuda.empty_cache()
+
+
+@pytest.mark.parametrize("adds_to_stream", [False, True])
+def test_prompt_products_on_pairs_of_sms_follow_plain(folder, monkeypatch, adds_to_stream):
+    """The prompt path with its products on pairs of SMs: q/k/v with head norm, rotation and cache
+    write in the epilogue, gate/up with SwiGLU in the epilogue, and (second run) the two products
+    that add to the residual stream as well.  The prompts are cut into pieces, so later pieces and
+    the decoded tokens read cache pages that the epilogue wrote.  (A few hundred rows would go to
+    the library: the rule that wants the tiles to fill the GPU's pairs is switched off here.)"""
+    from enginekernel_b200 import Engine
+    from enginekernel_b200.ops import lib, linear
+    monkeypatch.setattr(linear, "PAIR_MIN_FILL", 0.0)
+    monkeypatch.setattr(linear, "PAIR_ADDS_TO_STREAM", adds_to_stream)
+    model = helpers.plain_model(folder)
+    eng = Engine(folder, "bfloat16", max_tokens=2048, max_batch=4, max_step_tokens=200)
+    seqs = tiny_models.random_prompts(CFG, [300, 70, 129], seed=9)
+    with lib.LaunchRecord() as record:
+        got = helpers.batch_then_steps(eng, seqs, [290, 66, 129])
+    eng.runner.check_kernels()
+    names = set(record.names())
+    assert any(n.startswith("ek_gemm_pair_qkv_rope") for n in names), names
+    assert any(n.startswith("ek_gemm_pair_bf16[19456") for n in names), names        # gate/up with SwiGLU
+    assert any(n.startswith("library_addmm") for n in names) == (not adds_to_stream), names
+    assert not any("qk_norm_rope_kv" in n or "silu_mul" in n for n in names), names  # their kernels did not run
+    for s, g in zip(seqs, got):
+        err = helpers.rel_err(g, plain.logits(model, s))
+        assert err <= helpers.TOL["bfloat16"], (len(s), err)
