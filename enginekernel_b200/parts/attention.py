@@ -68,7 +68,7 @@ class Attention(Mixer):
 
     def begin_step(self, ctx):
         """The table of tiles of the tcgen05 prompt attention, once per step and shape of the heads."""
-        if ctx.is_decode or not kernels.attention_prefill_tc_supported(
+        if ctx.is_decode or ctx.n_seqs > kernels.PREFILL_TC_MAX_SEQS or not kernels.attention_prefill_tc_supported(
                 self.dtype, self.head_dim, self.num_heads, self.num_kv_heads):
             return
         key = self._tiles_key()
@@ -158,8 +158,8 @@ class Attention(Mixer):
         if not ctx.is_decode and kernels.attention_prefill_supported(
                 self.dtype, self.head_dim, self.num_heads, self.num_kv_heads):
             prefill = kernels.attention_prefill_bf16
-            if kernels.attention_prefill_tc_supported(self.dtype, self.head_dim, self.num_heads,
-                                                      self.num_kv_heads):
+            if ctx.n_seqs <= kernels.PREFILL_TC_MAX_SEQS and kernels.attention_prefill_tc_supported(
+                    self.dtype, self.head_dim, self.num_heads, self.num_kv_heads):
                 prefill = kernels.attention_prefill_tc      # tcgen05: head sizes 64 and 128
             extra = {}
             if prefill is kernels.attention_prefill_tc:

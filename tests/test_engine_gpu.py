@@ -252,6 +252,25 @@ def test_more_than_64_sequences_decode_together(folders, plains):
         assert helpers.rel_err(got[i], plain.logits(plains[tag], seqs[i])) <= helpers.TOL["bfloat16"]
 
 
+def test_a_prompt_step_of_more_sequences_than_the_tile_table_takes(folders, plains):
+    """1,100 short prompts in one step: the tcgen05 prompt attention takes 1,024 sequences a step, so
+    this step runs on the mma.sync kernel instead of being refused (head size 64, bfloat16)."""
+    from enginekernel_b200 import Engine
+    tag = "E"
+    cfg = CONFIGS[tag][0]
+    n = 1100
+    eng = Engine(folders[tag], "bfloat16", max_tokens=64 * n, max_batch=n)
+    seqs = tiny_models.random_prompts(cfg, [2 + (i % 4) for i in range(n)], seed=23)
+    slots = [eng.open_sequence() for _ in seqs]
+    logits = eng.step([(slot, s, [len(s) - 1]) for slot, s in zip(slots, seqs)]).cpu()
+    for slot in slots:
+        eng.close_sequence(slot)
+    eng.runner.check_kernels()
+    for i in (0, 511, 1023, 1024, 1099):
+        want = plain.logits(plains[tag], seqs[i])[-1:]
+        assert helpers.rel_err(logits[i:i + 1], want) <= helpers.TOL["bfloat16"], i
+
+
 def test_sizes_the_tensor_core_path_cannot_address_still_work(tmp_path):
     """A width that is a multiple of 4 but not of 8: bfloat16 falls back to the library product
     instead of refusing or computing wrong."""
