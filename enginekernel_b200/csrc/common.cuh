@@ -229,6 +229,16 @@ __device__ __forceinline__ void st_cluster_f32x4(float* own, unsigned rank, floa
   asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};"
                ::"r"(r), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
 }
+// Four floats (16-byte aligned) to the same shared-memory offset in block `rank` of this cluster, as
+// an asynchronous store that counts its 16 bytes on the mbarrier at `own_bar`'s offset in that block:
+// a thread there that has seen the barrier's phase complete sees the data.
+__device__ __forceinline__ void st_async_f32x4(float* own, unsigned rank, float4 v, unsigned own_bar) {
+  unsigned a = (unsigned)__cvta_generic_to_shared(own), r, b;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(rank));
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(b) : "r"(own_bar), "r"(rank));
+  asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.f32 [%0], {%1, %2, %3, %4}, [%5];"
+               ::"r"(r), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w), "r"(b) : "memory");
+}
 // Four floats (16-byte aligned) at the same shared-memory offset in block `rank` of this cluster.
 __device__ __forceinline__ float4 ld_cluster_f32x4(const float* own, unsigned rank) {
   unsigned a = (unsigned)__cvta_generic_to_shared(own), r;

@@ -18,7 +18,8 @@
 //     a thread-block cluster: each leaves its partial tile in its own shared memory and sums
 //     its share of the tile's columns over all of them, in split order, through distributed
 //     shared memory (with at most 8 sequences each block sends its partial sums to the
-//     owning block instead).  More splits than that go through scratch in global memory, and
+//     owning block instead, by stores that count their bytes on a barrier of the owner, and
+//     only the owner waits - for those bytes, not for the cluster).  More splits than that go through scratch in global memory, and
 //     the block that delivers the last partial of a tile adds them in split order.
 //   * direct (prompts): P = activations, Q = weights, 128 x 256 tiles.
 // Epilogues: bfloat16, 32-bit, or SwiGLU (the tile holds gate rows/columns in its first
@@ -105,10 +106,10 @@ gemm_tc_bf16_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
   extern __shared__ __align__(1024) unsigned char smem[];
   unsigned char* p_tiles = smem;
   unsigned char* q_tiles = smem + STAGES * kBytesP;
-  uint64_t* bars = (uint64_t*)(q_tiles + STAGES * kBytesQ);   // full[STAGES], empty[STAGES], accum
-  uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES + 1);
+  uint64_t* bars = (uint64_t*)(q_tiles + STAGES * kBytesQ);   // full[STAGES], empty[STAGES], accum, received
+  uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES + 2);
   int& is_last = *(int*)(tmem_slot + 1);
-  float* rstd_s = (float*)(tmem_slot + 2);     // [64] 1/rms of each sequence (a norm deferred to here)
+  float* rstd_s = (float*)(tmem_slot + 4);     // [64] 1/rms of each sequence (a norm deferred to here)
   // Clustered narrowest form with at most 8 sequences: what the other blocks of the cluster send,
   // [split][sequence of mine][weight row] (kTcRecvFloats floats, 16-byte aligned)
   float* recv = rstd_s + 64;
@@ -127,15 +128,30 @@ gemm_tc_bf16_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
     tma_prefetch_map(&map_q);
   }
   const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES),
-                 accum_bar = smem_u32(bars + 2 * STAGES);
+                 accum_bar = smem_u32(bars + 2 * STAGES), recv_bar = smem_u32(bars + 2 * STAGES + 1);
+  // The narrowest clustered form with at most kTcPushRows sequences: every block sends its partial
+  // sums of a sequence into the shared memory of the block that owns the sequence, by stores that
+  // count their bytes on a barrier of the owner (st.async); the owner waits for the bytes it
+  // expects and no block waits for the whole cluster.
+  constexpr bool kCanPush = CL && BN == 16;
+  const int push_slots = (prm.rows_q + n_split - 1) / n_split;     // sequences a block owns at most
+  const bool push = kCanPush && n_split * push_slots <= kTcPushRows;
   if (tid == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(full0 + 8 * s, 1);
       mbar_init(empty0 + 8 * s, 1);
     }
     mbar_init(accum_bar, TWO ? 2 : 1);
+    mbar_init(recv_bar, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    if (push) {                                  // the sequences split, split + n_split, ...: 512 bytes from every block each
+      const int mine = prm.rows_q > split ? (prm.rows_q - split + n_split - 1) / n_split : 0;
+      mbar_expect_tx(recv_bar, (uint32_t)(n_split * mine * kTcBM * 4));
+    }
   }
+  // (the barrier exists in every block of the cluster before a store from another block reaches it:
+  // arrive here, wait just before the first such store)
+  if (kCanPush) asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
   if (warp == 0) tmem_alloc(smem_u32(tmem_slot), kTmemCols);
   tc_fence_before();
   __syncthreads();
@@ -324,8 +340,8 @@ gemm_tc_bf16_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
     // multiplying), and after ONE cluster barrier every block has all it needs at home.
     float* red = (float*)smem;
     constexpr int NS = CL ? kTcMaxCluster : 1;
-    const int slots = (prm.rows_q + n_split - 1) / n_split;    // sequences a block owns at most
-    const bool push = CL && BN == 16 && n_split * slots <= kTcPushRows;
+    const int slots = push_slots;
+    if (kCanPush) asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
     if (!failed) {
 #pragma unroll 1
       for (int c0 = 0; c0 < BN && c0 < prm.rows_q; c0 += 16) {
@@ -345,12 +361,18 @@ gemm_tc_bf16_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
       if (!failed) {
         for (int f = tid; f < prm.rows_q * (kTcBM / 4); f += 128) {
           const int m = f / (kTcBM / 4), c = 4 * (f % (kTcBM / 4));
-          st_cluster_f32x4(&recv[(split * slots + m / n_split) * kTcBM + c], (unsigned)(m % n_split),
-                           *reinterpret_cast<const float4*>(&red[m * kTcBM + c]));
+          st_async_f32x4(&recv[(split * slots + m / n_split) * kTcBM + c], (unsigned)(m % n_split),
+                         *reinterpret_cast<const float4*>(&red[m * kTcBM + c]), recv_bar);
         }
       }
+      // what this block owns has arrived when its barrier has counted the bytes (a block that gave
+      // up sends nothing: the others' waits run out and say so)
+      if (!mbar_wait(recv_bar, 0, prm.status, 5) && tid == 0) atomicCAS(prm.status, 0, 5);
+    } else if (CL) {
+      cluster_sync();
+    } else {
+      __syncthreads();
     }
-    if (CL) cluster_sync(); else __syncthreads();
     if (!failed) {
       // One 16-byte load a block of the cluster and thread; all loads of a batch are issued before
       // the first sum.
@@ -652,7 +674,7 @@ static int launch_tc(const CUtensorMap& mp, const CUtensorMap& mq, const TcParam
   constexpr int STAGES = SWAP ? swap_stages(BN) : (BN <= 128 ? 6 : 2);
   // ring, barriers, TMEM slot + flag, 64 row scales, and the receive buffer of the clustered
   // narrowest form; 2 x (this + 1 KB the system keeps) fits an SM's 228 KB
-  constexpr size_t smem = (size_t)STAGES * (kTcBM * kTcBK * 2 + BN * kTcBK * 2) + (2 * STAGES + 1) * 8 + 8 +
+  constexpr size_t smem = (size_t)STAGES * (kTcBM * kTcBK * 2 + BN * kTcBK * 2) + (2 * STAGES + 2) * 8 + 16 +
                           64 * 4 + ((CL && BN == 16) ? kTcPushRows * kTcBM * 4 : 0);
   static_assert(!SWAP || 2 * (smem + 1024) <= 228 * 1024, "two blocks an SM");
   auto kernel = gemm_tc_bf16_kernel<BN, EPI, SWAP, STAGES, CL>;
