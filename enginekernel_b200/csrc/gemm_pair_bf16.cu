@@ -12,7 +12,7 @@
 // tiles, so that the pairs running together share operands in L2).  Roles in a block:
 //   warps 0..7       epilogue: two threads a row (TMEM lane) of the block's half tile, one for
 //                    each half of the tile's columns (warps w and w + 4 reach the same lanes)
-//   warp 8, 1 thread TMA producer of this block's operand halves (ring of kPairStages stages); the
+//   warp 8, 1 thread TMA producer of this block's operand halves (ring of five or six stages); the
 //                    copies of both blocks complete on the FIRST block's barrier
 //   warp 9, 1 thread (first block only) MMA issuer; frees a stage in both blocks and hands a
 //                    finished accumulator to both blocks' epilogues by tcgen05.commit to both
@@ -22,8 +22,10 @@
 // tile's columns j and 128 + j are one output's gate and up); and for the q/k/v product of an
 // attention layer with heads of 128 the per-head RMSNorm of q and k, the rotation by the token's
 // position and the write of k and v into the paged cache (a tile is two whole heads of 256 tokens
-// and a thread holds one token's row of both, so norm and rotation need no exchange; same
-// arithmetic as qk_norm_rope_kv_wide_kernel, on the 32-bit sums, with one rounding).
+// and a thread holds one token's row of one of them, so norm and rotation need no exchange; same
+// arithmetic as qk_norm_rope_kv_wide_kernel, on the 32-bit sums, with one rounding).  That form
+// takes a few neighbouring column tiles of a row tile in a row and keeps the cosines and sines of
+// its 128 tokens' positions in shared memory meanwhile (in place of the ring's sixth stage).
 //
 // Every barrier wait is bounded; a wait that runs out records a code in `status`, the block stops
 // taking tiles, and both blocks of the pair still meet at the end before the tensor memory is
@@ -36,14 +38,26 @@ enum { PAIR_EPI_BF16 = 0, PAIR_EPI_ADD_F32 = 1, PAIR_EPI_SWIGLU = 2, PAIR_EPI_QK
 
 constexpr int kPairRows = 128;                 // rows of x and of w that ONE block stages
 constexpr int kPairTile = 256;                 // the pair's tile: 256 rows of x by 256 rows of w
-constexpr int kPairStages = 6;
+// Stages of the operand ring: six of 32 KB, or five for the q/k/v form, which keeps its tokens' angles
+// in shared memory beside the ring (the sixth stage is worth 1 % to the products).
+__host__ __device__ constexpr int pair_stages(int epi) { return epi == 3 ? 5 : 6; }
 constexpr int kPairThreads = 320;
 constexpr int kPairEpilogueWarps = 8;
 constexpr int kPairGroup = 8;                  // row tiles walked together
 constexpr uint32_t kPairHalfBytes = kPairRows * kTcBK * 2;          // one operand half of a stage
 constexpr uint32_t kPairStageBytes = 2 * kPairHalfBytes;            // x half + w half
 constexpr uint32_t kPairTxBytes = 2 * kPairStageBytes;              // both blocks' copies
-constexpr size_t kPairSmem = (size_t)kPairStages * kPairStageBytes + (2 * kPairStages + 4) * 8 + 16;
+// The q/k/v form's angles: for each of the block's 128 tokens the 64 cosines and 64 sines of its
+// position, rows 4 floats apart from a multiple of 32 so that a warp's 16-byte accesses, a row a lane,
+// meet no bank twice.
+constexpr int kPairTabRow = 132;
+constexpr size_t kPairTabBytes = (size_t)kPairRows * kPairTabRow * 4;
+// barriers: full[S], empty[S], acc_full[2], acc_empty[2], and for each quarter of the rows "angles
+// there" and "angles no longer needed"
+__host__ __device__ constexpr size_t pair_smem(int epi) {
+  return (size_t)pair_stages(epi) * kPairStageBytes + (epi == 3 ? kPairTabBytes : 0) +
+         (2 * pair_stages(epi) + 4 + 8) * 8 + 16;
+}
 
 struct PairParams {
   void* out;          // bfloat16 [M, N] (or [M, N / 2] with SwiGLU), or the 32-bit stream [M, N]
@@ -51,6 +65,7 @@ struct PairParams {
   int M, N;           // rows of x; rows of w (both halves together with SwiGLU)
   int k_blocks;
   int tiles_m, tiles_n, n_pairs;
+  int chunk, n_chunks;  // a pair takes `chunk` neighbouring column tiles of one row tile in a row (a unit)
   int swiglu_half;    // row of w where the up half starts
   int wide;           // rows of `out` (and of the cache pages) are 32-byte aligned
   int* status;
@@ -85,6 +100,14 @@ __device__ __forceinline__ void store_bf16x16(bf16* dst, const float* v, bool wi
     *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
     *reinterpret_cast<uint4*>(dst + 8) = make_uint4(w[4], w[5], w[6], w[7]);
   }
+}
+
+// Eight consecutive floats (32-byte aligned) with one load: a thread of the epilogue reads its own
+// token's row of a table, so a warp's load touches 32 rows, and what that costs is the number of
+// 32-byte sectors asked of L2, not the bytes.
+__device__ __forceinline__ void load_f32x8(const float* p, float4& a, float4& b) {
+  asm volatile("ld.global.nc.v8.f32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=f"(a.x), "=f"(a.y), "=f"(a.z), "=f"(a.w), "=f"(b.x), "=f"(b.y), "=f"(b.z), "=f"(b.w) : "l"(p));
 }
 
 // bfloat16 x bfloat16 -> float, both K-major, M = 256 over the pair, N = 256.
@@ -167,31 +190,37 @@ __device__ __forceinline__ uint32_t mma_stage_pair(uint32_t d_tmem, uint64_t da,
   return ready;
 }
 
-// The i-th tile of the list: row tiles in groups of kPairGroup, inside a group the row tile runs
-// fastest, so that pairs working side by side share rows of x and of w.
-__device__ __forceinline__ void pair_tile(const PairParams& prm, int t, int& tile_m, int& tile_n) {
-  const int per_group = kPairGroup * prm.tiles_n;
-  const int g = t / per_group, r = t - g * per_group;
+// The u-th unit of the list: a row tile and a chunk of `chunk` neighbouring column tiles.  Row tiles
+// go in groups of kPairGroup, inside a group the row tile runs fastest, so that pairs working side by
+// side share rows of x and of w.  (With chunk = 1 a unit is a tile.)
+__device__ __forceinline__ void pair_unit(const PairParams& prm, int u, int& tile_m, int& chunk_n) {
+  const int per_group = kPairGroup * prm.n_chunks;
+  const int g = u / per_group, r = u - g * per_group;
   const int rows = min(kPairGroup, prm.tiles_m - g * kPairGroup);
-  tile_n = r / rows;
-  tile_m = g * kPairGroup + (r - tile_n * rows);
+  chunk_n = r / rows;
+  tile_m = g * kPairGroup + (r - chunk_n * rows);
 }
 
 template <int EPI>
 __global__ void __launch_bounds__(kPairThreads, 1)
 gemm_pair_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                       const PairParams prm) {
+  constexpr int kPairStages = pair_stages(EPI);
   extern __shared__ __align__(1024) unsigned char smem[];
-  uint64_t* bars = (uint64_t*)(smem + (size_t)kPairStages * kPairStageBytes);
-  // full[S] (used in the first block), empty[S], acc_full[2], acc_empty[2] (used in the first block)
+  float* tab = (float*)(smem + (size_t)kPairStages * kPairStageBytes);          // (q/k/v form only)
+  uint64_t* bars = (uint64_t*)(smem + (size_t)kPairStages * kPairStageBytes +
+                               (EPI == PAIR_EPI_QKV_ROPE ? kPairTabBytes : 0));
+  // full[S] (used in the first block), empty[S], acc_full[2], acc_empty[2] (used in the first block),
+  // tab_full[4], tab_free[4]
   const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + kPairStages),
-                 acc_full0 = smem_u32(bars + 2 * kPairStages), acc_empty0 = smem_u32(bars + 2 * kPairStages + 2);
-  uint32_t* tmem_slot = (uint32_t*)(bars + 2 * kPairStages + 4);
+                 acc_full0 = smem_u32(bars + 2 * kPairStages), acc_empty0 = smem_u32(bars + 2 * kPairStages + 2),
+                 tab_full0 = smem_u32(bars + 2 * kPairStages + 4), tab_free0 = smem_u32(bars + 2 * kPairStages + 8);
+  uint32_t* tmem_slot = (uint32_t*)(bars + 2 * kPairStages + 12);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const uint32_t rank = cluster_rank();
   const int pair = blockIdx.x >> 1;
-  const int n_tiles = prm.tiles_m * prm.tiles_n;
+  const int n_units = prm.tiles_m * prm.n_chunks;
 
   if (tid == 0) {
     tma_prefetch_map(&map_x);
@@ -204,6 +233,7 @@ gemm_pair_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
       mbar_init(acc_full0 + 8 * b, 1);
       mbar_init(acc_empty0 + 8 * b, 2 * kPairEpilogueWarps);   // a lane of each epilogue warp of both blocks
     }
+    for (int q = 0; q < 8; ++q) mbar_init(tab_full0 + 8 * q, 2);   // the two warps that share a quarter of the rows
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == kPairEpilogueWarps) tmem_alloc_pair(smem_u32(tmem_slot), 512);
@@ -222,10 +252,13 @@ gemm_pair_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
     // ------------------------------------------------------------------ TMA producer
     const uint32_t full_first = map_to_rank(full0, 0);       // the first block's barriers
     int c = 0;                                                // stage fillings so far
-    for (int t = pair; t < n_tiles && ok; t += prm.n_pairs) {
-      int tile_m, tile_n;
-      pair_tile(prm, t, tile_m, tile_n);
+    for (int u = pair; u < n_units && ok; u += prm.n_pairs) {
+      int tile_m, chunk_n;
+      pair_unit(prm, u, tile_m, chunk_n);
       const int x_row = tile_m * kPairTile + (int)rank * kPairRows;
+      for (int j = 0; j < prm.chunk && ok; ++j) {
+      const int tile_n = chunk_n * prm.chunk + j;
+      if (tile_n >= prm.tiles_n) break;
       const int w_row = EPI == PAIR_EPI_SWIGLU ? (int)rank * prm.swiglu_half + tile_n * kPairRows
                                                : tile_n * kPairTile + (int)rank * kPairRows;
       for (int kb = 0; kb < prm.k_blocks; ++kb, ++c) {
@@ -239,6 +272,7 @@ gemm_pair_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
         tma_load_2d_pair(dst, &map_x, kb * kTcBK, x_row, full_first + 8 * s);
         tma_load_2d_pair(dst + kPairHalfBytes, &map_w, kb * kTcBK, w_row, full_first + 8 * s);
       }
+      }
     }
   } else if (tid == 32 * (kPairEpilogueWarps + 1) && rank == 0) {
     // ------------------------------------------------------------------ MMA issuer (first block)
@@ -251,7 +285,10 @@ gemm_pair_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
     const uint32_t stage0 = smem_u32(smem);
     int c = 0, i = 0;                          // stages consumed, tiles done
     uint32_t ready = 0;                        // the stage c is known to be full
-    for (int t = pair; t < n_tiles && ok; t += prm.n_pairs, ++i) {
+    for (int u = pair; u < n_units && ok; u += prm.n_pairs) {
+      int tile_m, chunk_n;
+      pair_unit(prm, u, tile_m, chunk_n);
+      for (int j = 0; j < prm.chunk && ok && chunk_n * prm.chunk + j < prm.tiles_n; ++j, ++i) {
       const int buf = i & 1;
       if (i >= 2) {                            // the epilogues of tile i - 2 have read this accumulator
         ok = mbar_wait(acc_empty0 + 8 * buf, ((i >> 1) & 1) ^ 1, prm.status, 42);
@@ -275,49 +312,64 @@ gemm_pair_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
       }
       if (!ok) break;
       tc_commit_pair(acc_full0 + 8 * buf);     // the tile's accumulator is complete in both blocks
+      }
     }
   } else if (warp < kPairEpilogueWarps) {
     // ------------------------------------------------------------------ epilogue
     const uint32_t acc_empty_first = map_to_rank(acc_empty0, 0);
     const int quarter = warp & 3, side = warp >> 2;       // lanes 32 quarter ..., columns' half
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
-    int i = 0;
-    for (int t = pair; t < n_tiles && ok; t += prm.n_pairs, ++i) {
-      int tile_m, tile_n;
-      pair_tile(prm, t, tile_m, tile_n);
-      const int buf = i & 1;
+    int i = 0, units = 0;
+    for (int u = pair; u < n_units && ok; u += prm.n_pairs, ++units) {
+      int tile_m, chunk_n;
+      pair_unit(prm, u, tile_m, chunk_n);
       const int m = tile_m * kPairTile + (int)rank * kPairRows + quarter * 32 + lane;
-      // q/k/v form: the token's position, cache page and angles do not depend on the accumulator, so
-      // they are asked for before the wait for it (three dependent rounds of loads otherwise stand
-      // between the accumulator and its first store)
-      int pos = -1;
+      // q/k/v form: what depends on the token alone is fetched once for the unit's column tiles - its
+      // position, its cache page, and the cosines and sines of its position, which go to shared
+      // memory: the two warps that share these 32 rows (one head each) bring one table each and use
+      // both.  (Fetched per head and tile by every thread, a row a lane, the angles were a third of the
+      // launch: 512 bytes for each of 24 to 40 heads of every token, asked of L2 sector by sector.)
+      int pos = -1, page = 0;
+      float* my_tab = tab + (size_t)(quarter * 32 + lane) * kPairTabRow;
+      if (EPI == PAIR_EPI_QKV_ROPE) {
+        pos = m < prm.M ? prm.positions[m] : -1;
+        if (pos >= 0 && prm.write_kv)
+          page = prm.cache.block_table[(size_t)prm.slots[m] * prm.cache.table_stride + pos / EK_PAGE];
+        // the angles of the unit before are no longer read by either warp
+        if (units > 0) ok = mbar_wait(tab_free0 + 8 * quarter, (units - 1) & 1, prm.status, 45);
+        if (!ok) break;
+        if (pos >= 0) {
+          const float* src = (side == 0 ? prm.cos_tab : prm.sin_tab) + (size_t)pos * 64;
+          float* to = my_tab + 64 * side;
+#pragma unroll
+          for (int e = 0; e < 64; e += 8) {
+            float4 a, b;
+            load_f32x8(src + e, a, b);
+            *reinterpret_cast<float4*>(to + e) = a;
+            *reinterpret_cast<float4*>(to + e + 4) = b;
+          }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(tab_full0 + 8 * quarter);
+        ok = mbar_wait(tab_full0 + 8 * quarter, units & 1, prm.status, 46);
+        if (!ok) break;
+      }
+      for (int j = 0; j < prm.chunk && ok && chunk_n * prm.chunk + j < prm.tiles_n; ++j, ++i) {
+      const int tile_n = chunk_n * prm.chunk + j;
+      const int buf = i & 1;
       bf16* dst = nullptr;
       bool is_q = false, is_k = false, is_v = false;
-      const float* cs = nullptr;
-      const float* sn = nullptr;
-      float4 c4[4], s4[4];                      // the angles of the head's first 16 pairs
       if (EPI == PAIR_EPI_QKV_ROPE) {
         const int n_kv = prm.cache.heads, nq = prm.n_q_heads;
         const int head = 2 * tile_n + side;     // columns 0..127 of the tile: warps 0..3; 128..255: warps 4..7
         is_q = head < nq;
         is_k = !is_q && head < nq + n_kv;
         is_v = !is_q && !is_k && head < nq + 2 * n_kv;
-        pos = m < prm.M ? prm.positions[m] : -1;
         if (is_q) {
           dst = (bf16*)prm.out + (size_t)m * prm.ldo + (size_t)head * 128;
         } else if ((is_k || is_v) && prm.write_kv && pos >= 0) {
-          const int page = prm.cache.block_table[(size_t)prm.slots[m] * prm.cache.table_stride + pos / EK_PAGE];
           const int kv_head = is_k ? head - nq : head - nq - n_kv;
           dst = (bf16*)(is_k ? prm.cache.k : prm.cache.v) + page_offset(prm.cache, page, kv_head, pos);
-        }
-        if (is_q || (is_k && prm.write_kv)) {
-          cs = prm.cos_tab + (size_t)max(pos, 0) * 64;
-          sn = prm.sin_tab + (size_t)max(pos, 0) * 64;
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            c4[e] = *reinterpret_cast<const float4*>(cs + 4 * e);
-            s4[e] = *reinterpret_cast<const float4*>(sn + 4 * e);
-          }
         }
       }
       ok = mbar_wait(acc_full0 + 8 * buf, (i >> 1) & 1, prm.status, 44);
@@ -381,14 +433,6 @@ gemm_pair_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
           }
 #pragma unroll
           for (int c0 = 0; c0 < 64; c0 += 16) {
-            float4 cn[4], sx[4];                  // the next 16 pairs' angles fly under this step
-            if (c0 + 16 < 64) {
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                cn[e] = *reinterpret_cast<const float4*>(cs + c0 + 16 + 4 * e);
-                sx[e] = *reinterpret_cast<const float4*>(sn + c0 + 16 + 4 * e);
-              }
-            }
 #pragma unroll
             for (int e = 0; e < 16; e += 4) {
               float4 gl = make_float4(rstd, rstd, rstd, rstd), gh = gl;
@@ -398,25 +442,19 @@ gemm_pair_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
                 gl = make_float4(a.x * rstd, a.y * rstd, a.z * rstd, a.w * rstd);
                 gh = make_float4(b.x * rstd, b.y * rstd, b.z * rstd, b.w * rstd);
               }
-              const float4 cc = c4[e / 4], sv = s4[e / 4];
+              const float4 cc = *reinterpret_cast<const float4*>(my_tab + c0 + e);
+              const float4 sv = *reinterpret_cast<const float4*>(my_tab + 64 + c0 + e);
               const float cv[4] = {cc.x, cc.y, cc.z, cc.w}, sw[4] = {sv.x, sv.y, sv.z, sv.w};
               const float g0[4] = {gl.x, gl.y, gl.z, gl.w}, g1[4] = {gh.x, gh.y, gh.z, gh.w};
 #pragma unroll
-              for (int i = 0; i < 4; ++i) {
-                const float x = v[c0 + e + i] * g0[i], y = v[64 + c0 + e + i] * g1[i];   // gain * x / rms
-                v[c0 + e + i] = x * cv[i] - y * sw[i];
-                v[64 + c0 + e + i] = y * cv[i] + x * sw[i];
+              for (int i2 = 0; i2 < 4; ++i2) {
+                const float x = v[c0 + e + i2] * g0[i2], y = v[64 + c0 + e + i2] * g1[i2];   // gain * x / rms
+                v[c0 + e + i2] = x * cv[i2] - y * sw[i2];
+                v[64 + c0 + e + i2] = y * cv[i2] + x * sw[i2];
               }
             }
             store_bf16x16(dst + c0, v + c0, prm.wide);
             store_bf16x16(dst + 64 + c0, v + 64 + c0, prm.wide);
-            if (c0 + 16 < 64) {
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                c4[e] = cn[e];
-                s4[e] = sx[e];
-              }
-            }
           }
         }
       } else {
@@ -465,6 +503,11 @@ gemm_pair_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
           }
         }
       }
+      }                                        // the unit's column tiles
+      if (EPI == PAIR_EPI_QKV_ROPE && ok) {      // this warp has read the unit's angles for the last time
+        __syncwarp();
+        if (lane == 0) mbar_arrive(tab_free0 + 8 * quarter);
+      }
     }
   }
 
@@ -486,7 +529,7 @@ static int launch_pair(const CUtensorMap& mx, const CUtensorMap& mw, PairParams 
   if (device < 0 || device >= kMaxDevices) return EK_ERR_ARG;
   cudaLaunchConfig_t cfg = {};
   cfg.blockDim = dim3(kPairThreads);
-  cfg.dynamicSmemBytes = kPairSmem;
+  cfg.dynamicSmemBytes = pair_smem(EPI);
   cfg.stream = stream;
   cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -497,7 +540,7 @@ static int launch_pair(const CUtensorMap& mx, const CUtensorMap& mw, PairParams 
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   if (pairs_that_fit[device] == 0) {
-    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kPairSmem);
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pair_smem(EPI));
     if (e != cudaSuccess) return (int)e;
     prefer_carveout((const void*)kernel, 100);
     // how many pairs the device holds at once (not every SM need have a free neighbour)
@@ -509,8 +552,23 @@ static int launch_pair(const CUtensorMap& mx, const CUtensorMap& mw, PairParams 
     if (clusters < 1) return EK_ERR_ARG;
     pairs_that_fit[device] = clusters;
   }
-  const int n_tiles = prm.tiles_m * prm.tiles_n;
-  prm.n_pairs = n_tiles < pairs_that_fit[device] ? n_tiles : pairs_that_fit[device];
+  // Units of work: the q/k/v form takes a few neighbouring column tiles of a row tile in a row, so that
+  // what it fetches per token serves them all, and still leaves about eight units a row tile to deal out
+  prm.chunk = 1;
+  if (EPI == PAIR_EPI_QKV_ROPE) {
+    // rounds of units x (a unit's K blocks + what its fetch of the angles costs, about five K blocks'
+    // time), for the chunk sizes that leave at least two units a row tile
+    long long best = -1;
+    for (int c = 1; c <= 8 && 2 * c <= prm.tiles_n + c - 1; ++c) {
+      const long long units = (long long)prm.tiles_m * ((prm.tiles_n + c - 1) / c);
+      const long long rounds = (units + pairs_that_fit[device] - 1) / pairs_that_fit[device];
+      const long long cost = rounds * ((long long)c * prm.k_blocks + 5);
+      if (best < 0 || cost < best) { best = cost; prm.chunk = c; }
+    }
+  }
+  prm.n_chunks = (prm.tiles_n + prm.chunk - 1) / prm.chunk;
+  const int n_units = prm.tiles_m * prm.n_chunks;
+  prm.n_pairs = n_units < pairs_that_fit[device] ? n_units : pairs_that_fit[device];
   cfg.gridDim = dim3(2 * prm.n_pairs);
   cfg.numAttrs = 2;
   return (int)cudaLaunchKernelEx(&cfg, kernel, mx, mw, prm);
@@ -562,8 +620,8 @@ EK_EXPORT int ek_gemm_pair_qkv_rope(void* out, const void* x, const void* w, int
   if (M <= 0) return 0;
   if (K <= 0 || K % 8 || ldx % 8 || ldw % 8 || ldo % 8 || !status || n_q_heads <= 0 || n_kv_heads <= 0 ||
       !positions || !token_slot || !cos_tab || !sin_tab || !k_pages || !v_pages || !block_table ||
-      ((uintptr_t)x & 15) || ((uintptr_t)w & 15) || ((uintptr_t)out & 15) || ((uintptr_t)cos_tab & 15) ||
-      ((uintptr_t)sin_tab & 15) || ((uintptr_t)q_gain & 15) || ((uintptr_t)k_gain & 15) ||
+      ((uintptr_t)x & 15) || ((uintptr_t)w & 15) || ((uintptr_t)out & 15) || ((uintptr_t)cos_tab & 31) ||
+      ((uintptr_t)sin_tab & 31) || ((uintptr_t)q_gain & 15) || ((uintptr_t)k_gain & 15) ||
       ((uintptr_t)k_pages & 15) || ((uintptr_t)v_pages & 15))
     return EK_ERR_ARG;
   PairParams prm{};
