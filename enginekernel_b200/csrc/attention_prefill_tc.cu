@@ -316,6 +316,7 @@ attention_prefill_tc_kernel(bf16* __restrict__ out, const __grid_constant__ CUte
   if (!failed) {
     if (tid < kFaRows) {                           // whole warps: tcgen05.ld is warp-wide
       const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+      const bool wide_out = ((uintptr_t)out & 31) == 0;     // rows of D values are then 32-byte aligned
       const int row = min(r, n_rows - 1);
       bf16* o = out + ((size_t)(t_first + row / group) * n_q_heads + kv_head * group + row % group) * D;
 #pragma unroll
@@ -325,14 +326,20 @@ attention_prefill_tc_kernel(bf16* __restrict__ out, const __grid_constant__ CUte
         tmem_ld_wait();
         if (r < n_rows) {
 #pragma unroll
-          for (int j = 0; j < 32; j += 8) {
-            uint32_t w[4];
+          for (int j = 0; j < 32; j += 16) {     // 32 bytes a store: whole sectors of L2, a row a lane
+            uint32_t w[8];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
+            for (int i = 0; i < 8; ++i) {
               __nv_bfloat162 h = __floats2bfloat162_rn(v[j + 2 * i] * inv, v[j + 2 * i + 1] * inv);
               w[i] = *reinterpret_cast<uint32_t*>(&h);
             }
-            *reinterpret_cast<uint4*>(o + c + j) = make_uint4(w[0], w[1], w[2], w[3]);
+            if (wide_out) {
+              asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(o + c + j), "r"(w[0]),
+                           "r"(w[1]), "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]) : "memory");
+            } else {
+              *reinterpret_cast<uint4*>(o + c + j) = make_uint4(w[0], w[1], w[2], w[3]);
+              *reinterpret_cast<uint4*>(o + c + j + 8) = make_uint4(w[4], w[5], w[6], w[7]);
+            }
           }
         }
       }
