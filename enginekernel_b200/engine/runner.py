@@ -87,9 +87,9 @@ class PlanBuffers:
 
 # Tokens one pass over the model takes at most; a step that brings more is cut into pieces.  Bigger
 # pieces fill the GPU better (Qwen3-0.6B shape, 64 prompts of 7,936 tokens: 1,048 ms to the first
-# token with pieces of 8,192, 986 ms with 32,768); the workspaces grow with them (about 100 KB a
-# token at the Qwen3-4B shape).
-DEFAULT_MAX_STEP_TOKENS = 32768
+# token with pieces of 8,192, 931 ms with 32,768, 920 ms with 65,536, 916 ms with 131,072); the
+# workspaces grow with the largest piece that is actually run (about 100 KB a token at the Qwen3-4B shape).
+DEFAULT_MAX_STEP_TOKENS = 65536
 
 
 class ModelRunner:
