@@ -257,21 +257,21 @@ gemm_pair_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
       pair_unit(prm, u, tile_m, chunk_n);
       const int x_row = tile_m * kPairTile + (int)rank * kPairRows;
       for (int j = 0; j < prm.chunk && ok; ++j) {
-      const int tile_n = chunk_n * prm.chunk + j;
-      if (tile_n >= prm.tiles_n) break;
-      const int w_row = EPI == PAIR_EPI_SWIGLU ? (int)rank * prm.swiglu_half + tile_n * kPairRows
-                                               : tile_n * kPairTile + (int)rank * kPairRows;
-      for (int kb = 0; kb < prm.k_blocks; ++kb, ++c) {
-        const int s = c % kPairStages;
-        if (c >= kPairStages) {
-          ok = mbar_wait(empty0 + 8 * s, ((c / kPairStages) & 1) ^ 1, prm.status, 41);
-          if (!ok) break;
+        const int tile_n = chunk_n * prm.chunk + j;
+        if (tile_n >= prm.tiles_n) break;
+        const int w_row = EPI == PAIR_EPI_SWIGLU ? (int)rank * prm.swiglu_half + tile_n * kPairRows
+                                                 : tile_n * kPairTile + (int)rank * kPairRows;
+        for (int kb = 0; kb < prm.k_blocks; ++kb, ++c) {
+          const int s = c % kPairStages;
+          if (c >= kPairStages) {
+            ok = mbar_wait(empty0 + 8 * s, ((c / kPairStages) & 1) ^ 1, prm.status, 41);
+            if (!ok) break;
+          }
+          if (rank == 0) mbar_expect_tx(full0 + 8 * s, kPairTxBytes);
+          const uint32_t dst = smem_u32(smem + (size_t)s * kPairStageBytes);
+          tma_load_2d_pair(dst, &map_x, kb * kTcBK, x_row, full_first + 8 * s);
+          tma_load_2d_pair(dst + kPairHalfBytes, &map_w, kb * kTcBK, w_row, full_first + 8 * s);
         }
-        if (rank == 0) mbar_expect_tx(full0 + 8 * s, kPairTxBytes);
-        const uint32_t dst = smem_u32(smem + (size_t)s * kPairStageBytes);
-        tma_load_2d_pair(dst, &map_x, kb * kTcBK, x_row, full_first + 8 * s);
-        tma_load_2d_pair(dst + kPairHalfBytes, &map_w, kb * kTcBK, w_row, full_first + 8 * s);
-      }
       }
     }
   } else if (tid == 32 * (kPairEpilogueWarps + 1) && rank == 0) {
@@ -289,29 +289,29 @@ gemm_pair_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
       int tile_m, chunk_n;
       pair_unit(prm, u, tile_m, chunk_n);
       for (int j = 0; j < prm.chunk && ok && chunk_n * prm.chunk + j < prm.tiles_n; ++j, ++i) {
-      const int buf = i & 1;
-      if (i >= 2) {                            // the epilogues of tile i - 2 have read this accumulator
-        ok = mbar_wait(acc_empty0 + 8 * buf, ((i >> 1) & 1) ^ 1, prm.status, 42);
-        if (!ok) break;
-        tc_fence_after();
-      }
-      const uint32_t acc = tmem_base + (uint32_t)(buf * kPairTile);
-      for (int kb = 0; kb < prm.k_blocks; ++kb, ++c) {
-        const int s = c % kPairStages;
-        if (!ready) {
-          ok = mbar_wait(full0 + 8 * s, (c / kPairStages) & 1, prm.status, 43);
+        const int buf = i & 1;
+        if (i >= 2) {                            // the epilogues of tile i - 2 have read this accumulator
+          ok = mbar_wait(acc_empty0 + 8 * buf, ((i >> 1) & 1) ^ 1, prm.status, 42);
           if (!ok) break;
+          tc_fence_after();
         }
-        tc_fence_after();
-        const int s_next = (c + 1) % kPairStages;
-        const uint32_t base = stage0 + (uint32_t)s * kPairStageBytes;
-        static_assert(kTcBK == 64, "mma_stage_pair issues four MMAs of K = 16");
-        ready = mma_stage_pair(acc, smem_desc_k_sw128(base), smem_desc_k_sw128(base + kPairHalfBytes), idesc,
-                               kb ? 1u : 0u, empty0 + 8 * s, full0 + 8 * s_next,
-                               ((c + 1) / kPairStages) & 1);
-      }
-      if (!ok) break;
-      tc_commit_pair(acc_full0 + 8 * buf);     // the tile's accumulator is complete in both blocks
+        const uint32_t acc = tmem_base + (uint32_t)(buf * kPairTile);
+        for (int kb = 0; kb < prm.k_blocks; ++kb, ++c) {
+          const int s = c % kPairStages;
+          if (!ready) {
+            ok = mbar_wait(full0 + 8 * s, (c / kPairStages) & 1, prm.status, 43);
+            if (!ok) break;
+          }
+          tc_fence_after();
+          const int s_next = (c + 1) % kPairStages;
+          const uint32_t base = stage0 + (uint32_t)s * kPairStageBytes;
+          static_assert(kTcBK == 64, "mma_stage_pair issues four MMAs of K = 16");
+          ready = mma_stage_pair(acc, smem_desc_k_sw128(base), smem_desc_k_sw128(base + kPairHalfBytes), idesc,
+                                 kb ? 1u : 0u, empty0 + 8 * s, full0 + 8 * s_next,
+                                 ((c + 1) / kPairStages) & 1);
+        }
+        if (!ok) break;
+        tc_commit_pair(acc_full0 + 8 * buf);     // the tile's accumulator is complete in both blocks
       }
     }
   } else if (warp < kPairEpilogueWarps) {
@@ -355,154 +355,154 @@ gemm_pair_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
         if (!ok) break;
       }
       for (int j = 0; j < prm.chunk && ok && chunk_n * prm.chunk + j < prm.tiles_n; ++j, ++i) {
-      const int tile_n = chunk_n * prm.chunk + j;
-      const int buf = i & 1;
-      bf16* dst = nullptr;
-      bool is_q = false, is_k = false, is_v = false;
-      if (EPI == PAIR_EPI_QKV_ROPE) {
-        const int n_kv = prm.cache.heads, nq = prm.n_q_heads;
-        const int head = 2 * tile_n + side;     // columns 0..127 of the tile: warps 0..3; 128..255: warps 4..7
-        is_q = head < nq;
-        is_k = !is_q && head < nq + n_kv;
-        is_v = !is_q && !is_k && head < nq + 2 * n_kv;
-        if (is_q) {
-          dst = (bf16*)prm.out + (size_t)m * prm.ldo + (size_t)head * 128;
-        } else if ((is_k || is_v) && prm.write_kv && pos >= 0) {
-          const int kv_head = is_k ? head - nq : head - nq - n_kv;
-          dst = (bf16*)(is_k ? prm.cache.k : prm.cache.v) + page_offset(prm.cache, page, kv_head, pos);
+        const int tile_n = chunk_n * prm.chunk + j;
+        const int buf = i & 1;
+        bf16* dst = nullptr;
+        bool is_q = false, is_k = false, is_v = false;
+        if (EPI == PAIR_EPI_QKV_ROPE) {
+          const int n_kv = prm.cache.heads, nq = prm.n_q_heads;
+          const int head = 2 * tile_n + side;     // columns 0..127 of the tile: warps 0..3; 128..255: warps 4..7
+          is_q = head < nq;
+          is_k = !is_q && head < nq + n_kv;
+          is_v = !is_q && !is_k && head < nq + 2 * n_kv;
+          if (is_q) {
+            dst = (bf16*)prm.out + (size_t)m * prm.ldo + (size_t)head * 128;
+          } else if ((is_k || is_v) && prm.write_kv && pos >= 0) {
+            const int kv_head = is_k ? head - nq : head - nq - n_kv;
+            dst = (bf16*)(is_k ? prm.cache.k : prm.cache.v) + page_offset(prm.cache, page, kv_head, pos);
+          }
         }
-      }
-      ok = mbar_wait(acc_full0 + 8 * buf, (i >> 1) & 1, prm.status, 44);
-      if (!ok) break;
-      tc_fence_after();
-      const uint32_t acc = lane_addr + (uint32_t)(buf * kPairTile);
-      // This thread's 128 columns of the accumulator in one go (one wait for tensor memory instead of
-      // one a chunk: with the MMAs of the next tile running, each such wait takes about a microsecond),
-      // then the accumulator is handed back and the rest works from registers.
-      float v[128];
-      {
-        const uint32_t first = EPI == PAIR_EPI_SWIGLU ? acc + (uint32_t)(side * 64) : acc + (uint32_t)(side * 128);
-        tmem_ld32_nowait(first, v);
-        tmem_ld32_nowait(first + 32, v + 32);
-        if (EPI == PAIR_EPI_SWIGLU) {            // gate columns 64 side .. + 63, then their up columns
-          tmem_ld32_nowait(first + 128, v + 64);
-          tmem_ld32_nowait(first + 160, v + 96);
-        } else {
-          tmem_ld32_nowait(first + 64, v + 64);
-          tmem_ld32_nowait(first + 96, v + 96);
+        ok = mbar_wait(acc_full0 + 8 * buf, (i >> 1) & 1, prm.status, 44);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t acc = lane_addr + (uint32_t)(buf * kPairTile);
+        // This thread's 128 columns of the accumulator in one go (one wait for tensor memory instead of
+        // one a chunk: with the MMAs of the next tile running, each such wait takes about a microsecond),
+        // then the accumulator is handed back and the rest works from registers.
+        float v[128];
+        {
+          const uint32_t first = EPI == PAIR_EPI_SWIGLU ? acc + (uint32_t)(side * 64) : acc + (uint32_t)(side * 128);
+          tmem_ld32_nowait(first, v);
+          tmem_ld32_nowait(first + 32, v + 32);
+          if (EPI == PAIR_EPI_SWIGLU) {            // gate columns 64 side .. + 63, then their up columns
+            tmem_ld32_nowait(first + 128, v + 64);
+            tmem_ld32_nowait(first + 160, v + 96);
+          } else {
+            tmem_ld32_nowait(first + 64, v + 64);
+            tmem_ld32_nowait(first + 96, v + 96);
+          }
+          tmem_ld_wait();
         }
-        tmem_ld_wait();
-      }
-      tc_fence_before();                       // read: the MMAs of tile i + 2 may overwrite the accumulator
-      __syncwarp();
-      if (lane == 0) mbar_arrive_cluster(acc_empty_first + 8 * buf);
+        tc_fence_before();                       // read: the MMAs of tile i + 2 may overwrite the accumulator
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(acc_empty_first + 8 * buf);
 
-      if (EPI == PAIR_EPI_SWIGLU) {
-        const int n0 = tile_n * kPairRows + side * 64;     // this thread's outputs: n0 .. n0 + 63
-        bf16* o = (bf16*)prm.out + (size_t)m * prm.ldo + n0;
-        if (m < prm.M) {
+        if (EPI == PAIR_EPI_SWIGLU) {
+          const int n0 = tile_n * kPairRows + side * 64;     // this thread's outputs: n0 .. n0 + 63
+          bf16* o = (bf16*)prm.out + (size_t)m * prm.ldo + n0;
+          if (m < prm.M) {
 #pragma unroll
-          for (int c0 = 0; c0 < 64; c0 += 16) {
+            for (int c0 = 0; c0 < 64; c0 += 16) {
 #pragma unroll
-            for (int e = 0; e < 16; ++e)
-              v[c0 + e] = __fdividef(v[c0 + e], 1.f + __expf(-v[c0 + e])) * v[64 + c0 + e];
-            if (n0 + c0 + 16 <= prm.swiglu_half) {
-              store_bf16x16(o + c0, v + c0, prm.wide);
-            } else {
               for (int e = 0; e < 16; ++e)
-                if (n0 + c0 + e < prm.swiglu_half) o[c0 + e] = __float2bfloat16_rn(v[c0 + e]);
-            }
-          }
-        }
-      } else if (EPI == PAIR_EPI_QKV_ROPE) {
-        // the tile holds two heads of this thread's token, one for each half of the epilogue warps
-        const bool store = pos >= 0 && dst != nullptr;
-        if (is_v && prm.write_kv) {               // values: rounded and stored
-          if (store) {
-#pragma unroll
-            for (int c0 = 0; c0 < 128; c0 += 16) store_bf16x16(dst + c0, v + c0, prm.wide);
-          }
-        } else if (store && (is_q || is_k)) {
-          const float* gain = is_q ? prm.q_gain : prm.k_gain;
-          float rstd = 1.f;
-          if (gain) {
-            float ss[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-            for (int e = 0; e < 128; ++e) ss[e & 3] = fmaf(v[e], v[e], ss[e & 3]);
-            rstd = rsqrtf(((ss[0] + ss[1]) + (ss[2] + ss[3])) * (1.f / 128.f) + prm.qk_eps);
-          }
-#pragma unroll
-          for (int c0 = 0; c0 < 64; c0 += 16) {
-#pragma unroll
-            for (int e = 0; e < 16; e += 4) {
-              float4 gl = make_float4(rstd, rstd, rstd, rstd), gh = gl;
-              if (gain) {
-                const float4 a = *reinterpret_cast<const float4*>(gain + c0 + e);
-                const float4 b = *reinterpret_cast<const float4*>(gain + 64 + c0 + e);
-                gl = make_float4(a.x * rstd, a.y * rstd, a.z * rstd, a.w * rstd);
-                gh = make_float4(b.x * rstd, b.y * rstd, b.z * rstd, b.w * rstd);
-              }
-              const float4 cc = *reinterpret_cast<const float4*>(my_tab + c0 + e);
-              const float4 sv = *reinterpret_cast<const float4*>(my_tab + 64 + c0 + e);
-              const float cv[4] = {cc.x, cc.y, cc.z, cc.w}, sw[4] = {sv.x, sv.y, sv.z, sv.w};
-              const float g0[4] = {gl.x, gl.y, gl.z, gl.w}, g1[4] = {gh.x, gh.y, gh.z, gh.w};
-#pragma unroll
-              for (int i2 = 0; i2 < 4; ++i2) {
-                const float x = v[c0 + e + i2] * g0[i2], y = v[64 + c0 + e + i2] * g1[i2];   // gain * x / rms
-                v[c0 + e + i2] = x * cv[i2] - y * sw[i2];
-                v[64 + c0 + e + i2] = y * cv[i2] + x * sw[i2];
+                v[c0 + e] = __fdividef(v[c0 + e], 1.f + __expf(-v[c0 + e])) * v[64 + c0 + e];
+              if (n0 + c0 + 16 <= prm.swiglu_half) {
+                store_bf16x16(o + c0, v + c0, prm.wide);
+              } else {
+                for (int e = 0; e < 16; ++e)
+                  if (n0 + c0 + e < prm.swiglu_half) o[c0 + e] = __float2bfloat16_rn(v[c0 + e]);
               }
             }
-            store_bf16x16(dst + c0, v + c0, prm.wide);
-            store_bf16x16(dst + 64 + c0, v + 64 + c0, prm.wide);
           }
-        }
-      } else {
-        const int n0 = tile_n * kPairTile + side * 128;     // this thread's columns: n0 .. n0 + 127
-        if (m < prm.M) {
+        } else if (EPI == PAIR_EPI_QKV_ROPE) {
+          // the tile holds two heads of this thread's token, one for each half of the epilogue warps
+          const bool store = pos >= 0 && dst != nullptr;
+          if (is_v && prm.write_kv) {               // values: rounded and stored
+            if (store) {
 #pragma unroll
-          for (int c0 = 0; c0 < 128; c0 += 32) {
-            if (n0 + c0 >= prm.N) break;
-            if (EPI == PAIR_EPI_ADD_F32) {
-              float* o = (float*)prm.out + (size_t)m * prm.ldo + n0 + c0;
-              if (n0 + c0 + 32 <= prm.N && prm.wide) {
-                float old[32];
+              for (int c0 = 0; c0 < 128; c0 += 16) store_bf16x16(dst + c0, v + c0, prm.wide);
+            }
+          } else if (store && (is_q || is_k)) {
+            const float* gain = is_q ? prm.q_gain : prm.k_gain;
+            float rstd = 1.f;
+            if (gain) {
+              float ss[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-                for (int j = 0; j < 32; j += 8)
-                  asm volatile("ld.global.v8.f32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
-                               : "=f"(old[j]), "=f"(old[j + 1]), "=f"(old[j + 2]), "=f"(old[j + 3]), "=f"(old[j + 4]),
-                                 "=f"(old[j + 5]), "=f"(old[j + 6]), "=f"(old[j + 7]) : "l"(o + j) : "memory");
+              for (int e = 0; e < 128; ++e) ss[e & 3] = fmaf(v[e], v[e], ss[e & 3]);
+              rstd = rsqrtf(((ss[0] + ss[1]) + (ss[2] + ss[3])) * (1.f / 128.f) + prm.qk_eps);
+            }
 #pragma unroll
-                for (int j = 0; j < 32; j += 8)
-                  asm volatile("st.global.v8.f32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(o + j),
-                               "f"(old[j] + v[c0 + j]), "f"(old[j + 1] + v[c0 + j + 1]), "f"(old[j + 2] + v[c0 + j + 2]),
-                               "f"(old[j + 3] + v[c0 + j + 3]), "f"(old[j + 4] + v[c0 + j + 4]),
-                               "f"(old[j + 5] + v[c0 + j + 5]), "f"(old[j + 6] + v[c0 + j + 6]),
-                               "f"(old[j + 7] + v[c0 + j + 7]) : "memory");
-              } else if (n0 + c0 + 32 <= prm.N) {
+            for (int c0 = 0; c0 < 64; c0 += 16) {
 #pragma unroll
-                for (int j = 0; j < 32; j += 4) {
-                  const float4 old = *reinterpret_cast<const float4*>(o + j);
-                  *reinterpret_cast<float4*>(o + j) = make_float4(old.x + v[c0 + j], old.y + v[c0 + j + 1],
-                                                                  old.z + v[c0 + j + 2], old.w + v[c0 + j + 3]);
+              for (int e = 0; e < 16; e += 4) {
+                float4 gl = make_float4(rstd, rstd, rstd, rstd), gh = gl;
+                if (gain) {
+                  const float4 a = *reinterpret_cast<const float4*>(gain + c0 + e);
+                  const float4 b = *reinterpret_cast<const float4*>(gain + 64 + c0 + e);
+                  gl = make_float4(a.x * rstd, a.y * rstd, a.z * rstd, a.w * rstd);
+                  gh = make_float4(b.x * rstd, b.y * rstd, b.z * rstd, b.w * rstd);
+                }
+                const float4 cc = *reinterpret_cast<const float4*>(my_tab + c0 + e);
+                const float4 sv = *reinterpret_cast<const float4*>(my_tab + 64 + c0 + e);
+                const float cv[4] = {cc.x, cc.y, cc.z, cc.w}, sw[4] = {sv.x, sv.y, sv.z, sv.w};
+                const float g0[4] = {gl.x, gl.y, gl.z, gl.w}, g1[4] = {gh.x, gh.y, gh.z, gh.w};
+#pragma unroll
+                for (int i2 = 0; i2 < 4; ++i2) {
+                  const float x = v[c0 + e + i2] * g0[i2], y = v[64 + c0 + e + i2] * g1[i2];   // gain * x / rms
+                  v[c0 + e + i2] = x * cv[i2] - y * sw[i2];
+                  v[64 + c0 + e + i2] = y * cv[i2] + x * sw[i2];
+                }
+              }
+              store_bf16x16(dst + c0, v + c0, prm.wide);
+              store_bf16x16(dst + 64 + c0, v + 64 + c0, prm.wide);
+            }
+          }
+        } else {
+          const int n0 = tile_n * kPairTile + side * 128;     // this thread's columns: n0 .. n0 + 127
+          if (m < prm.M) {
+#pragma unroll
+            for (int c0 = 0; c0 < 128; c0 += 32) {
+              if (n0 + c0 >= prm.N) break;
+              if (EPI == PAIR_EPI_ADD_F32) {
+                float* o = (float*)prm.out + (size_t)m * prm.ldo + n0 + c0;
+                if (n0 + c0 + 32 <= prm.N && prm.wide) {
+                  float old[32];
+#pragma unroll
+                  for (int j = 0; j < 32; j += 8)
+                    asm volatile("ld.global.v8.f32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                                 : "=f"(old[j]), "=f"(old[j + 1]), "=f"(old[j + 2]), "=f"(old[j + 3]), "=f"(old[j + 4]),
+                                   "=f"(old[j + 5]), "=f"(old[j + 6]), "=f"(old[j + 7]) : "l"(o + j) : "memory");
+#pragma unroll
+                  for (int j = 0; j < 32; j += 8)
+                    asm volatile("st.global.v8.f32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(o + j),
+                                 "f"(old[j] + v[c0 + j]), "f"(old[j + 1] + v[c0 + j + 1]), "f"(old[j + 2] + v[c0 + j + 2]),
+                                 "f"(old[j + 3] + v[c0 + j + 3]), "f"(old[j + 4] + v[c0 + j + 4]),
+                                 "f"(old[j + 5] + v[c0 + j + 5]), "f"(old[j + 6] + v[c0 + j + 6]),
+                                 "f"(old[j + 7] + v[c0 + j + 7]) : "memory");
+                } else if (n0 + c0 + 32 <= prm.N) {
+#pragma unroll
+                  for (int j = 0; j < 32; j += 4) {
+                    const float4 old = *reinterpret_cast<const float4*>(o + j);
+                    *reinterpret_cast<float4*>(o + j) = make_float4(old.x + v[c0 + j], old.y + v[c0 + j + 1],
+                                                                    old.z + v[c0 + j + 2], old.w + v[c0 + j + 3]);
+                  }
+                } else {
+                  for (int e = 0; e < 32; ++e)
+                    if (n0 + c0 + e < prm.N) o[e] += v[c0 + e];
                 }
               } else {
-                for (int e = 0; e < 32; ++e)
-                  if (n0 + c0 + e < prm.N) o[e] += v[c0 + e];
-              }
-            } else {
-              bf16* o = (bf16*)prm.out + (size_t)m * prm.ldo + n0 + c0;
-              if (n0 + c0 + 32 <= prm.N) {
-                store_bf16x16(o, v + c0, prm.wide);
-                store_bf16x16(o + 16, v + c0 + 16, prm.wide);
-              } else {
-                for (int e = 0; e < 32; ++e)
-                  if (n0 + c0 + e < prm.N) o[e] = __float2bfloat16_rn(v[c0 + e]);
+                bf16* o = (bf16*)prm.out + (size_t)m * prm.ldo + n0 + c0;
+                if (n0 + c0 + 32 <= prm.N) {
+                  store_bf16x16(o, v + c0, prm.wide);
+                  store_bf16x16(o + 16, v + c0 + 16, prm.wide);
+                } else {
+                  for (int e = 0; e < 32; ++e)
+                    if (n0 + c0 + e < prm.N) o[e] = __float2bfloat16_rn(v[c0 + e]);
+                }
               }
             }
           }
         }
-      }
       }                                        // the unit's column tiles
       if (EPI == PAIR_EPI_QKV_ROPE && ok) {      // this warp has read the unit's angles for the last time
         __syncwarp();
